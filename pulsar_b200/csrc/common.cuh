@@ -1,0 +1,60 @@
+// Shared device helpers of the sm_100a kernels.
+//
+// Every launcher in this library is an extern "C" function that takes raw device
+// pointers, sizes and a cudaStream_t, launches on that stream, and returns the
+// cudaError_t of the launch as an int (0 = success, negative = an argument the
+// kernel refuses).  Nothing here allocates or synchronises.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define PB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Refusals (returned instead of a wrong result).
+#define PB_ERR_BAD_DTYPE (-2)
+#define PB_ERR_BAD_SIZE (-3)
+#define PB_ERR_TOO_LARGE (-4)
+
+enum PbDtype { PB_F32 = 0, PB_BF16 = 1 };
+
+namespace pb {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads, in a fixed order (lane tree, then warp 0's
+// lane tree over the warp partials), so the result does not depend on scheduling.
+// `scratch` needs 32 floats.  Every thread gets the total.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();   // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : 0.0f;
+    t = warp_sum(t);
+    return t;
+}
+
+inline int launch_status() { return (int)cudaPeekAtLastError(); }
+
+}  // namespace pb

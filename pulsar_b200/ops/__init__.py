@@ -1,0 +1,208 @@
+"""Typed Python wrappers over the C interface of the CUDA library.
+
+Each wrapper checks what the kernel cannot check itself (device, dtype, shape,
+contiguity), passes raw pointers and the current CUDA stream, and raises on any
+non-zero status.  There is no CPU path: a tensor that is not on a CUDA device is an
+error, and a missing library is an error at first use.
+
+The reference exposes its kernels as ``torch.ops.pulsar.*`` through TorchBind
+(pulsar/ext/ops.cpp:8-74; pulsar/src/pulsar/core/ops.py:198-494).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc.build import library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+_ERRORS = {-2: "unsupported dtype", -3: "unsupported size or argument", -4: "size exceeds the kernel's limit"}
+
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_SIGNATURES = {
+    "pb_embed": [_I, _P, _P, _P, _I, _I, _I, _P],
+    "pb_add_rmsnorm": [_I, _P, _P, _P, _P, _P, _I, _I, _F, _I, _P],
+    "pb_rope_table": [_P, _P, _P, _P, _I, _I, _P],
+    "pb_qk_norm_rope_write": [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P],
+    "pb_silu_mul": [_I, _P, _P, _I, _I, _P],
+    "pb_paged_attention_generic": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
+    "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _P, _P],
+}
+_fns = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def fn(name: str):
+    f = _fns.get(name)
+    if f is None:
+        f = getattr(library(), name)
+        f.argtypes = _SIGNATURES[name]
+        f.restype = ctypes.c_int
+        _fns[name] = f
+    return f
+
+
+def register_signature(name: str, argtypes) -> None:
+    _SIGNATURES[name] = list(argtypes)
+
+
+def check(status: int, name: str) -> None:
+    if status != 0:
+        what = _ERRORS.get(status, f"CUDA error {status}")
+        raise KernelError(f"{name}: {what}")
+
+
+def code(dtype: torch.dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not float32 or bfloat16") from None
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise KernelError("kernel arguments must be contiguous CUDA tensors "
+                              f"(found device {t.device}, contiguous={t.is_contiguous()}); there is no CPU path")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] (float32) = table[ids[t]]."""
+    _cuda(table, ids, out)
+    assert ids.dtype == torch.int32 and out.dtype == torch.float32 and out.shape == (ids.numel(), table.shape[1])
+    check(fn("pb_embed")(code(table.dtype), _p(table), _p(ids), _p(out), ids.numel(), table.shape[1], table.shape[0],
+                         stream()), "embed")
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
+    """x = residual (+ delta); residual = x when write_back; out = rmsnorm(x) * weight.
+    With ``rows`` only those rows are normalised, gathered into ``out``; the residual is left alone."""
+    _cuda(residual, delta, weight, out, rows)
+    width = residual.shape[-1]
+    assert residual.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == width
+    assert delta is None or (delta.dtype == out.dtype and delta.shape == residual.shape)
+    if rows is not None:
+        assert rows.dtype == torch.int32
+        write_back = False
+    n_out = rows.numel() if rows is not None else residual.shape[0]
+    assert out.shape == (n_out, width)
+    check(fn("pb_add_rmsnorm")(code(out.dtype), _p(residual), _p(delta), _p(weight), _p(out), _p(rows), n_out, width,
+                               float(eps), int(write_back), stream()), "add_rmsnorm")
+
+
+def rope_table(positions: torch.Tensor, quadrants_per_position: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> None:
+    _cuda(positions, quadrants_per_position, cos, sin)
+    half = quadrants_per_position.numel()
+    assert positions.dtype == torch.int32 and quadrants_per_position.dtype == torch.float64
+    assert cos.dtype == torch.float32 and sin.dtype == torch.float32
+    assert cos.shape == (positions.numel(), half) and sin.shape == cos.shape
+    check(fn("pb_rope_table")(_p(positions), _p(quadrants_per_position), _p(cos), _p(sin), positions.numel(), half,
+                              stream()), "rope_table")
+
+
+def qk_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor],
+                       v_pool: Optional[torch.Tensor], slots: Optional[torch.Tensor], cos: torch.Tensor,
+                       sin: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                       eps: float, n_heads: int, n_kv_heads: int, head_dim: int, rotary: int, page_size: int) -> None:
+    """Per-head RMSNorm (when weights are given) and rotation of q and k, q to ``q_out``,
+    k and v into their pages.  ``n_kv_heads`` 0: the row holds q only."""
+    _cuda(qkv, q_out, k_pool, v_pool, slots, cos, sin, q_weight, k_weight)
+    n = qkv.shape[0]
+    assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim and q_out.dtype == qkv.dtype
+    assert cos.shape == (n, rotary // 2) and sin.shape == cos.shape and cos.dtype == torch.float32
+    if n_kv_heads:
+        assert k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype and slots.dtype == torch.int32
+        assert k_pool.shape[1:] == (n_kv_heads, page_size, head_dim) and v_pool.shape == k_pool.shape
+    for w in (q_weight, k_weight):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == head_dim)
+    check(fn("pb_qk_norm_rope_write")(code(qkv.dtype), _p(qkv), _p(q_out), _p(k_pool), _p(v_pool), _p(slots), _p(cos),
+                                      _p(sin), _p(q_weight), _p(k_weight), float(eps), n, n_heads, n_kv_heads, head_dim,
+                                      rotary, page_size, stream()), "qk_norm_rope_write")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    _cuda(gate_up, out)
+    n, two_i = gate_up.shape
+    assert out.shape == (n, two_i // 2) and out.dtype == gate_up.dtype and two_i % 2 == 0
+    check(fn("pb_silu_mul")(code(out.dtype), _p(gate_up), _p(out), n, two_i // 2, stream()), "silu_mul")
+
+
+def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                            block_table: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                            seq_of_token: torch.Tensor, scale: float, window: Optional[int]) -> None:
+    _cuda(q, k_pool, v_pool, out, block_table, cu_q, kv_len, seq_of_token)
+    n, hq, d = q.shape
+    pages, hkv, page_size, d2 = k_pool.shape
+    assert d2 == d and v_pool.shape == k_pool.shape and out.shape == q.shape
+    assert k_pool.dtype == q.dtype and v_pool.dtype == q.dtype and out.dtype == q.dtype
+    for t in (block_table, cu_q, kv_len, seq_of_token):
+        assert t.dtype == torch.int32
+    assert block_table.dim() == 2 and seq_of_token.numel() == n
+    check(fn("pb_paged_attention_generic")(code(q.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
+                                           block_table.shape[1], _p(cu_q), _p(kv_len), _p(seq_of_token), n, hq, hkv, d,
+                                           page_size, float(scale), int(window or 0), stream()), "paged_attention_generic")
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = a @ w.T in float32 multiply-adds (no tensor cores)."""
+    _cuda(a, w, out)
+    m, k = a.shape
+    n, k2 = w.shape
+    assert k2 == k and out.shape == (m, n)
+    check(fn("pb_gemm_simt")(code(a.dtype), code(w.dtype), code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream()),
+          "gemm_simt")
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+           uniform: Optional[torch.Tensor] = None) -> None:
+    """out[r] = argmax (temperature <= 0 or None) or a draw from the filtered softmax."""
+    _cuda(logits, out, temperature, top_k, top_p, uniform)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == rows
+    assert temperature is None or (temperature.dtype == torch.float32 and temperature.numel() == rows)
+    assert top_k is None or (top_k.dtype == torch.int32 and top_k.numel() == rows)
+    assert top_p is None or (top_p.dtype == torch.float32 and top_p.numel() == rows)
+    assert uniform is None or (uniform.dtype == torch.float32 and uniform.numel() == rows)
+    check(fn("pb_sample")(_p(logits), rows, vocab, _p(temperature), _p(top_k), _p(top_p), _p(uniform), _p(out),
+                          stream()), "sample")
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = a @ w.T.  float32 operands take the float32 CUDA-core product (true 32-bit,
+    no reduced-precision mode).  bfloat16 operands take the library product with
+    float32 accumulation, as the reference does for every projection
+    (pulsar-core/src/model/qwen3.cpp:82-84: at::linear)."""
+    if a.dtype == torch.float32 and w.dtype == torch.float32:
+        gemm_simt(a, w, out)
+        return
+    _cuda(a, w, out)
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"linear: operand dtypes {a.dtype} / {w.dtype} must both be float32 or both bfloat16")
+    if out.dtype == torch.bfloat16:
+        torch.mm(a, w.t(), out=out)
+    else:
+        out.copy_(torch.mm(a, w.t(), out_dtype=torch.float32))
+
+
+def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, window: Optional[int]) -> None:
+    """Attention of the step's query tokens over their pages.  ``cache`` is a CacheView
+    (pools, block table), ``ctx`` the StepContext (cu_q, kv_len, seq_of_token)."""
+    paged_attention_generic(q, cache.k_pool, cache.v_pool, out, cache.block_table, ctx.cu_q, ctx.kv_len,
+                            ctx.seq_of_token, scale, window)
