@@ -55,6 +55,7 @@ class ModelRunner:
         self._staging_next = 0
         self._index_buf: Optional[torch.Tensor] = None
         self.steps_run = 0
+        self.h2d_bytes = 0          # bytes of index arrays copied to the device so far
 
     # ------------------------------------------------------------------ memory
     def scratch(self, tag: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
@@ -182,6 +183,7 @@ class ModelRunner:
             self.scratch_epoch += 1
         dev = self._index_buf
         dev[:total].copy_(stage[:total], non_blocking=True)
+        self.h2d_bytes += total * 4
         ev = torch.cuda.Event()
         ev.record()
         self._staging_events[self._staging_slot] = ev

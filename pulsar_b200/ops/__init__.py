@@ -53,7 +53,12 @@ def register_signature(name: str, argtypes) -> None:
     _SIGNATURES[name] = list(argtypes)
 
 
-def check(status: int, name: str) -> None:
+LAUNCHES = 0      # kernels of this library launched so far (each wrapper call launches one or more)
+
+
+def check(status: int, name: str, kernels: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += kernels
     if status != 0:
         what = _ERRORS.get(status, f"CUDA error {status}")
         raise KernelError(f"{name}: {what}")
