@@ -1,0 +1,237 @@
+// Paged decode attention, split over the keys: every sequence of the batch brings one
+// query token.  One block handles (split of the keys, kv head, sequence) for all query
+// heads of that kv head's group, so a key or value row is fetched once for the group;
+// the block writes an unnormalised partial (running maximum, sum, accumulator) per head
+// to scratch memory and a second kernel merges the partials in split order.
+//
+// The grid does not depend on the context length: split i of n covers keys
+// [lo + i*chunk, lo + (i+1)*chunk) with chunk = ceil(n_keys / n) rounded up to a tile,
+// computed on the device from kv_len, so a captured launch stays valid as the
+// sequences grow.  Splits past the end write an empty partial.
+//
+// Scores, softmax and accumulators are float32 (expf); any group size, any head size
+// that is a multiple of 16 up to 256, float32 or bfloat16 storage, optional window.
+//
+// Role in the reference: pulsar-core/src/kernels/paged_attention.cu:295-412
+// (paged_decode_split_kernel, paged_decode_combine_kernel; auto_splits :432-438).
+#include "common.cuh"
+
+namespace {
+
+using namespace pb;
+
+constexpr int kWarps = 4;
+constexpr int kMaxD = 256;
+constexpr int kAcc = kMaxD / 32;
+constexpr int kGP = 4;          // query heads handled per pass over the keys
+
+__device__ __forceinline__ void load_row16(const float* p, float (&f)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void load_row16(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// partial layout: [S, Hq, n_splits, D + 2] floats: acc[D], m, l
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                    float* __restrict__ partial, const int* __restrict__ block_table, int table_stride,
+                    const int* __restrict__ kv_len, int Hq, int Hkv, int D, int page_size, float scale, int window,
+                    int n_splits) {
+    extern __shared__ float smem[];
+    const int G = Hq / Hkv;
+    float* q_s = smem;                                  // [kGP][D]
+    float* p_s = q_s + kGP * D;                         // [kWarps][kGP][32]
+    float* m_s = p_s + kWarps * kGP * 32;               // [kWarps][kGP]
+    float* l_s = m_s + kWarps * kGP;                    // [kWarps][kGP]
+    float* acc_s = l_s + kWarps * kGP;                  // [kWarps][kGP][D]
+
+    const int split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int p = kv_len[s] - 1;                        // position of the query token
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int n_keys = p - lo + 1;
+    int chunk = (n_keys + n_splits - 1) / n_splits;
+    chunk = (chunk + 31) & ~31;
+    const int begin = lo + split * chunk;
+    const int end = min(p + 1, begin + chunk);          // keys [begin, end)
+    const int* table = block_table + (size_t)s * table_stride;
+    const int stride = D + 2;
+
+    for (int g0 = 0; g0 < G; g0 += kGP) {
+        const int gn = min(kGP, G - g0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < gn * D; i += blockDim.x) {
+            const int g = i / D, d = i - g * D;
+            q_s[g * D + d] = to_float(q[((size_t)s * Hq + kvh * G + g0 + g) * D + d]) * scale;
+        }
+        __syncthreads();
+
+        float m_run[kGP], l_run[kGP], acc[kGP][kAcc];
+#pragma unroll
+        for (int g = 0; g < kGP; ++g) {
+            m_run[g] = -INFINITY; l_run[g] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kAcc; ++i) acc[g][i] = 0.0f;
+        }
+
+        for (int j0 = begin + warp * 32; j0 < end; j0 += kWarps * 32) {
+            const int j = j0 + lane;
+            const bool valid = j < end;
+            float sc[kGP];
+#pragma unroll
+            for (int g = 0; g < kGP; ++g) sc[g] = 0.0f;
+            if (valid) {
+                const int page = table[j / page_size];
+                const T* kr = k_pool + (((size_t)page * Hkv + kvh) * page_size + j % page_size) * D;
+                for (int d = 0; d < D; d += 8) {
+                    float kf[8];
+                    load_row16(kr + d, kf);
+#pragma unroll
+                    for (int g = 0; g < kGP; ++g) {
+                        if (g < gn) {
+                            const float4 qa = *reinterpret_cast<const float4*>(q_s + g * D + d);
+                            const float4 qb = *reinterpret_cast<const float4*>(q_s + g * D + d + 4);
+                            sc[g] = fmaf(qa.x, kf[0], sc[g]); sc[g] = fmaf(qa.y, kf[1], sc[g]);
+                            sc[g] = fmaf(qa.z, kf[2], sc[g]); sc[g] = fmaf(qa.w, kf[3], sc[g]);
+                            sc[g] = fmaf(qb.x, kf[4], sc[g]); sc[g] = fmaf(qb.y, kf[5], sc[g]);
+                            sc[g] = fmaf(qb.z, kf[6], sc[g]); sc[g] = fmaf(qb.w, kf[7], sc[g]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int g = 0; g < kGP; ++g) {
+                if (g < gn) {
+                    const float m_new = fmaxf(m_run[g], warp_max(valid ? sc[g] : -INFINITY));
+                    const float pv = valid ? expf(sc[g] - m_new) : 0.0f;
+                    const float corr = expf(m_run[g] - m_new);
+                    l_run[g] = l_run[g] * corr + warp_sum(pv);
+                    m_run[g] = m_new;
+#pragma unroll
+                    for (int i = 0; i < kAcc; ++i) acc[g][i] *= corr;
+                    p_s[(warp * kGP + g) * 32 + lane] = pv;
+                }
+            }
+            __syncwarp();
+            const int n_here = min(32, end - j0);
+            for (int kk = 0; kk < n_here; ++kk) {
+                const int jj = j0 + kk;
+                const int page = table[jj / page_size];
+                const T* vr = v_pool + (((size_t)page * Hkv + kvh) * page_size + jj % page_size) * D;
+                float vf[kAcc];
+#pragma unroll
+                for (int i = 0; i < kAcc; ++i) {
+                    const int d = lane + 32 * i;
+                    vf[i] = d < D ? to_float(vr[d]) : 0.0f;
+                }
+#pragma unroll
+                for (int g = 0; g < kGP; ++g) {
+                    if (g < gn) {
+                        const float pk = p_s[(warp * kGP + g) * 32 + kk];
+#pragma unroll
+                        for (int i = 0; i < kAcc; ++i) acc[g][i] = fmaf(pk, vf[i], acc[g][i]);
+                    }
+                }
+            }
+        }
+
+        // merge the warps in index order
+#pragma unroll
+        for (int g = 0; g < kGP; ++g) {
+            if (g < gn) {
+                if (lane == 0) { m_s[warp * kGP + g] = m_run[g]; l_s[warp * kGP + g] = l_run[g]; }
+#pragma unroll
+                for (int i = 0; i < kAcc; ++i) {
+                    const int d = lane + 32 * i;
+                    if (d < D) acc_s[(warp * kGP + g) * D + d] = acc[g][i];
+                }
+            }
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < gn * D; i += blockDim.x) {
+            const int g = i / D, d = i - g * D;
+            float m_all = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) m_all = fmaxf(m_all, m_s[w * kGP + g]);
+            float o = 0.0f, l_all = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float f = (m_all == -INFINITY) ? 0.0f : expf(m_s[w * kGP + g] - m_all);
+                o += acc_s[(w * kGP + g) * D + d] * f;
+                l_all += l_s[w * kGP + g] * f;
+            }
+            float* dst = partial + (((size_t)s * Hq + kvh * G + g0 + g) * n_splits + split) * stride;
+            dst[d] = o;
+            if (d == 0) { dst[D] = m_all; dst[D + 1] = l_all; }
+        }
+    }
+}
+
+template <typename T>
+__global__ void decode_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int D, int n_splits) {
+    const size_t row = blockIdx.x;                       // s * Hq + h
+    const int stride = D + 2;
+    const float* base = partial + row * n_splits * stride;
+    float m_all = -INFINITY;
+    for (int i = 0; i < n_splits; ++i) m_all = fmaxf(m_all, base[i * stride + D]);
+    float l_all = 0.0f;
+    for (int i = 0; i < n_splits; ++i) {
+        const float m = base[i * stride + D];
+        if (m > -INFINITY) l_all += base[i * stride + D + 1] * expf(m - m_all);
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float o = 0.0f;
+        for (int i = 0; i < n_splits; ++i) {
+            const float m = base[i * stride + D];
+            if (m > -INFINITY) o += base[i * stride + d] * expf(m - m_all);
+        }
+        out[row * D + d] = from_float<T>(o / l_all);
+    }
+}
+
+size_t split_smem(int D) {
+    return sizeof(float) * ((size_t)kGP * D + kWarps * kGP * 32 + 2 * kWarps * kGP + (size_t)kWarps * kGP * D);
+}
+
+}  // namespace
+
+// Floats of scratch the split kernel writes and the combine kernel reads.
+PB_EXPORT long long pb_decode_scratch_floats(int n_seqs, int Hq, int D, int n_splits) {
+    return (long long)n_seqs * Hq * n_splits * (D + 2);
+}
+
+// q, out [S, Hq, D] (one query token per sequence); partial: pb_decode_scratch_floats floats.
+PB_EXPORT int pb_paged_attention_decode(int dtype, const void* q, const void* k_pool, const void* v_pool, void* out,
+                                        float* partial, const int* block_table, int table_stride, const int* kv_len,
+                                        int n_seqs, int Hq, int Hkv, int D, int page_size, float scale, int window,
+                                        int n_splits, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (D <= 0 || D % 16 || D > kMaxD || Hkv <= 0 || Hq % Hkv || page_size <= 0 || n_splits <= 0) return PB_ERR_BAD_SIZE;
+    if (Hkv > 65535 || n_seqs > 65535) return PB_ERR_TOO_LARGE;
+    const size_t smem = split_smem(D);
+    dim3 grid(n_splits, Hkv, n_seqs);
+    if (dtype == PB_F32) {
+        decode_split_kernel<float><<<grid, kWarps * 32, smem, stream>>>((const float*)q, (const float*)k_pool,
+            (const float*)v_pool, partial, block_table, table_stride, kv_len, Hq, Hkv, D, page_size, scale, window, n_splits);
+        decode_combine_kernel<float><<<n_seqs * Hq, 128, 0, stream>>>(partial, (float*)out, D, n_splits);
+    } else if (dtype == PB_BF16) {
+        decode_split_kernel<__nv_bfloat16><<<grid, kWarps * 32, smem, stream>>>((const __nv_bfloat16*)q,
+            (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, partial, block_table, table_stride, kv_len, Hq, Hkv, D,
+            page_size, scale, window, n_splits);
+        decode_combine_kernel<__nv_bfloat16><<<n_seqs * Hq, 128, 0, stream>>>(partial, (__nv_bfloat16*)out, D, n_splits);
+    } else {
+        return PB_ERR_BAD_DTYPE;
+    }
+    return launch_status();
+}

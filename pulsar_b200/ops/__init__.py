@@ -29,6 +29,7 @@ _SIGNATURES = {
     "pb_qk_norm_rope_write": [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P],
     "pb_silu_mul": [_I, _P, _P, _I, _I, _P],
     "pb_paged_attention_generic": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "pb_paged_attention_decode": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _P, _P],
 }
@@ -206,8 +207,40 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         out.copy_(torch.mm(a, w.t(), out_dtype=torch.float32))
 
 
+def decode_splits(n_seqs: int, n_kv_heads: int) -> int:
+    """Splits of the keys per (sequence, kv head): enough blocks to fill 148 SMs four
+    times over.  A function of the batch alone, so that a captured step stays valid
+    while its sequences grow."""
+    return max(1, min(64, -(-592 // max(1, n_seqs * n_kv_heads))))
+
+
+def paged_attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                           partial: torch.Tensor, block_table: torch.Tensor, kv_len: torch.Tensor, scale: float,
+                           window: Optional[int], n_splits: int) -> None:
+    """One query token per sequence: q, out [S, Hq, D].  ``partial`` is float32 scratch of at
+    least S * Hq * n_splits * (D + 2) elements."""
+    _cuda(q, k_pool, v_pool, out, partial, block_table, kv_len)
+    s, hq, d = q.shape
+    pages, hkv, page_size, d2 = k_pool.shape
+    assert d2 == d and v_pool.shape == k_pool.shape and out.shape == q.shape and kv_len.numel() == s
+    assert k_pool.dtype == q.dtype and v_pool.dtype == q.dtype and out.dtype == q.dtype
+    assert block_table.dtype == torch.int32 and kv_len.dtype == torch.int32 and block_table.shape[0] == s
+    assert partial.dtype == torch.float32 and partial.numel() >= s * hq * n_splits * (d + 2)
+    check(fn("pb_paged_attention_decode")(code(q.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(partial),
+                                          _p(block_table), block_table.shape[1], _p(kv_len), s, hq, hkv, d, page_size,
+                                          float(scale), int(window or 0), n_splits, stream()),
+          "paged_attention_decode", kernels=2)
+
+
 def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, window: Optional[int]) -> None:
     """Attention of the step's query tokens over their pages.  ``cache`` is a CacheView
-    (pools, block table), ``ctx`` the StepContext (cu_q, kv_len, seq_of_token)."""
+    (pools, block table), ``ctx`` the StepContext (cu_q, kv_len, seq_of_token).  A step of
+    single tokens only takes the split-key decode kernel; anything else the generic one."""
+    if ctx.all_decode:
+        n_splits = decode_splits(ctx.n_seqs, cache.k_pool.shape[1])
+        partial = ctx.scratch("attn.partial", (ctx.n_seqs * q.shape[1] * n_splits * (q.shape[2] + 2),), torch.float32)
+        paged_attention_decode(q, cache.k_pool, cache.v_pool, out, partial, cache.block_table, ctx.kv_len, scale,
+                               window, n_splits)
+        return
     paged_attention_generic(q, cache.k_pool, cache.v_pool, out, cache.block_table, ctx.cu_q, ctx.kv_len,
                             ctx.seq_of_token, scale, window)

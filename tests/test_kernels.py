@@ -1,0 +1,354 @@
+"""Each CUDA kernel alone against a plain float64 reference of the same operation, at
+sizes other than the engine's tiny models: widths and vocabularies that are no power of
+two, head sizes in steps of 16, odd group sizes, ragged contexts, shuffled pages."""
+import math
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-5, torch.bfloat16: 1.6e-2}
+
+
+def dev(t):
+    return t.to("cuda")
+
+
+def close(got, ref, tol, what=""):
+    ref = ref.to(torch.float64)
+    err = float((got.detach().cpu().to(torch.float64) - ref.cpu()).abs().max() / ref.abs().max().clamp_min(1e-30))
+    assert err < tol, f"{what}: relative error {err:.3e} >= {tol}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,vocab", [(72, 301), (4096, 1000)])
+def test_embed(dtype, width, vocab):
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(vocab, width, generator=g).to(dtype)
+    ids = torch.tensor([0, vocab - 1, 5, 5, 17], dtype=torch.int32)
+    out = torch.empty(5, width, dtype=torch.float32, device="cuda")
+    ops.embed(dev(table), dev(ids), out)
+    assert torch.equal(out.cpu(), table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [48, 100, 4096, 5120])
+def test_add_rmsnorm(dtype, width):
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(1)
+    n, eps = 7, 3e-6
+    res = torch.randn(n, width, generator=g) * 3
+    res[2] = 0.0                                  # the all-zero row that only eps keeps finite
+    delta = (torch.randn(n, width, generator=g)).to(dtype)
+    delta[2] = 0
+    w = 1 + 0.1 * torch.randn(width, generator=g)
+    x = res.double() + delta.double()
+    ref = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.double()
+    r = dev(res.clone())
+    out = torch.empty(n, width, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(r, dev(delta), dev(w), eps, out)
+    close(out, ref, TOL[dtype], "normalised")
+    close(r, x, 1e-6, "residual written back")
+    assert torch.isfinite(out).all() and float(out[2].abs().max()) == 0.0
+    # gathered rows: residual untouched
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    r2 = dev(res.clone())
+    out2 = torch.empty(3, width, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(r2, dev(delta), dev(w), eps, out2, rows=dev(rows))
+    close(out2, ref[rows.long()], TOL[dtype], "gathered rows")
+    assert torch.equal(r2.cpu(), res)
+    # without delta
+    out3 = torch.empty(n, width, dtype=dtype, device="cuda")
+    r3 = dev(res.clone())
+    ops.add_rmsnorm(r3, None, dev(w), eps, out3)
+    x3 = res.double()
+    close(out3, x3 * torch.rsqrt((x3 * x3).mean(-1, keepdim=True) + eps) * w.double(), TOL[dtype], "no delta")
+
+
+@pytest.mark.parametrize("theta,rotary", [(1e4, 16), (1e6, 128), (5e5, 48)])
+def test_rope_table_large_positions(theta, rotary):
+    from pulsar_b200 import ops
+    pos = torch.tensor([0, 1, 2, 17, 4095, 32767, 131071, 1000003], dtype=torch.int32)
+    half = rotary // 2
+    inv = torch.tensor([theta ** (-2.0 * j / rotary) for j in range(half)], dtype=torch.float64)
+    ang = pos.double()[:, None] * inv[None, :]
+    cos = torch.empty(len(pos), half, dtype=torch.float32, device="cuda")
+    sin = torch.empty_like(cos)
+    ops.rope_table(dev(pos), dev(inv * (2.0 / math.pi)), cos, sin)
+    assert float((cos.cpu().double() - torch.cos(ang)).abs().max()) < 1e-6
+    assert float((sin.cpu().double() - torch.sin(ang)).abs().max()) < 1e-6
+
+
+def _rope_ref(x, pos, theta, rotary):
+    d = x.shape[-1]
+    half = rotary // 2
+    inv = torch.tensor([theta ** (-2.0 * j / rotary) for j in range(half)], dtype=torch.float64)
+    ang = pos.double()[:, None] * inv[None, :]
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    a, b = x[..., :half], x[..., half:rotary]
+    return torch.cat([a * c - b * s, b * c + a * s, x[..., rotary:]], dim=-1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,rotary,page,norm", [(4, 2, 16, 16, 16, True), (6, 3, 48, 48, 4, True),
+                                                       (5, 5, 80, 32, 8, False), (32, 8, 128, 128, 16, True),
+                                                       (3, 0, 32, 32, 8, True)])
+def test_qk_norm_rope_write(dtype, hq, hkv, d, rotary, page, norm):
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    n, pages, theta, eps = 11, 9, 1e5, 1e-5
+    qkv = torch.randn(n, (hq + 2 * hkv) * d, generator=g).to(dtype)
+    pos = torch.randint(0, 5000, (n,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * page, generator=g)[:n].to(torch.int32)
+    slots[4] = -1                                                 # a token whose k/v is not stored
+    qw = (1 + 0.1 * torch.randn(d, generator=g)) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, generator=g)) if norm else None
+    half = rotary // 2
+    inv = torch.tensor([theta ** (-2.0 * j / rotary) for j in range(half)], dtype=torch.float64)
+    cos = torch.empty(n, half, dtype=torch.float32, device="cuda")
+    sin = torch.empty_like(cos)
+    ops.rope_table(dev(pos), dev(inv * (2.0 / math.pi)), cos, sin)
+    q_out = torch.empty(n, hq, d, dtype=dtype, device="cuda")
+    kp = torch.full((pages, max(hkv, 1), page, d), 7.0, dtype=dtype, device="cuda") if hkv else None
+    vp = torch.full((pages, max(hkv, 1), page, d), 7.0, dtype=dtype, device="cuda") if hkv else None
+    ops.qk_norm_rope_write(dev(qkv), q_out, kp, vp, dev(slots) if hkv else None, cos, sin,
+                           dev(qw) if norm else None, dev(kw) if norm else None, eps, hq, hkv, d, rotary, page)
+    x = qkv.double()
+    q = x[:, :hq * d].view(n, hq, d)
+
+    def normed(t, w):
+        if w is None:
+            return t
+        return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * w.double()
+    close(q_out, _rope_ref(normed(q, qw), pos, theta, rotary), TOL[dtype], "q")
+    if hkv:
+        k = x[:, hq * d:(hq + hkv) * d].view(n, hkv, d)
+        v = x[:, (hq + hkv) * d:].view(n, hkv, d)
+        k_ref = _rope_ref(normed(k, kw), pos, theta, rotary)
+        kc, vc = kp.cpu().double(), vp.cpu().double()
+        untouched = torch.ones(pages * page, dtype=torch.bool)
+        for t in range(n):
+            sl = int(slots[t])
+            if sl < 0:
+                continue
+            untouched[sl] = False
+            close(kc[sl // page, :, sl % page, :], k_ref[t], TOL[dtype], f"k of token {t}")
+            assert torch.equal(vc[sl // page, :, sl % page, :], v[t]), "v is a plain copy"
+        flat = kc.permute(0, 2, 1, 3).reshape(pages * page, -1)
+        assert bool((flat[untouched] == 7.0).all()), "slots that were not addressed stay untouched"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [24, 176, 12288])
+def test_silu_mul(dtype, inter):
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    gu = (torch.randn(5, 2 * inter, generator=g) * 3).to(dtype)
+    out = torch.empty(5, inter, dtype=dtype, device="cuda")
+    ops.silu_mul(dev(gu), out)
+    a, b = gu.double()[:, :inter], gu.double()[:, inter:]
+    close(out, a * torch.sigmoid(a) * b, TOL[dtype])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (3, 130, 70), (65, 64, 33), (128, 301, 96), (200, 512, 1000)])
+def test_gemm_simt_is_true_float32(m, n, k):
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(4)
+    a, w = torch.randn(m, k, generator=g), torch.randn(n, k, generator=g)
+    out = torch.empty(m, n, dtype=torch.float32, device="cuda")
+    ops.gemm_simt(dev(a), dev(w), out)
+    close(out, a.double() @ w.double().T, 2e-6 * max(1, k / 64) ** 0.5)
+    # rows do not depend on which other rows are in the batch: bit-equal
+    if m > 2:
+        out2 = torch.empty(2, n, dtype=torch.float32, device="cuda")
+        ops.gemm_simt(dev(a[m - 2:].contiguous()), dev(w), out2)
+        assert torch.equal(out2, out[m - 2:])
+
+
+def test_gemm_simt_mixed_dtypes():
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    a, w = torch.randn(9, 100, generator=g).bfloat16(), torch.randn(37, 100, generator=g).bfloat16()
+    out = torch.empty(9, 37, dtype=torch.float32, device="cuda")
+    ops.gemm_simt(dev(a), dev(w), out)
+    close(out, a.double() @ w.double().T, 1e-5)
+
+
+# ------------------------------------------------------------------ attention
+def _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype, spike=None):
+    """Random q and a shuffled paged cache for sequences with the given new / total lengths."""
+    s = len(lens_q)
+    n = sum(lens_q)
+    pages_per = [-(-kv // page) for kv in lens_kv]
+    total_pages = sum(pages_per) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    width = max(pages_per)
+    table = torch.full((s, width), -1, dtype=torch.int32)
+    k_seq = [torch.randn(kv, hkv, d, generator=g) for kv in lens_kv]
+    v_seq = [torch.randn(kv, hkv, d, generator=g) for kv in lens_kv]
+    q = torch.randn(n, hq, d, generator=g)
+    if spike is not None:                 # one far key stands out: a kernel that loses it shows
+        si, key, head = spike
+        qrow = sum(lens_q[:si]) + lens_q[si] - 1
+        k_seq[si][key, head // (hq // hkv)] = q[qrow, head] * 6.0
+        v_seq[si][key, head // (hq // hkv)] = 50.0
+    kp = torch.zeros(total_pages, hkv, page, d)
+    vp = torch.zeros(total_pages, hkv, page, d)
+    at = 0
+    for i in range(s):
+        for lp in range(pages_per[i]):
+            pg = perm[at]
+            at += 1
+            table[i, lp] = pg
+            lo, hi = lp * page, min(lens_kv[i], (lp + 1) * page)
+            kp[pg, :, :hi - lo] = k_seq[i][lo:hi].permute(1, 0, 2)
+            vp[pg, :, :hi - lo] = v_seq[i][lo:hi].permute(1, 0, 2)
+    cu = [0]
+    for ql in lens_q:
+        cu.append(cu[-1] + ql)
+    seq_of = [i for i, ql in enumerate(lens_q) for _ in range(ql)]
+    q, kp, vp = q.to(dtype), kp.to(dtype), vp.to(dtype)
+    k_seq = [k.to(dtype).double() for k in k_seq]
+    v_seq = [v.to(dtype).double() for v in v_seq]
+    return dict(q=q, kp=kp, vp=vp, table=table, cu=torch.tensor(cu, dtype=torch.int32),
+                kv=torch.tensor(lens_kv, dtype=torch.int32), seq_of=torch.tensor(seq_of, dtype=torch.int32),
+                k_seq=k_seq, v_seq=v_seq)
+
+
+def _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window):
+    q = case["q"].double()
+    out = torch.zeros_like(q)
+    row = 0
+    for i, (ql, kv) in enumerate(zip(lens_q, lens_kv)):
+        for t in range(ql):
+            p = kv - ql + t
+            lo = max(0, p - window + 1) if window else 0
+            for h in range(hq):
+                g = h // (hq // hkv)
+                sc = (case["k_seq"][i][lo:p + 1, g] @ q[row, h]) * scale
+                out[row, h] = torch.softmax(sc, 0) @ case["v_seq"][i][lo:p + 1, g]
+            row += 1
+    return out
+
+
+ATTN_SHAPES = [  # hq, hkv, d, page
+    (4, 2, 16, 16), (8, 2, 32, 8), (6, 3, 48, 4), (5, 5, 64, 16), (32, 8, 128, 16), (14, 2, 96, 32), (3, 1, 256, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", ATTN_SHAPES)
+@pytest.mark.parametrize("window", [None, 37])
+def test_attention_generic_mixed_batch(dtype, hq, hkv, d, page, window):
+    """First portions, later portions and single tokens in one ragged batch
+    (the (new, total) pairs of pulsar/tests/test_paged_prefill.py:45-50 and more)."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(6)
+    lens_q = [16, 7, 33, 1, 1, 2, 64]
+    lens_kv = [16, 40, 33, 65, 1, 129, 100]
+    case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype, spike=(5, 3, hq - 1))
+    out = torch.empty(sum(lens_q), hq, d, dtype=dtype, device="cuda")
+    scale = 1.0 / math.sqrt(d)
+    ops.paged_attention_generic(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, dev(case["table"]), dev(case["cu"]),
+                                dev(case["kv"]), dev(case["seq_of"]), scale, window)
+    close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", ATTN_SHAPES)
+@pytest.mark.parametrize("window", [None, 50])
+@pytest.mark.parametrize("n_splits", [1, 3, 8, 64])
+def test_attention_decode_split(dtype, hq, hkv, d, page, window, n_splits):
+    """Ragged contexts of pulsar/tests/test_paged_attention.py:21-45, forced split counts
+    (empty splits included), one far key made to stand out."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(7)
+    lens_kv = [1, 7, 16, 33, 40, 65, 100, 129, 700]
+    lens_q = [1] * len(lens_kv)
+    case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype, spike=(8, 5, 0))
+    out = torch.empty(len(lens_kv), hq, d, dtype=dtype, device="cuda")
+    partial = torch.empty(len(lens_kv) * hq * n_splits * (d + 2), dtype=torch.float32, device="cuda")
+    scale = 1.0 / math.sqrt(d)
+    ops.paged_attention_decode(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, partial, dev(case["table"]),
+                               dev(case["kv"]), scale, window, n_splits)
+    close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window), TOL[dtype])
+
+
+def test_attention_refuses_bad_sizes():
+    from pulsar_b200 import ops
+    q = torch.zeros(1, 2, 24, device="cuda")           # head size 24 is no multiple of 16
+    kp = torch.zeros(1, 1, 16, 24, device="cuda")
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="unsupported size"):
+        ops.paged_attention_generic(q, kp, kp, torch.empty_like(q), z.view(1, 1), torch.tensor([0, 1], dtype=torch.int32).cuda(),
+                                    z + 1, z, 1.0, None)
+    with pytest.raises(ops.KernelError, match="no CPU path"):
+        ops.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
+
+
+# ------------------------------------------------------------------ sampling
+def test_argmax_lowest_index_on_ties():
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(8)
+    logits = torch.randn(6, 151936 // 8 + 3, generator=g)
+    logits[1, 77] = logits[1, 9000] = 50.0
+    logits[2, -1] = 60.0
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), out)
+    ref = torch.argmax(logits, dim=-1)
+    ref[1] = 77
+    assert out.cpu().tolist() == ref.tolist()
+
+
+def _survivors(row, temperature, top_k, top_p):
+    import sys, os
+    sys.path.insert(0, os.path.dirname(__file__))
+    from plain import qwen3_plain as plain
+    return plain.sample_filter(row, temperature, top_k, top_p)
+
+
+@pytest.mark.parametrize("top_k,top_p", [(0, 1.0), (5, 1.0), (0, 0.7), (3, 0.9), (50, 0.3)])
+def test_sample_survivors_and_inverse_cdf(top_k, top_p):
+    """Logits built as log(probs) so the surviving set is known
+    (pulsar-core/tests/runtime/test_sampler.cpp:56-135)."""
+    from pulsar_b200 import ops
+    vocab, temperature = 1000, 0.8
+    g = torch.Generator().manual_seed(9)
+    probs = torch.rand(vocab, generator=g).double() ** 4 + 1e-4
+    probs /= probs.sum()
+    logits = (torch.log(probs) * temperature).float()       # softmax(logits / T) == probs
+    rows = 64
+    uniform = (torch.arange(rows, dtype=torch.float32) + 0.5) / rows
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits.repeat(rows, 1)), out, dev(torch.full((rows,), temperature)),
+               dev(torch.full((rows,), top_k, dtype=torch.int32)), dev(torch.full((rows,), top_p)), dev(uniform))
+    sp, si = _survivors(logits, temperature, top_k, top_p)
+    keep = torch.zeros(vocab, dtype=torch.bool)
+    keep[si] = True
+    got = out.cpu().long()
+    assert bool(keep[got].all()), "a token outside the surviving set was drawn"
+    # inverse CDF over the survivors in index order
+    p = torch.softmax(logits.double() / temperature, 0) * keep
+    cdf = torch.cumsum(p, 0)
+    for r in range(rows):
+        target = float(uniform[r]) * float(p.sum())
+        want = int(torch.searchsorted(cdf, torch.tensor(target, dtype=torch.float64), right=True))
+        assert abs(float(cdf[got[r]]) - float(cdf[want])) <= 2e-6 or got[r] == want, (r, int(got[r]), want)
+
+
+def test_sample_mixed_rows_and_greedy_ignores_filters():
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(10)
+    logits = torch.randn(4, 333, generator=g) * 3
+    out = torch.empty(4, dtype=torch.int32, device="cuda")
+    temp = torch.tensor([0.0, 1.0, 0.0, 0.5])
+    ops.sample(dev(logits), out, dev(temp), dev(torch.tensor([1, 1, 7, 0], dtype=torch.int32)),
+               dev(torch.tensor([0.1, 1.0, 0.5, 1.0])), dev(torch.tensor([0.9, 0.9, 0.9, 0.0])))
+    got = out.cpu().tolist()
+    am = torch.argmax(logits, -1).tolist()
+    assert got[0] == am[0] and got[2] == am[2]
+    assert got[1] == am[1]              # top_k 1 leaves only the most probable
+    assert 0 <= got[3] < 333
