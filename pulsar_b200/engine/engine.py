@@ -73,7 +73,7 @@ class Engine:
         if cfg.max_running > cfg.max_sessions:        # engine.cpp:121-140
             raise ValueError("max_running must not exceed max_sessions")
         self.cache = CacheManager(model.cache_needs(), cfg.page_size, cfg.num_pages, cfg.max_sessions, model.dtype, cfg.device)
-        self.runner = ModelRunner(model, self.cache, cfg.device)
+        self.runner = ModelRunner(model, self.cache, cfg.device, cuda_graphs=cfg.cuda_graphs)
         self.scheduler = Scheduler(self.cache, cfg.max_running, cfg.max_chunk_size)
         self.sampler = Sampler(cfg.device)
         self.eos_id = cfg.eos_id

@@ -15,6 +15,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager, OutOfPages
 from ..parts.base import CacheView, HostBatch, StepContext
 
@@ -40,8 +41,9 @@ class ModelRunner:
     """Owns the scratch memory and the per-step index arrays; drives the model over the cache."""
 
     N_STAGING = 4
+    TABLE_BUCKET = 64          # block-table width of decode steps is rounded up to this many pages
 
-    def __init__(self, model, cache: CacheManager, device):
+    def __init__(self, model, cache: CacheManager, device, cuda_graphs: bool = True):
         self.model, self.cache = model, cache
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -55,6 +57,14 @@ class ModelRunner:
         self._staging_next = 0
         self._index_buf: Optional[torch.Tensor] = None
         self.steps_run = 0
+        # Decode steps (one token per request) are launch-bound: their kernel sequence is
+        # captured once per (batch size, block-table width) and replayed.
+        self.cuda_graphs = bool(cuda_graphs)
+        self._graphs: Dict[tuple, Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
+        self._graph_seen: Dict[tuple, int] = {}
+        self._graph_epoch = -1
+        self.graph_replays = 0
+        self._capturing = False
         self.h2d_bytes = 0          # bytes of index arrays copied to the device so far
 
     # ------------------------------------------------------------------ memory
@@ -65,6 +75,8 @@ class ModelRunner:
         key = f"{tag}|{dtype}"
         buf = self._scratch.get(key)
         if buf is None or buf.numel() < numel:
+            if self._capturing:
+                raise RuntimeError(f"scratch '{tag}' would be allocated during graph capture")
             grow = max(numel, 1) if buf is None else max(numel, 2 * buf.numel())
             buf = torch.empty(grow, dtype=dtype, device=self.device)
             self._scratch[key] = buf
@@ -154,7 +166,11 @@ class ModelRunner:
             cu_q.append(base + q_lens[i])
         widths = []
         for g in range(n_groups):
-            widths.append(max(1, max(len(cache.table(e.rid, g)) for e in entries)))
+            w = max(1, max(len(cache.table(e.rid, g)) for e in entries))
+            if ctx.all_decode:      # few distinct widths, so that captured steps are reused as contexts grow
+                w = -(-w // self.TABLE_BUCKET) * self.TABLE_BUCKET
+            widths.append(w)
+        ctx.table_widths = tuple(widths)
         segments: List[Tuple[str, List[int]]] = [
             ("token_ids", token_ids), ("positions", positions), ("seq_of_token", seq_of_token), ("cu_q", cu_q),
             ("kv_len", kv_lens), ("state_slots", state_slots), ("logit_rows", logit_rows)]
@@ -204,8 +220,46 @@ class ModelRunner:
         ``want`` lists.  The tensor is scratch memory: it is valid until the next step."""
         ctx = self.prepare(entries)
         with torch.cuda.device(self.device):
-            logits = self.model.forward(ctx)
+            logits = self._forward(ctx)
         self.steps_run += 1
+        return logits
+
+    def _forward(self, ctx: StepContext) -> torch.Tensor:
+        if not (self.cuda_graphs and ctx.all_decode):
+            return self.model.forward(ctx)
+        if self._graph_epoch != self.scratch_epoch:       # a buffer moved: every captured address is stale
+            self._graphs.clear()
+            self._graph_seen.clear()
+            self._graph_epoch = self.scratch_epoch
+        key = (ctx.n_tokens, ctx.n_seqs, int(ctx.logit_rows.numel()), ctx.table_widths,
+               tuple(int(t.data_ptr()) for t in (ctx.token_ids, ctx.logit_rows)))
+        hit = self._graphs.get(key)
+        if hit is not None:
+            hit[0].replay()
+            self.graph_replays += 1
+            ops.LAUNCHES += hit[2]
+            return hit[1]
+        seen = self._graph_seen.get(key, 0)
+        self._graph_seen[key] = seen + 1
+        if seen < 2:                                      # run eagerly first: buffers reach their final size
+            return self.model.forward(ctx)
+        epoch = self.scratch_epoch
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize(self.device)
+        launches = ops.LAUNCHES
+        self._capturing = True
+        try:
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+        finally:
+            self._capturing = False
+        launches = ops.LAUNCHES - launches            # kernels of this library inside the captured step
+        if self.scratch_epoch != epoch:                   # grew during capture: do not keep it
+            self._graph_epoch = -1
+            return self.model.forward(ctx)
+        self._graphs[key] = (graph, logits, launches)
+        graph.replay()
+        self.graph_replays += 1
         return logits
 
     def finish(self, rid: Hashable) -> None:
