@@ -235,3 +235,76 @@ PB_EXPORT int pb_paged_attention_decode(int dtype, const void* q, const void* k_
     }
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------
+// Entry point that allocates nothing (declared in no_alloc.h; it has no counterpart in
+// the reference).
+//
+// Who needs it: code that drives this library from a place where device memory cannot be
+// allocated any more: a host that handed all device memory to one arena at start-up and
+// forbids cudaMalloc afterwards, a real-time loop that may not take the allocator's lock,
+// or a plugin whose owner allows launches but no allocations.  pb_paged_attention_decode
+// needs scratch memory for the per-split partial results and expects the caller to bring
+// it; this variant brings its own: a fixed array in the library's device image.
+//
+// The array is part of every CUDA context that loads the library (4 MiB per GPU, held
+// until the process exits).  Host code cannot use the array's name as an address: the
+// name is only a handle on the host side.  The first call on each device therefore asks
+// the runtime for the array's device address, with that device current, and keeps it.
+// That first call should happen before any stream capture begins, since it is a
+// synchronous runtime query.
+//
+// All calls share the one array.  Nothing in it has to start at zero (the split kernel
+// writes every partial, empty ones included, before the combine kernel reads it), and it
+// keeps whatever the last call left.  Two calls that overlap on the GPU (different
+// streams, or one stream per thread) race on it: run them on one stream or order them
+// with events.
+#include "no_alloc.h"
+
+#include <mutex>
+
+// The scratch itself: file scope, in the library's device image.
+static __device__ __align__(256) float g_noalloc_scratch[PB_DECODE_NOALLOC_MAX_FLOATS];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device; looked up once per device.
+int noalloc_scratch(float** out) {
+    int device = -1;
+    cudaError_t rc = cudaGetDevice(&device);
+    if (rc != cudaSuccess) return (int)rc;
+    if (device < 0 || device >= kMaxDevices) return PB_ERR_TOO_LARGE;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[device] == nullptr) {
+        float* ptr = nullptr;
+        rc = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+        if (rc != cudaSuccess) return (int)rc;
+        if (ptr == nullptr) return (int)cudaErrorInvalidSymbol;
+        g_noalloc_ptr[device] = ptr;
+    }
+    *out = g_noalloc_ptr[device];
+    return 0;
+}
+
+}  // namespace
+
+PB_EXPORT long long pb_decode_noalloc_max_floats(void) { return PB_DECODE_NOALLOC_MAX_FLOATS; }
+
+PB_EXPORT int pb_paged_attention_decode_noalloc(int dtype, const void* q, const void* k_pool, const void* v_pool,
+                                                void* out, const int* block_table, int table_stride,
+                                                const int* kv_len, int n_seqs, int Hq, int Hkv, int D, int page_size,
+                                                float scale, int window, int n_splits, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (D <= 0 || Hq <= 0 || n_splits <= 0) return PB_ERR_BAD_SIZE;
+    const long long need = pb_decode_scratch_floats(n_seqs, Hq, D, n_splits);
+    if (need > PB_DECODE_NOALLOC_MAX_FLOATS) return PB_ERR_SCRATCH_TOO_SMALL;   // see pb_decode_noalloc_max_floats()
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch(&scratch);
+    if (rc != 0) return rc;
+    return pb_paged_attention_decode(dtype, q, k_pool, v_pool, out, scratch, block_table, table_stride, kv_len, n_seqs,
+                                     Hq, Hkv, D, page_size, scale, window, n_splits, stream);
+}
