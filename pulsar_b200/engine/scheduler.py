@@ -199,7 +199,8 @@ class Scheduler:
             s = self.seqs[rid]
             have = self._pages(s.n_cached) if self.cache.has(rid) else 0
             need_all = self._pages(len(s.tokens) + 1) - have
-            if need_all > self._free_pages() - planned_pages - self._held_back():
+            # what running requests still need (this step's pages included) stays theirs
+            if need_all > self._free_pages() - self._held_back():
                 break                          # head of the queue waits; nobody overtakes it
             if not self.cache.has(rid) and self.cache.n_free_slots() - sum(1 for e in out if not self.cache.has(e.rid)) <= 0:
                 break

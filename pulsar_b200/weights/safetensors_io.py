@@ -132,9 +132,11 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]], me
         offset += nbytes
     blob = json.dumps(header, separators=(",", ":")).encode("utf-8")
     blob += b" " * ((8 - len(blob) % 8) % 8)
-    with open(path, "wb") as f:
+    tmp = f"{path}.tmp{os.getpid()}"       # tensors being written may alias a map of the old file
+    with open(tmp, "wb") as f:
         f.write(struct.pack("<Q", len(blob)))
         f.write(blob)
         for _, t in items:
             c = t.detach().contiguous().cpu()
             f.write(c.view(torch.uint8).numpy().tobytes() if c.numel() else b"")
+    os.replace(tmp, path)

@@ -51,7 +51,7 @@ def read_folder(folder: str) -> Tuple[dict, Dict[str, torch.Tensor]]:
     weights = {}
     with safe_open(os.path.join(folder, "model.safetensors"), "pt") as f:
         for name in f.keys():
-            weights[name] = f.get_tensor(name)
+            weights[name] = f.get_tensor(name).clone()     # never alias the mapped file
     return cfg, weights
 
 

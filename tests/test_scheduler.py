@@ -1,0 +1,175 @@
+"""The scheduler's decisions without a GPU: a fake step function takes the pages and
+"samples" token 1.  Mirrors pulsar-core/tests/runtime/test_scheduler.cpp:2256-2334
+(prefill then decode, mixed step, portions 16+16+8, admission within the page budget, free
+on finish) and adds what this engine decides differently (whole-step budget, preemption)."""
+import pytest
+
+from pulsar_b200.cache import CacheManager, CacheNeed
+from pulsar_b200.engine.scheduler import Scheduler, SchedulerError
+
+
+def make(pages=16, page=4, max_running=4, budget=16, max_requests=8):
+    cache = CacheManager([CacheNeed.paged_kv(2, 16)], page, pages, max_requests)
+    return cache, Scheduler(cache, max_running, budget)
+
+
+def run_step(cache, sched, eos=-1, token=1):
+    """What Engine.step_once does around the model: take pages, note progress, sample."""
+    plan = sched.schedule()
+    for e in plan:
+        if not cache.has(e.rid):
+            cache.open(e.rid)
+        cache.append(e.rid, len(e.tokens))
+    sched.on_step(plan)
+    finished = []
+    for e in plan:
+        if e.sample and sched.on_token(e.rid, token, eos):
+            sched.finish(e.rid)
+            finished.append(e.rid)
+    cache.check_consistency()
+    return plan, finished
+
+
+def shape(plan):
+    return [(e.rid, len(e.tokens), e.sample) for e in plan]
+
+
+def test_prefill_then_decode():
+    cache, s = make()
+    s.add_request("a", list(range(10)), 3)
+    assert shape(run_step(cache, s)[0]) == [("a", 10, True)]
+    plan, _ = run_step(cache, s)
+    assert shape(plan) == [("a", 1, True)] and plan[0].tokens == [1]        # the sampled token is fed next
+    plan, fin = run_step(cache, s)
+    assert fin == ["a"] and not s.has_work() and cache.n_free_pages() == [16]
+
+
+def test_portions_under_the_budget():
+    cache, s = make(budget=16)
+    s.add_request("a", list(range(40)), 2)
+    assert shape(run_step(cache, s)[0]) == [("a", 16, False)]
+    assert shape(run_step(cache, s)[0]) == [("a", 16, False)]
+    assert shape(run_step(cache, s)[0]) == [("a", 8, True)]                  # 16 + 16 + 8
+    assert shape(run_step(cache, s)[0]) == [("a", 1, True)]
+
+
+def test_mixed_step_decodes_first_and_counts_them_in_the_budget():
+    cache, s = make(budget=8, pages=32)
+    s.add_request("a", list(range(5)), 10)
+    run_step(cache, s)
+    s.add_request("b", list(range(20)), 10)
+    plan, _ = run_step(cache, s)
+    assert shape(plan) == [("a", 1, True), ("b", 7, False)]                  # 1 decoded token + 7 prompt tokens = 8
+    plan, _ = run_step(cache, s)
+    assert shape(plan) == [("a", 1, True), ("b", 7, False)]
+    plan, _ = run_step(cache, s)
+    assert shape(plan) == [("a", 1, True), ("b", 6, True)]
+    plan, _ = run_step(cache, s)
+    assert sorted(shape(plan)) == [("a", 1, True), ("b", 1, True)]
+
+
+def test_two_prompts_share_a_step_in_fifo_order():
+    cache, s = make(budget=16, pages=32)
+    s.add_request("a", list(range(10)), 2)
+    s.add_request("b", list(range(10)), 2)
+    assert shape(run_step(cache, s)[0]) == [("a", 10, True), ("b", 6, False)]
+    assert shape(run_step(cache, s)[0]) == [("a", 1, True), ("b", 4, True)]
+
+
+def test_admission_waits_for_pages_and_the_head_blocks_the_queue():
+    cache, s = make(pages=6, page=4, budget=64)
+    s.add_request("a", list(range(15)), 4)          # 15 + 1 -> 4 pages
+    s.add_request("b", list(range(11)), 2)          # 11 + 1 -> 3 pages: does not fit beside a
+    s.add_request("c", [1, 2], 2)                   # would fit, but waits behind b
+    assert shape(run_step(cache, s)[0]) == [("a", 15, True)]
+    assert list(s.waiting) == ["b", "c"]
+    for _ in range(3):
+        plan, fin = run_step(cache, s)
+        assert [e.rid for e in plan] == ["a"]
+    assert fin == ["a"]                              # a finished: pages are free again
+    plan, _ = run_step(cache, s)
+    assert shape(plan) == [("b", 11, True), ("c", 2, True)]
+
+
+def test_max_running_bounds_admission():
+    cache, s = make(max_running=2, pages=64, budget=64)
+    for r in "abc":
+        s.add_request(r, [1, 2, 3], 2)
+    assert [e.rid for e in run_step(cache, s)[0]] == ["a", "b"]
+    plan, fin = run_step(cache, s)
+    assert sorted(fin) == ["a", "b"]
+    assert [e.rid for e in run_step(cache, s)[0]] == ["c"]
+
+
+def test_pages_run_out_while_decoding_the_youngest_is_preempted_and_recomputed():
+    cache, s = make(pages=4, page=4, budget=64)
+    with pytest.raises(SchedulerError, match="never"):      # 10 + 12 tokens need 6 pages: refused at submit
+        s.add_request("huge", list(range(10)), 12)
+    s.add_request("old", list(range(7)), 9)          # 16 tokens at most: the whole pool
+    s.add_request("young", list(range(3)), 9)        # 12 tokens at most
+    run_step(cache, s)                               # both admitted: 2 + 1 pages, 1 free
+    assert s.running == ["old", "young"]
+    preempted_at = None
+    outputs = {"old": 0, "young": 0}
+    for step in range(40):
+        plan, fin = run_step(cache, s)
+        for e in plan:
+            if e.sample:
+                outputs[e.rid] += 1
+        if s.n_preemptions and preempted_at is None:
+            preempted_at = step
+            assert "young" in s.waiting and "old" in s.running       # the request admitted last gives way
+            assert not cache.has("young")
+        if not s.has_work():
+            break
+    assert preempted_at is not None and not s.has_work()
+    assert cache.n_free_pages() == [4]
+    assert s.n_preemptions >= 1
+
+
+def test_preempted_request_is_recomputed_from_all_its_tokens():
+    cache, s = make(pages=4, page=4, budget=64)
+    s.add_request("old", list(range(7)), 9)
+    s.add_request("young", list(range(3)), 9)
+    seen_prefill = []
+    for _ in range(40):
+        plan, _ = run_step(cache, s)
+        seen_prefill += [(e.rid, len(e.tokens)) for e in plan if len(e.tokens) > 1]
+        if not s.has_work():
+            break
+    young = [n for rid, n in seen_prefill if rid == "young"]
+    assert young[0] == 3 and len(young) >= 2 and young[1] > 3        # prompt, later prompt + what it had generated
+
+
+def test_finish_gives_pages_back_and_eos_stops():
+    cache, s = make()
+    s.add_request("a", [5, 6, 7], 50)
+    run_step(cache, s, eos=9, token=4)
+    plan, fin = run_step(cache, s, eos=9, token=9)
+    assert fin == ["a"] and cache.n_free_pages() == [16] and not cache.has("a")
+
+
+def test_park_keeps_pages_and_a_further_turn_continues_from_them():
+    cache, s = make(pages=16)
+    s.add_request("a", [1, 2, 3, 4, 5], 2)
+    run_step(cache, s)
+    plan = s.schedule()
+    cache.append("a", 1); s.on_step(plan)
+    assert s.on_token("a", 1, -1) is True
+    s.park("a")
+    assert not s.has_work() and cache.has("a") and cache.length("a") == 6
+    s.extend_request("a", [7, 8, 9], 2)
+    plan, _ = run_step(cache, s)
+    assert shape(plan) == [("a", 4, True)] and plan[0].tokens == [1, 7, 8, 9]    # last sampled token + the new turn
+    assert cache.length("a") == 10
+
+
+def test_refusals():
+    cache, s = make()
+    with pytest.raises(SchedulerError):
+        s.add_request("a", [], 3)
+    s.add_request("a", [1], 3)
+    with pytest.raises(SchedulerError, match="already"):
+        s.add_request("a", [1], 3)
+    with pytest.raises(SchedulerError):
+        Scheduler(cache, 0, 8)
