@@ -212,10 +212,13 @@ class Engine:
                 sid = self.create_session(prompts[i], ov)
                 self.feed(sid, [], max_new_tokens)
                 owner[sid] = i
-            for sid, tok, finished in self.step(max(1, len(owner))):
-                if sid in owner:
+            before = self.forwards
+            for sid, tok, finished in self.step_once():      # one forward at a time: a finished
+                if sid in owner:                              # sequence gives its pages back at once
                     results[owner[sid]].append(tok)
                     if finished:
                         self.release(sid)
                         del owner[sid]
+            if self.forwards == before and self.scheduler.has_work():
+                raise RuntimeError("the scheduler has work but nothing can run: the pool is too small for it")
         return results

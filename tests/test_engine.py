@@ -1,0 +1,181 @@
+"""Generation through the entry points: greedy tokens against the plain implementation,
+long decoding, the first tokens of a sequence, sampling that a seed reproduces, preemption
+when pages run out, several turns on kept pages (GPU)."""
+import json
+import os
+import random
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import helpers
+from helpers import TINY, TOL
+from plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, (raw, seed, page) in TINY.items():
+        d = tmp_path_factory.mktemp(f"eng{name}")
+        helpers.make_folder(d, raw, seed)
+        out[name] = str(d)
+    return out
+
+
+def _engine(folder, dtype, page, **kw):
+    from pulsar_b200.engine.engine import Engine
+    cfg = dict(dtype=dtype, page_size=page, num_pages=64, max_sessions=4, max_running=4, max_chunk_size=16, eos_id=-1)
+    cfg.update(kw)
+    return Engine(folder, cfg)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_equals_the_plain_implementation(folders, name):
+    raw, seed, page = TINY[name]
+    cfg, weights = helpers.read_folder(folders[name])
+    rng = random.Random(seed)
+    prompts = [helpers.random_tokens(rng, n, raw["vocab_size"]) for n in (1, 23, 40, 7, 18)]
+    eng = _engine(folders[name], "float32", page, max_chunk_size=11)       # prompts are cut into portions, 4 at a time
+    got = eng.generate(prompts, 9)
+    want = [plain.greedy_generate(cfg, weights, p, 9) for p in prompts]
+    assert got == want
+    assert eng.cache.live_requests() == [] and all(f == 64 for f in eng.cache.n_free_pages())
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_bfloat16_follows_the_plain_logits(folders, name):
+    """Rounding may flip near-ties, so each emitted token is checked against the plain logits
+    of its own prefix: it must be (nearly) the most probable one."""
+    raw, seed, page = TINY[name]
+    cfg, weights = helpers.read_folder(folders[name])
+    w16 = helpers.as_bf16_matrices(weights)
+    prompts = [helpers.random_tokens(random.Random(3), 19, raw["vocab_size"])]
+    out = _engine(folders[name], "bfloat16", page).generate(prompts, 8)[0]
+    seq = list(prompts[0])
+    for tok in out:
+        row = plain.forward(cfg, w16, seq, torch.float64)[-1]
+        assert float(row.max() - row[tok]) <= TOL["bfloat16"] * float(row.abs().max())
+        seq.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_long_decoding(folders, name, dtype):
+    """300 tokens one by one after a short prompt: page edges and (in C) the window's edge are
+    crossed many times; every position's logits are compared."""
+    from pulsar_b200.replay import Replay
+    raw, seed, page = TINY[name]
+    cfg, weights = helpers.read_folder(folders[name])
+    if dtype == "bfloat16":
+        weights = helpers.as_bf16_matrices(weights)
+    toks = helpers.random_tokens(random.Random(9), 305, raw["vocab_size"])
+    ref = plain.forward(cfg, weights, toks, torch.float64)
+    rp = Replay(folders[name], dtype, 320, page_size=page)
+    rows = [rp.run_step({"step": 0, "entries": [{"id": "a", "tokens": toks[:5], "want": [0, 1, 2, 3, 4]}]})]
+    for i in range(5, len(toks)):
+        rows.append(rp.run_step({"step": i, "entries": [{"id": "a", "tokens": [toks[i]], "want": [0]}]}))
+    got = torch.cat(rows)
+    for pos in range(len(toks)):
+        err = helpers.rel_err(got[pos], ref[pos])
+        assert err < TOL[dtype], f"position {pos}: {err:.2e}"
+    assert rp.runner.graph_replays > 200           # the decode steps ran as captured graphs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(folders, dtype):
+    from pulsar_b200.replay import Replay
+    raw, seed, page = TINY["B"]
+    cfg, weights = helpers.read_folder(folders["B"])
+    if dtype == "bfloat16":
+        weights = helpers.as_bf16_matrices(weights)
+    rp = Replay(folders["B"], dtype, 128, page_size=page)
+    for toks in ([5], [5, 9], [400, 1, 2]):
+        ref = plain.forward(cfg, weights, toks, torch.float64)
+        got = rp.run_step({"step": 0, "entries": [{"id": "x", "tokens": toks, "want": list(range(len(toks)))}], "end": ["x"]})
+        assert helpers.rel_err(got, ref) < TOL[dtype]
+        # the same, token by token from position 0
+        rows = [rp.run_step({"step": i, "entries": [{"id": "y", "tokens": [t], "want": [0]}],
+                             "end": ["y"] if i == len(toks) - 1 else []}) for i, t in enumerate(toks)]
+        assert helpers.rel_err(torch.cat(rows), ref) < TOL[dtype]
+
+
+def test_sampling_is_reproducible_per_request_and_obeys_top_k(folders):
+    raw, seed, page = TINY["B"]
+    cfg, weights = helpers.read_folder(folders["B"])
+    rng = random.Random(4)
+    p1, p2, p3 = (helpers.random_tokens(rng, n, raw["vocab_size"]) for n in (12, 5, 20))
+    eng = _engine(folders["B"], "float32", page)
+    a = eng.generate([p1], 12, temperature=0.9, top_k=8, top_p=0.95, seed=11)[0]
+    b = eng.generate([p1], 12, temperature=0.9, top_k=8, top_p=0.95, seed=11)[0]
+    assert a == b                                                         # same seed, same tokens
+    batch = eng.generate([p1, p2, p3], 12, temperature=0.9, top_k=8, top_p=0.95, seed=11)
+    assert batch[0] == a                                                  # whatever else is in the batch
+    c = eng.generate([p1], 12, temperature=0.9, top_k=8, top_p=0.95, seed=12)[0]
+    assert c != a
+    seq = list(p1)
+    for tok in a:                                                         # every draw lies in the surviving set
+        row = plain.forward(cfg, weights, seq, torch.float64)[-1]
+        _, keep = plain.sample_filter(row, 0.9, 8, 0.95)
+        assert tok in keep.tolist()
+        seq.append(tok)
+    g1 = eng.generate([p2], 6, temperature=0.0, top_k=3, seed=5)[0]       # temperature 0 is greedy whatever the rest
+    assert g1 == plain.greedy_generate(cfg, weights, p2, 6)
+
+
+def test_pages_run_out_preempts_and_the_tokens_stay_the_same(folders):
+    raw, seed, page = TINY["A"]                                           # page 16
+    cfg, weights = helpers.read_folder(folders["A"])
+    rng = random.Random(6)
+    prompts = [helpers.random_tokens(rng, n, raw["vocab_size"]) for n in (30, 20, 28)]
+    want = [plain.greedy_generate(cfg, weights, p, 40) for p in prompts]
+    eng = _engine(folders["A"], "float32", page, num_pages=9, max_chunk_size=64)    # 144 tokens of cache for 218 needed
+    got = eng.generate(prompts, 40)
+    assert eng.scheduler.n_preemptions >= 1
+    assert got == want
+    assert all(f == 9 for f in eng.cache.n_free_pages())
+    from pulsar_b200.engine.scheduler import SchedulerError
+    with pytest.raises(SchedulerError, match="never"):
+        eng.generate([list(range(100))], 60)                              # could never fit: refused at submit
+
+
+def test_sessions_turn_by_turn_on_kept_pages(folders):
+    from pulsar_b200.api import Pulsar
+    raw, seed, page = TINY["B"]
+    cfg, weights = helpers.read_folder(folders["B"])
+    p = Pulsar(folders["B"], dict(page_size=page, num_pages=64, max_sessions=2, max_running=2, max_chunk_size=16),
+               dtype=torch.float32)
+    s = p.create_session([3, 4, 5])
+    s.send([6, 7], 4)
+    first = list(s.recv())
+    assert first == plain.greedy_generate(cfg, weights, [3, 4, 5, 6, 7], 4)
+    assert s.get_state() == "parked" and p.engine.cache.has(s.seq_id)     # finished turn: pages are kept
+    s.send([9, 9, 8], 3)
+    second = list(s.recv())
+    assert second == plain.greedy_generate(cfg, weights, [3, 4, 5, 6, 7] + first + [9, 9, 8], 3)
+    s.destroy()
+    assert p.engine.cache.live_requests() == [] and s.get_state() == "unknown"
+    with pytest.raises(Exception, match="unknown keys"):
+        Pulsar(folders["B"], dict(pagesize=8))
+
+
+def test_engine_refuses_a_cpu_device(folders):
+    from pulsar_b200.engine.engine import Engine
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        Engine(folders["A"], dict(device="cpu"))
+
+
+def test_command_line(folders, tmp_path):
+    raw, seed, page = TINY["A"]
+    cfg, weights = helpers.read_folder(folders["A"])
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "pulsar-generate"), "--model", folders["A"], "--dtype",
+                          "float32", "--prompt_ids", "1,2,3,4", "--prompt_ids", "9 8 7", "--gen_tokens", "5", "--max_pages",
+                          "32", "--eos_id", "-1", "--json"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    got = json.loads(out.stdout.strip().splitlines()[-1])["outputs"]
+    assert got == [plain.greedy_generate(cfg, weights, p, 5) for p in ([1, 2, 3, 4], [9, 8, 7])]
