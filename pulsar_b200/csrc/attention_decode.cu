@@ -308,3 +308,13 @@ PB_EXPORT int pb_paged_attention_decode_noalloc(int dtype, const void* q, const 
     return pb_paged_attention_decode(dtype, q, k_pool, v_pool, out, scratch, block_table, table_stride, kv_len, n_seqs,
                                      Hq, Hkv, D, page_size, scale, window, n_splits, stream);
 }
+
+// The merge of per-split partials alone, for kernels that write partials in this file's layout.
+PB_EXPORT int pb_decode_combine(int dtype, const float* partial, void* out, int rows, int D, int n_splits,
+                                cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (dtype == PB_F32) decode_combine_kernel<float><<<rows, 128, 0, stream>>>(partial, (float*)out, D, n_splits);
+    else if (dtype == PB_BF16) decode_combine_kernel<__nv_bfloat16><<<rows, 128, 0, stream>>>(partial, (__nv_bfloat16*)out, D, n_splits);
+    else return PB_ERR_BAD_DTYPE;
+    return launch_status();
+}

@@ -1,0 +1,310 @@
+// Paged decode attention on the tensor cores for bfloat16 pages with head size 64 or 128
+// and up to 16 query heads per kv head.
+//
+// One block per (split of the keys, kv head, sequence).  The group's query heads fill the
+// rows of one 16-row MMA tile (as the reference packs them,
+// pulsar-core/src/kernels/paged_attention.cu:101-203); keys and values stream through a
+// three-stage cp.async pipeline of 64-key tiles, gathered page by page through the block
+// table into XOR-swizzled shared memory, so that ldmatrix reads are free of bank
+// conflicts.  Each of the four warps owns 16 keys of a tile: S = Q K^T with
+// mma.m16n8k16, an online softmax in float32 on the accumulator fragments (exp2f on
+// scores pre-multiplied by scale*log2(e)), P rounded to bfloat16 as the A operand of
+// O += P V.  The warps' partial results are merged through shared memory and written in
+// the layout of the split kernel (attention_decode.cu), whose combine kernel finishes.
+//
+// This kernel exists for memory bandwidth: a decode step reads every cached key and value
+// once, and what limits it is the number of bytes in flight per SM, not arithmetic.
+#include "common.cuh"
+
+#include <cuda_pipeline.h>
+#include <mma.h>
+
+namespace {
+
+using namespace pb;
+typedef __nv_bfloat16 bf16;
+
+constexpr int kTile = 64;        // keys per pipeline stage
+constexpr int kStages = 3;
+constexpr int kWarps = 4;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+    const int bytes = pred ? 16 : 0;           // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Shared-memory tile [kTile rows][D] of bf16, 16-byte chunks XOR-swizzled by the row.
+template <int D>
+__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
+    constexpr int kChunks = D / 8;
+    return (uint32_t)(row * kChunks + (chunk ^ (row & 7))) * 16u;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kWarps * 32, 2)
+decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                 float* __restrict__ partial, const int* __restrict__ block_table, int table_stride,
+                 const int* __restrict__ kv_len, int Hq, int Hkv, int page_size, float scale, int window, int n_splits) {
+    constexpr int kChunks = D / 8;                    // 16-byte chunks per row
+    constexpr int kTileBytes = kTile * D * 2;
+    constexpr int kKSteps = D / 16;                   // k-steps of Q K^T
+    constexpr int kNTiles = D / 8;                    // n-tiles of P V
+    extern __shared__ __align__(128) unsigned char smem[];
+    // [stage][K tile | V tile]; after the main loop the same memory holds the warps' partial results
+    const uint32_t smem_base = smem_u32(smem);
+
+    const int split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int G = Hq / Hkv;
+    const int p = kv_len[s] - 1;
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int n_keys = p - lo + 1;
+    int chunk = (n_keys + n_splits - 1) / n_splits;
+    chunk = (chunk + kTile - 1) / kTile * kTile;
+    const int begin = lo + split * chunk;
+    const int end = min(p + 1, begin + chunk);        // keys [begin, end)
+    const int* table = block_table + (size_t)s * table_stride;
+    const int tile0 = begin / kTile;                  // tiles are aligned to absolute key indices (whole pages)
+    const int n_tiles = begin < end ? (end - 1) / kTile - tile0 + 1 : 0;
+
+    // Q fragments: rows = query heads of the group (zero beyond G), straight from global memory.
+    uint32_t qa[kKSteps][4];
+    {
+        const bf16* q0 = q + ((size_t)s * Hq + (size_t)kvh * G) * D;
+#pragma unroll
+        for (int ks = 0; ks < kKSteps; ++ks) {
+            const int c0 = ks * 16 + 2 * t;
+            qa[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + c0) : 0u;
+            qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + c0) : 0u;
+            qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + c0 + 8) : 0u;
+            qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + c0 + 8) : 0u;
+        }
+    }
+
+    auto issue_tile = [&](int tile_index, int stage) {
+        const int key0 = (tile0 + tile_index) * kTile;
+        const uint32_t k_dst = smem_base + stage * 2 * kTileBytes, v_dst = k_dst + kTileBytes;
+#pragma unroll
+        for (int i = 0; i < kTile * kChunks / (kWarps * 32); ++i) {
+            const int idx = i * kWarps * 32 + tid;
+            const int row = idx / kChunks, c = idx % kChunks;
+            const int key = key0 + row;
+            const bool ok = key >= begin && key < end;
+            size_t at = 0;
+            if (ok) {
+                const int page = table[key / page_size];
+                at = (((size_t)page * Hkv + kvh) * page_size + key % page_size) * D + c * 8;
+            }
+            const uint32_t off = tile_offset<D>(row, c);
+            cp_async16(k_dst + off, k_pool + at, ok);
+            cp_async16(v_dst + off, v_pool + at, ok);
+        }
+    };
+
+    float o[kNTiles][4];
+#pragma unroll
+    for (int i = 0; i < kNTiles; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};     // rows g and g + 8
+    const float sl2 = scale * kLog2e;
+
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) {
+        if (i < n_tiles) issue_tile(i, i);
+        cp_async_commit();
+    }
+    for (int it = 0; it < n_tiles; ++it) {
+        cp_async_wait<kStages - 2>();
+        __syncthreads();                              // tile `it` has landed; stage (it-1) % kStages is free
+        if (it + kStages - 1 < n_tiles) issue_tile(it + kStages - 1, (it + kStages - 1) % kStages);
+        cp_async_commit();
+
+        const int stage = it % kStages;
+        const uint32_t k_s = smem_base + stage * 2 * kTileBytes, v_s = k_s + kTileBytes;
+        const int key_base = (tile0 + it) * kTile + warp * 16;            // this warp's 16 keys
+        if (key_base >= end || key_base + 16 <= begin) continue;           // nothing of this warp's is in range
+
+        // S = Q K^T for 16 heads x 16 keys (two n-tiles of 8 keys)
+        float sc[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f; }
+#pragma unroll
+        for (int ks = 0; ks < kKSteps; ++ks) {
+            // matrices: (keys 0-7, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 0-7), (keys 8-15, d 8-15)
+            uint32_t kb[4];
+            const int row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);
+            const int c = ks * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(kb, k_s + tile_offset<D>(row, c));
+            mma_bf16(sc[0], qa[ks], kb[0], kb[1]);
+            mma_bf16(sc[1], qa[ks], kb[2], kb[3]);
+        }
+        // mask and scale; thread holds keys key_base + n*8 + 2t + {0,1} for rows g (c0,c1) and g+8 (c2,c3)
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key_base + n * 8 + 2 * t + (e & 1);
+                const float v = (key >= begin && key < end) ? sc[n][e] * sl2 : -INFINITY;
+                sc[n][e] = v;
+                tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
+            }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float mx = tmax[r];
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[r], mx);                      // finite: at least one key of the warp is in range
+            corr[r] = exp2f(m_run[r] - m_new);
+            m_run[r] = m_new;
+            l_run[r] *= corr[r];
+        }
+        uint32_t pa[4];
+        {
+            float pv[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    pv[n][e] = exp2f(sc[n][e] - m_run[e >> 1]);
+                    l_run[e >> 1] += pv[n][e];
+                }
+            pa[0] = pack_bf16(pv[0][0], pv[0][1]);
+            pa[1] = pack_bf16(pv[0][2], pv[0][3]);
+            pa[2] = pack_bf16(pv[1][0], pv[1][1]);
+            pa[3] = pack_bf16(pv[1][2], pv[1][3]);
+        }
+#pragma unroll
+        for (int i = 0; i < kNTiles; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        // O += P V: V^T fragments by transposing ldmatrix over [16 keys][16 d] blocks
+#pragma unroll
+        for (int i = 0; i < kNTiles; i += 2) {
+            // matrices: (keys 0-7, d i*8..), (keys 8-15, d i*8..), (keys 0-7, d (i+1)*8..), (keys 8-15, d (i+1)*8..)
+            uint32_t vb[4];
+            const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            const int c = i + (lane >> 4);
+            ldmatrix_x4_trans(vb, v_s + tile_offset<D>(row, c));
+            mma_bf16(o[i], pa, vb[0], vb[1]);
+            mma_bf16(o[i + 1], pa, vb[2], vb[3]);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // Merge the four warps (each saw a quarter of the keys) and write the split's partial.
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    float* o_s = reinterpret_cast<float*>(smem);            // [kWarps][16][D]
+    float* m_s = o_s + kWarps * 16 * D;                      // [kWarps][16]
+    float* l_s = m_s + kWarps * 16;
+#pragma unroll
+    for (int i = 0; i < kNTiles; ++i) {
+        const int d = i * 8 + 2 * t;
+        o_s[(warp * 16 + g) * D + d] = o[i][0];
+        o_s[(warp * 16 + g) * D + d + 1] = o[i][1];
+        o_s[(warp * 16 + g + 8) * D + d] = o[i][2];
+        o_s[(warp * 16 + g + 8) * D + d + 1] = o[i][3];
+    }
+    if (t == 0) {
+        m_s[warp * 16 + g] = m_run[0]; m_s[warp * 16 + g + 8] = m_run[1];
+        l_s[warp * 16 + g] = l_run[0]; l_s[warp * 16 + g + 8] = l_run[1];
+    }
+    __syncthreads();
+    const int stride = D + 2;
+    for (int i = tid; i < G * D; i += kWarps * 32) {
+        const int h = i / D, d = i - h * D;
+        float m_all = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) m_all = fmaxf(m_all, m_s[w * 16 + h]);
+        float acc = 0.0f, l_all = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float f = (m_s[w * 16 + h] == -INFINITY) ? 0.0f : exp2f(m_s[w * 16 + h] - m_all);
+            acc += o_s[(w * 16 + h) * D + d] * f;
+            l_all += l_s[w * 16 + h] * f;
+        }
+        float* dst = partial + (((size_t)s * Hq + (size_t)kvh * G + h) * n_splits + split) * stride;
+        dst[d] = acc;
+        if (d == 0) { dst[D] = m_all * 0.6931471805599453f; dst[D + 1] = l_all; }   // maximum back in natural-log units
+    }
+}
+
+template <int D>
+int launch_tc(const void* q, const void* k_pool, const void* v_pool, float* partial, const int* block_table,
+              int table_stride, const int* kv_len, int n_seqs, int Hq, int Hkv, int page_size, float scale, int window,
+              int n_splits, cudaStream_t stream) {
+    constexpr int pipeline = kStages * 2 * kTile * D * 2;
+    constexpr int merge = (kWarps * 16 * D + 2 * kWarps * 16) * 4;
+    constexpr int smem = pipeline > merge ? pipeline : merge;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t rc = cudaFuncSetAttribute(decode_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (rc != cudaSuccess) return (int)rc;
+        configured = true;
+    }
+    dim3 grid(n_splits, Hkv, n_seqs);
+    decode_tc_kernel<D><<<grid, kWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, partial,
+                                                             block_table, table_stride, kv_len, Hq, Hkv, page_size, scale,
+                                                             window, n_splits);
+    return launch_status();
+}
+
+}  // namespace
+
+PB_EXPORT int pb_decode_combine(int dtype, const float* partial, void* out, int rows, int D, int n_splits, cudaStream_t stream);
+
+// 1 if pb_paged_attention_decode_tc takes these sizes (else the split kernel of attention_decode.cu serves).
+PB_EXPORT int pb_decode_tc_supported(int dtype, int Hq, int Hkv, int D, int page_size) {
+    if (dtype != PB_BF16 || Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16) return 0;
+    if (D != 64 && D != 128) return 0;
+    if (page_size <= 0 || page_size > kTile || (kTile % page_size)) return 0;
+    return 1;
+}
+
+// Same arguments and scratch as pb_paged_attention_decode.
+PB_EXPORT int pb_paged_attention_decode_tc(int dtype, const void* q, const void* k_pool, const void* v_pool, void* out,
+                                           float* partial, const int* block_table, int table_stride, const int* kv_len,
+                                           int n_seqs, int Hq, int Hkv, int D, int page_size, float scale, int window,
+                                           int n_splits, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (!pb_decode_tc_supported(dtype, Hq, Hkv, D, page_size) || n_splits <= 0) return PB_ERR_BAD_SIZE;
+    if (Hkv > 65535 || n_seqs > 65535) return PB_ERR_TOO_LARGE;
+    int rc;
+    if (D == 64)
+        rc = launch_tc<64>(q, k_pool, v_pool, partial, block_table, table_stride, kv_len, n_seqs, Hq, Hkv, page_size, scale,
+                           window, n_splits, stream);
+    else
+        rc = launch_tc<128>(q, k_pool, v_pool, partial, block_table, table_stride, kv_len, n_seqs, Hq, Hkv, page_size, scale,
+                            window, n_splits, stream);
+    if (rc != 0) return rc;
+    return pb_decode_combine(dtype, partial, out, n_seqs * Hq, D, n_splits, stream);
+}

@@ -30,6 +30,8 @@ _SIGNATURES = {
     "pb_silu_mul": [_I, _P, _P, _I, _I, _P],
     "pb_paged_attention_generic": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "pb_paged_attention_decode": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "pb_paged_attention_decode_tc": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "pb_decode_tc_supported": [_I, _I, _I, _I, _I],
     "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _P, _P],
 }
@@ -214,11 +216,20 @@ def decode_splits(n_seqs: int, n_kv_heads: int) -> int:
     return max(1, min(64, -(-592 // max(1, n_seqs * n_kv_heads))))
 
 
+def decode_tc_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether the tensor-core decode kernel takes these sizes (bfloat16, head size 64 or 128,
+    groups up to 16, pages that divide 64)."""
+    if dtype != torch.bfloat16:
+        return False
+    return bool(fn("pb_decode_tc_supported")(BF16, n_heads, n_kv_heads, head_dim, page_size))
+
+
 def paged_attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                            partial: torch.Tensor, block_table: torch.Tensor, kv_len: torch.Tensor, scale: float,
-                           window: Optional[int], n_splits: int) -> None:
+                           window: Optional[int], n_splits: int, tensor_cores: Optional[bool] = None) -> None:
     """One query token per sequence: q, out [S, Hq, D].  ``partial`` is float32 scratch of at
-    least S * Hq * n_splits * (D + 2) elements."""
+    least S * Hq * n_splits * (D + 2) elements.  ``tensor_cores``: None picks the tensor-core
+    kernel where it applies, False forces the CUDA-core kernel, True insists."""
     _cuda(q, k_pool, v_pool, out, partial, block_table, kv_len)
     s, hq, d = q.shape
     pages, hkv, page_size, d2 = k_pool.shape
@@ -226,10 +237,12 @@ def paged_attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     assert k_pool.dtype == q.dtype and v_pool.dtype == q.dtype and out.dtype == q.dtype
     assert block_table.dtype == torch.int32 and kv_len.dtype == torch.int32 and block_table.shape[0] == s
     assert partial.dtype == torch.float32 and partial.numel() >= s * hq * n_splits * (d + 2)
-    check(fn("pb_paged_attention_decode")(code(q.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(partial),
-                                          _p(block_table), block_table.shape[1], _p(kv_len), s, hq, hkv, d, page_size,
-                                          float(scale), int(window or 0), n_splits, stream()),
-          "paged_attention_decode", kernels=2)
+    if tensor_cores is None:
+        tensor_cores = decode_tc_supported(q.dtype, hq, hkv, d, page_size)
+    name = "pb_paged_attention_decode_tc" if tensor_cores else "pb_paged_attention_decode"
+    check(fn(name)(code(q.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(partial),
+                   _p(block_table), block_table.shape[1], _p(kv_len), s, hq, hkv, d, page_size,
+                   float(scale), int(window or 0), n_splits, stream()), name[3:], kernels=2)
 
 
 def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, window: Optional[int]) -> None:

@@ -277,6 +277,50 @@ def test_attention_decode_split(dtype, hq, hkv, d, page, window, n_splits):
     close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window), TOL[dtype])
 
 
+TC_SHAPES = [(32, 8, 128, 16), (5, 5, 64, 16), (16, 1, 128, 32), (8, 2, 64, 8), (12, 4, 128, 64), (7, 7, 128, 4)]
+
+
+@pytest.mark.parametrize("hq,hkv,d,page", TC_SHAPES)
+@pytest.mark.parametrize("window", [None, 50, 333])
+@pytest.mark.parametrize("n_splits", [1, 2, 5, 37])
+def test_attention_decode_tensor_cores(hq, hkv, d, page, window, n_splits):
+    """The tensor-core decode kernel against the plain reference and against the CUDA-core
+    kernel it stands in for: ragged contexts, tile and page edges (63, 64, 65, 128, 129),
+    windows that start inside a tile, more splits than tiles."""
+    from pulsar_b200 import ops
+    dtype = torch.bfloat16
+    assert ops.decode_tc_supported(dtype, hq, hkv, d, page)
+    g = torch.Generator().manual_seed(11)
+    lens_kv = [1, 15, 16, 17, 63, 64, 65, 128, 129, 700, 1025]
+    lens_q = [1] * len(lens_kv)
+    case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype, spike=(9, 5, hq - 1))
+    scale = 1.0 / math.sqrt(d)
+    outs = []
+    for tc in (True, False):
+        out = torch.full((len(lens_kv), hq, d), float("nan"), dtype=dtype, device="cuda")
+        partial = torch.full((len(lens_kv) * hq * n_splits * (d + 2),), float("nan"), dtype=torch.float32, device="cuda")
+        ops.paged_attention_decode(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, partial, dev(case["table"]),
+                                   dev(case["kv"]), scale, window, n_splits, tensor_cores=tc)
+        outs.append(out)
+    ref = _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window)
+    close(outs[0], ref, TOL[dtype], "tensor cores vs plain")
+    close(outs[0], outs[1].double(), TOL[dtype], "tensor cores vs CUDA cores")
+
+
+def test_decode_tensor_cores_applicability():
+    from pulsar_b200 import ops
+    assert not ops.decode_tc_supported(torch.float32, 32, 8, 128, 16)
+    assert not ops.decode_tc_supported(torch.bfloat16, 32, 8, 96, 16)       # head size
+    assert not ops.decode_tc_supported(torch.bfloat16, 34, 2, 128, 16)      # group of 17
+    assert not ops.decode_tc_supported(torch.bfloat16, 32, 8, 128, 24)      # page does not divide the tile
+    q = torch.zeros(1, 4, 96, dtype=torch.bfloat16, device="cuda")
+    kp = torch.zeros(2, 2, 16, 96, dtype=torch.bfloat16, device="cuda")
+    z = torch.ones(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="unsupported size"):
+        ops.paged_attention_decode(q, kp, kp, torch.empty_like(q), torch.empty(4 * 98, device="cuda"), z.view(1, 1), z, 1.0,
+                                   None, 1, tensor_cores=True)
+
+
 def test_attention_refuses_bad_sizes():
     from pulsar_b200 import ops
     q = torch.zeros(1, 2, 24, device="cuda")           # head size 24 is no multiple of 16

@@ -59,7 +59,8 @@ def test_no_alloc_entry_matches_existing_entry_twice_in_a_row(dtype):
         scale = 1.0 / math.sqrt(d)
         want = torch.empty_like(q)
         partial = torch.empty(lib.pb_decode_scratch_floats(n_seqs, hq, d, n_splits), dtype=torch.float32, device="cuda")
-        ops.paged_attention_decode(q, kp, vp, want, partial, table, lens, scale, window or None, n_splits)
+        ops.paged_attention_decode(q, kp, vp, want, partial, table, lens, scale, window or None, n_splits,
+                                   tensor_cores=False)     # the entry point this one is a variant of
         got = torch.full_like(q, float("nan"))
         mem_before = torch.cuda.memory_allocated()
         rc = lib.pb_paged_attention_decode_noalloc(code, q.data_ptr(), kp.data_ptr(), vp.data_ptr(), got.data_ptr(),
