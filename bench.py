@@ -121,20 +121,22 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int, sampl
     from pulsar_b200.engine.runner import StepEntry
     runner, cache = engine.runner, engine.cache
     rids = [("bench", i) for i in range(batch)]
-    start_len = context - steps - warmup
+    settle = 4          # untimed steps before the warm-up: scratch buffers reach their size, the step is captured
+    start_len = context - steps - warmup - settle
     for rid in rids:
         cache.open(rid)
         cache.append(rid, start_len)
     gen = torch.Generator().manual_seed(1)
-    toks = torch.randint(0, engine.model.spec.vocab_size, (steps + warmup, batch), generator=gen).tolist()
+    toks = torch.randint(0, engine.model.spec.vocab_size, (steps + warmup + settle, batch), generator=gen).tolist()
     ids = torch.empty(batch, dtype=torch.int32, device="cuda:0")
 
     def one(i):
         logits = runner.step([StepEntry(rid, [toks[i][b]], [0]) for b, rid in enumerate(rids)])
         ops.sample(logits, ids)
-    for i in range(warmup):
+    for i in range(settle + warmup):
         one(i)
     torch.cuda.synchronize()
+    warmup += settle
     if sampler is not None:
         sampler.start()
     launches0 = ops.LAUNCHES

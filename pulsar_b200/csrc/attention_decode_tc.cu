@@ -14,54 +14,15 @@
 //
 // This kernel exists for memory bandwidth: a decode step reads every cached key and value
 // once, and what limits it is the number of bytes in flight per SM, not arithmetic.
-#include "common.cuh"
-
-#include <cuda_pipeline.h>
-#include <mma.h>
+#include "mma_common.cuh"
 
 namespace {
 
 using namespace pb;
-typedef __nv_bfloat16 bf16;
 
 constexpr int kTile = 64;        // keys per pipeline stage
 constexpr int kStages = 3;
 constexpr int kWarps = 4;
-constexpr float kLog2e = 1.4426950408889634f;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
-    const int bytes = pred ? 16 : 0;           // 0: the 16 bytes are filled with zeros
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// Shared-memory tile [kTile rows][D] of bf16, 16-byte chunks XOR-swizzled by the row.
-template <int D>
-__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
-    constexpr int kChunks = D / 8;
-    return (uint32_t)(row * kChunks + (chunk ^ (row & 7))) * 16u;
-}
 
 template <int D>
 __global__ void __launch_bounds__(kWarps * 32, 2)
@@ -254,7 +215,7 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
         }
         float* dst = partial + (((size_t)s * Hq + (size_t)kvh * G + h) * n_splits + split) * stride;
         dst[d] = acc;
-        if (d == 0) { dst[D] = m_all * 0.6931471805599453f; dst[D + 1] = l_all; }   // maximum back in natural-log units
+        if (d == 0) { dst[D] = m_all * kLn2; dst[D + 1] = l_all; }   // maximum back in natural-log units
     }
 }
 

@@ -32,6 +32,9 @@ _SIGNATURES = {
     "pb_paged_attention_decode": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_paged_attention_decode_tc": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_decode_tc_supported": [_I, _I, _I, _I, _I],
+    "pb_paged_attention_prefill_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "pb_prefill_tc_supported": [_I, _I, _I, _I, _I],
+    "pb_prefill_tc_tile": [],
     "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _P, _P],
 }
@@ -245,15 +248,51 @@ def paged_attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
                    float(scale), int(window or 0), n_splits, stream()), name[3:], kernels=2)
 
 
+def prefill_tc_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    if dtype != torch.bfloat16:
+        return False
+    return bool(fn("pb_prefill_tc_supported")(BF16, n_heads, n_kv_heads, head_dim, page_size))
+
+
+def prefill_tc_tiles(q_lens) -> int:
+    """Blocks along the query axis: each sequence's new tokens in tiles of 64."""
+    tile = fn("pb_prefill_tc_tile")()
+    return sum(-(-int(n) // tile) for n in q_lens)
+
+
+def paged_attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                               block_table: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, n_q_tiles: int,
+                               scale: float, window: Optional[int]) -> None:
+    """Tensor-core attention for a ragged batch of portions (bfloat16, head size 64 or 128)."""
+    _cuda(q, k_pool, v_pool, out, block_table, cu_q, kv_len)
+    n, hq, d = q.shape
+    pages, hkv, page_size, d2 = k_pool.shape
+    assert d2 == d and v_pool.shape == k_pool.shape and out.shape == q.shape
+    assert k_pool.dtype == q.dtype and v_pool.dtype == q.dtype and out.dtype == q.dtype
+    assert block_table.dtype == torch.int32 and cu_q.dtype == torch.int32 and kv_len.dtype == torch.int32
+    s = kv_len.numel()
+    assert cu_q.numel() == s + 1 and block_table.shape[0] == s
+    check(fn("pb_paged_attention_prefill_tc")(code(q.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
+                                              block_table.shape[1], _p(cu_q), _p(kv_len), s, n_q_tiles, hq, hkv, d,
+                                              page_size, float(scale), int(window or 0), stream()),
+          "paged_attention_prefill_tc")
+
+
 def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, window: Optional[int]) -> None:
     """Attention of the step's query tokens over their pages.  ``cache`` is a CacheView
     (pools, block table), ``ctx`` the StepContext (cu_q, kv_len, seq_of_token).  A step of
-    single tokens only takes the split-key decode kernel; anything else the generic one."""
+    single tokens only takes a split-key decode kernel; anything else the tensor-core prefill
+    kernel where it applies (bfloat16, head size 64 or 128), else the generic kernel."""
     if ctx.all_decode:
         n_splits = decode_splits(ctx.n_seqs, cache.k_pool.shape[1])
         partial = ctx.scratch("attn.partial", (ctx.n_seqs * q.shape[1] * n_splits * (q.shape[2] + 2),), torch.float32)
         paged_attention_decode(q, cache.k_pool, cache.v_pool, out, partial, cache.block_table, ctx.kv_len, scale,
                                window, n_splits)
+        return
+    hkv, page_size = cache.k_pool.shape[1], cache.k_pool.shape[2]
+    if prefill_tc_supported(q.dtype, q.shape[1], hkv, q.shape[2], page_size):
+        paged_attention_prefill_tc(q, cache.k_pool, cache.v_pool, out, cache.block_table, ctx.cu_q, ctx.kv_len,
+                                   prefill_tc_tiles(ctx.host.q_lens), scale, window)
         return
     paged_attention_generic(q, cache.k_pool, cache.v_pool, out, cache.block_table, ctx.cu_q, ctx.kv_len,
                             ctx.seq_of_token, scale, window)

@@ -32,7 +32,14 @@ TINY_C = dict(
     rms_norm_eps=3e-6, tie_word_embeddings=False, use_sliding_window=True, sliding_window=12,
     max_window_layers=2, hidden_act="silu", attention_bias=False, initializer_range=0.04, eos_token_id=5)
 
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 4)}     # config, seed, page size
+# Head size 64: the sizes at which the bfloat16 path runs its tensor-core attention kernels.
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=320, hidden_size=128, intermediate_size=192,
+    num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=64, rope_theta=100000.0,
+    rms_norm_eps=2e-6, tie_word_embeddings=True, use_sliding_window=True, sliding_window=40,
+    max_window_layers=1, hidden_act="silu", attention_bias=False, initializer_range=0.03, eos_token_id=3)
+
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 4), "D": (TINY_D, 3, 16)}     # config, seed, page size
 
 
 def make_folder(tmpdir: str, raw: dict, seed: int, store_dtype=torch.float32, std: Optional[float] = None) -> str:

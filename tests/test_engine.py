@@ -48,7 +48,7 @@ def test_greedy_generation_equals_the_plain_implementation(folders, name):
     assert eng.cache.live_requests() == [] and all(f == 64 for f in eng.cache.n_free_pages())
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_greedy_generation_bfloat16_follows_the_plain_logits(folders, name):
     """Rounding may flip near-ties, so each emitted token is checked against the plain logits
     of its own prefix: it must be (nearly) the most probable one."""
@@ -65,7 +65,7 @@ def test_greedy_generation_bfloat16_follows_the_plain_logits(folders, name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "C"])
+@pytest.mark.parametrize("name", ["A", "C", "D"])
 def test_long_decoding(folders, name, dtype):
     """300 tokens one by one after a short prompt: page edges and (in C) the window's edge are
     crossed many times; every position's logits are compared."""

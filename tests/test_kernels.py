@@ -307,6 +307,25 @@ def test_attention_decode_tensor_cores(hq, hkv, d, page, window, n_splits):
     close(outs[0], outs[1].double(), TOL[dtype], "tensor cores vs CUDA cores")
 
 
+@pytest.mark.parametrize("hq,hkv,d,page", TC_SHAPES)
+@pytest.mark.parametrize("window", [None, 37, 200])
+def test_attention_prefill_tensor_cores(hq, hkv, d, page, window):
+    """Ragged batch: first portions, later portions that start inside a page and a tile,
+    single tokens, lengths around the 64-row tile (63, 64, 65, 130), one far key that stands out."""
+    from pulsar_b200 import ops
+    dtype = torch.bfloat16
+    assert ops.prefill_tc_supported(dtype, hq, hkv, d, page)
+    g = torch.Generator().manual_seed(12)
+    lens_q = [16, 7, 33, 1, 1, 2, 64, 63, 65, 130, 5]
+    lens_kv = [16, 40, 33, 65, 1, 129, 100, 63, 300, 130, 517]
+    case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype, spike=(10, 3, hq - 1))
+    out = torch.full((sum(lens_q), hq, d), float("nan"), dtype=dtype, device="cuda")
+    scale = 1.0 / math.sqrt(d)
+    ops.paged_attention_prefill_tc(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, dev(case["table"]),
+                                   dev(case["cu"]), dev(case["kv"]), ops.prefill_tc_tiles(lens_q), scale, window)
+    close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window), TOL[dtype])
+
+
 def test_decode_tensor_cores_applicability():
     from pulsar_b200 import ops
     assert not ops.decode_tc_supported(torch.float32, 32, 8, 128, 16)

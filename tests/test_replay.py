@@ -64,7 +64,7 @@ def _round64(n):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole(folders, name, dtype):
     raw, seed, page = TINY[name]
     rng = random.Random(seed)
@@ -75,7 +75,7 @@ def test_whole(folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_tail_decoded_one_by_one(folders, name, dtype):
     raw, seed, page = TINY[name]
     rng = random.Random(seed + 10)
@@ -87,7 +87,7 @@ def test_tail_decoded_one_by_one(folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_of_changing_size(folders, name, dtype):
     raw, seed, page = TINY[name]
     rng = random.Random(seed + 20)
@@ -99,7 +99,7 @@ def test_portions_of_changing_size(folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_with_page_reuse(folders, name, dtype):
     raw, seed, page = TINY[name]
     rng = random.Random(seed + 30)
