@@ -64,6 +64,68 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     }
 }
 
+// The same with the row held in registers: 4 elements per thread and vector (VPT vectors
+// per thread), one read of every input, vector loads and stores.  width % 4 == 0.
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u);
+    v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+template <typename T, int VPT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                       const float* __restrict__ weight, T* __restrict__ out,
+                                       const int* __restrict__ rows, int width, float eps, int write_back) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* res = residual + (size_t)src * width;
+    const T* del = delta ? delta + (size_t)src * width : nullptr;
+    float x[VPT][4];
+    float local = 0.0f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int i = (threadIdx.x + v * blockDim.x) * 4;
+        if (i < width) {
+            load4(res + i, x[v]);
+            if (del) {
+                float d[4];
+                load4(del + i, d);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) x[v][e] += d[e];
+            }
+            if (write_back) store4(res + i, x[v]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) local += x[v][e] * x[v][e];
+        }
+    }
+    const float total = block_sum(local, scratch);
+    const float inv = rsqrtf(total / (float)width + eps);
+    T* o = out + (size_t)r * width;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int i = (threadIdx.x + v * blockDim.x) * 4;
+        if (i < width) {
+            float w[4], y[4];
+            load4(weight + i, w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) y[e] = x[v][e] * inv * w[e];
+            store4(o + i, y);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- rotary tables
 // cos/sin [N, half] of angle = position * quadrants_per_position[j] * pi/2.  The
 // product is formed in float64 and whole quadrants are removed there (exact), so only
@@ -122,10 +184,49 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
         dst = (is_k ? k_pool : v_pool) + at;
     }
     if (!is_q && !is_k) {
-        for (int i = lane; i < D; i += 32) dst[i] = src[i];
+        if ((D * sizeof(T)) % 16 == 0) {                   // rows are 16-byte aligned: copy vectors
+            const uint4* s16 = reinterpret_cast<const uint4*>(src);
+            uint4* d16 = reinterpret_cast<uint4*>(dst);
+            for (int i = lane; i < (int)(D * sizeof(T) / 16); i += 32) d16[i] = s16[i];
+        } else {
+            for (int i = lane; i < D; i += 32) dst[i] = src[i];
+        }
         return;
     }
     const float* w = is_q ? q_weight : k_weight;
+    if (sizeof(T) == 2 && rotary == D && (D & 3) == 0) {
+        // bfloat16, full rotation: each lane takes element pairs (2i, 2i+1) of both halves with 4-byte accesses.
+        const int half = D >> 1;
+        const int pairs = half >> 1;                       // pairs per half
+        const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src);
+        uint32_t* d32 = reinterpret_cast<uint32_t*>(dst);
+        float ss = 0.0f;
+        for (int i = lane; i < pairs; i += 32) {
+            const uint32_t a = s32[i], b = s32[i + pairs];
+            const float a0 = __uint_as_float(a << 16), a1 = __uint_as_float(a & 0xffff0000u);
+            const float b0 = __uint_as_float(b << 16), b1 = __uint_as_float(b & 0xffff0000u);
+            ss += a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1;
+        }
+        float inv = 1.0f;
+        if (w) inv = rsqrtf(warp_sum(ss) / (float)D + eps);
+        const float2* ct2 = reinterpret_cast<const float2*>(cos_t + (size_t)t * half);
+        const float2* st2 = reinterpret_cast<const float2*>(sin_t + (size_t)t * half);
+        for (int i = lane; i < pairs; i += 32) {
+            const uint32_t a = s32[i], b = s32[i + pairs];
+            float a0 = __uint_as_float(a << 16) * inv, a1 = __uint_as_float(a & 0xffff0000u) * inv;
+            float b0 = __uint_as_float(b << 16) * inv, b1 = __uint_as_float(b & 0xffff0000u) * inv;
+            if (w) {
+                const float2 wa = reinterpret_cast<const float2*>(w)[i], wb = reinterpret_cast<const float2*>(w)[i + pairs];
+                a0 *= wa.x; a1 *= wa.y; b0 *= wb.x; b1 *= wb.y;
+            }
+            const float2 c = ct2[i], sn = st2[i];
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
+            d32[i] = *reinterpret_cast<const uint32_t*>(&lo);
+            d32[i + pairs] = *reinterpret_cast<const uint32_t*>(&hi);
+        }
+        return;
+    }
     float inv = 1.0f;
     if (w) {
         float ss = 0.0f;
@@ -164,6 +265,26 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     }
 }
 
+// The same on 16-byte vectors of bfloat16 (inter % 8 == 0, 16-byte aligned rows).
+__global__ void silu_mul_bf16x8_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, int inter8, size_t total8) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / inter8;
+        const int i = (int)(idx - t * inter8);
+        const uint4 gv = gu[t * 2 * inter8 + i], uv = gu[t * 2 * inter8 + inter8 + i];
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t r[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xffff0000u);
+            const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xffff0000u);
+            const __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+            r[k] = *reinterpret_cast<const uint32_t*>(&v);
+        }
+        out[idx] = make_uint4(r[0], r[1], r[2], r[3]);
+    }
+}
+
 int block_for(int width) {
     int b = 32;
     while (b < 1024 && b * 4 < width) b <<= 1;
@@ -186,12 +307,26 @@ PB_EXPORT int pb_add_rmsnorm(int dtype, float* residual, const void* delta, cons
                              const int* rows, int n_out, int width, float eps, int write_back, cudaStream_t stream) {
     if (n_out <= 0) return 0;
     if (rows && write_back) return PB_ERR_BAD_SIZE;   // gathered rows are read-only
+    if (dtype != PB_F32 && dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
+    const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
+    if (width % 4 == 0 && width <= 8192 && aligned) {
+        const int vecs = width / 4;
+        const int vpt = vecs <= 1024 ? 1 : 2;
+        int threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;
+        if (dtype == PB_F32) {
+            if (vpt == 1) add_rmsnorm_vec_kernel<float, 1><<<n_out, threads, 0, stream>>>(residual, (const float*)delta, weight, (float*)out, rows, width, eps, write_back);
+            else add_rmsnorm_vec_kernel<float, 2><<<n_out, threads, 0, stream>>>(residual, (const float*)delta, weight, (float*)out, rows, width, eps, write_back);
+        } else {
+            if (vpt == 1) add_rmsnorm_vec_kernel<__nv_bfloat16, 1><<<n_out, threads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, width, eps, write_back);
+            else add_rmsnorm_vec_kernel<__nv_bfloat16, 2><<<n_out, threads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, width, eps, write_back);
+        }
+        return launch_status();
+    }
     const int b = block_for(width);
     if (dtype == PB_F32)
         add_rmsnorm_kernel<float><<<n_out, b, 0, stream>>>(residual, (const float*)delta, weight, (float*)out, rows, width, eps, write_back);
-    else if (dtype == PB_BF16)
+    else
         add_rmsnorm_kernel<__nv_bfloat16><<<n_out, b, 0, stream>>>(residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, width, eps, write_back);
-    else return PB_ERR_BAD_DTYPE;
     return launch_status();
 }
 
@@ -229,7 +364,11 @@ PB_EXPORT int pb_silu_mul(int dtype, const void* gate_up, void* out, int n, int 
     const int b = 256;
     size_t blocks = (total + b - 1) / b;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    if (dtype == PB_F32) silu_mul_kernel<float><<<(int)blocks, b, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    if (dtype == PB_BF16 && inter % 8 == 0 && ((uintptr_t)gate_up & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        size_t total8 = total / 8, blocks8 = (total8 + b - 1) / b;
+        if (blocks8 > 148 * 16) blocks8 = 148 * 16;
+        silu_mul_bf16x8_kernel<<<(int)blocks8, b, 0, stream>>>((const uint4*)gate_up, (uint4*)out, inter / 8, total8);
+    } else if (dtype == PB_F32) silu_mul_kernel<float><<<(int)blocks, b, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
     else if (dtype == PB_BF16) silu_mul_kernel<__nv_bfloat16><<<(int)blocks, b, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
     else return PB_ERR_BAD_DTYPE;
     return launch_status();

@@ -1,0 +1,166 @@
+// out[M, N] = x[M, K] * W[N, K]^T for a handful of tokens (M <= 16) in bfloat16: the
+// projections of a decode step, where every weight is read once and the time is the time
+// to stream W from HBM.
+//
+// The weights take the role of the MMA's 16-row operand and the tokens that of its 8-wide
+// one (mma.m16n8k16, float32 accumulators).  Nothing is staged in shared memory: a thread
+// loads 16 contiguous bytes of a weight row straight into the registers of the A fragment
+// and 16 bytes of a token's activations into the B fragment; because a dot product does
+// not care about the order of its terms, the k-index that a fragment slot stands for is
+// permuted the same way on both sides, which makes the vector loads legal.  A block owns
+// 16 weight rows; its 8 warps split K, keep 8 vector loads each in flight, and their
+// partial sums are added in warp order through shared memory.
+//
+// Epilogues: plain (bfloat16 or float32 output), or SwiGLU: the block's 16 rows are 8 gate
+// rows and the 8 up rows that belong to them, and it writes silu(gate) * up (float32
+// gating, one rounding), so the [M, 2I] intermediate never exists.
+//
+// The reference calls at::linear three times for q/k/v, once for o, twice for gate/up and
+// once for down, plus two elementwise kernels for the gating
+// (pulsar-core/src/model/qwen3.cpp:82-84, 114, 117-119).
+#include "mma_common.cuh"
+
+namespace {
+
+using namespace pb;
+
+constexpr int kWarps = 8;
+constexpr int kRows = 16;
+constexpr int kBlockK = 32;      // k per two MMAs: 4 threads x 8 contiguous elements
+constexpr int kUnroll = 4;
+
+__device__ __forceinline__ uint4 load_stream(const void* p) {      // weights: read once, keep them out of L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+enum { kPlain = 0, kSwiGLU = 1 };
+
+// NT: n-tiles of 8 tokens.  Mode kSwiGLU: rows r of the block are gate rows 8*b + r (r < 8) and up rows
+// inter + 8*b + (r - 8); the output has `inter` columns.
+template <int NT, int MODE, typename OutT>
+__global__ void __launch_bounds__(kWarps * 32)
+gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
+                   int inter) {
+    __shared__ float red[kWarps][kRows][8 * NT + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    int row_a, row_b;                                   // weight rows behind fragment rows g and g + 8
+    if (MODE == kSwiGLU) { row_a = blockIdx.x * 8 + g; row_b = inter + blockIdx.x * 8 + g; }
+    else { row_a = blockIdx.x * kRows + g; row_b = row_a + 8; }
+    const bf16* wa_p = w + (size_t)row_a * K + 8 * t;
+    const bf16* wb_p = w + (size_t)row_b * K + 8 * t;
+    const bf16* x_p[NT];
+    bool x_ok[NT];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        x_ok[n] = n * 8 + g < M;
+        x_p[n] = x + (size_t)(x_ok[n] ? n * 8 + g : 0) * K + 8 * t;
+    }
+    float c[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) { c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.0f; }
+
+    const int blocks = K / kBlockK;
+    const int kb_begin = (int)((long long)blocks * warp / kWarps), kb_end = (int)((long long)blocks * (warp + 1) / kWarps);
+    int kb = kb_begin;
+    for (; kb + kUnroll <= kb_end; kb += kUnroll) {
+        uint4 wa[kUnroll], wb[kUnroll], xv[kUnroll][NT];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            wa[u] = load_stream(wa_p + (size_t)(kb + u) * kBlockK);
+            wb[u] = load_stream(wb_p + (size_t)(kb + u) * kBlockK);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+                xv[u][n] = x_ok[n] ? __ldg(reinterpret_cast<const uint4*>(x_p[n] + (size_t)(kb + u) * kBlockK)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const uint32_t a1[4] = {wa[u].x, wb[u].x, wa[u].y, wb[u].y};
+            const uint32_t a2[4] = {wa[u].z, wb[u].z, wa[u].w, wb[u].w};
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                mma_bf16(c[n], a1, xv[u][n].x, xv[u][n].y);
+                mma_bf16(c[n], a2, xv[u][n].z, xv[u][n].w);
+            }
+        }
+    }
+    for (; kb < kb_end; ++kb) {
+        const uint4 wa = load_stream(wa_p + (size_t)kb * kBlockK), wb = load_stream(wb_p + (size_t)kb * kBlockK);
+        const uint32_t a1[4] = {wa.x, wb.x, wa.y, wb.y};
+        const uint32_t a2[4] = {wa.z, wb.z, wa.w, wb.w};
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            const uint4 xv = x_ok[n] ? __ldg(reinterpret_cast<const uint4*>(x_p[n] + (size_t)kb * kBlockK)) : make_uint4(0, 0, 0, 0);
+            mma_bf16(c[n], a1, xv.x, xv.y);
+            mma_bf16(c[n], a2, xv.z, xv.w);
+        }
+    }
+    // accumulator (row g | g+8, token n*8 + 2t | +1) -> shared memory, then the warps are added in order
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        red[warp][g][n * 8 + 2 * t] = c[n][0];
+        red[warp][g][n * 8 + 2 * t + 1] = c[n][1];
+        red[warp][g + 8][n * 8 + 2 * t] = c[n][2];
+        red[warp][g + 8][n * 8 + 2 * t + 1] = c[n][3];
+    }
+    __syncthreads();
+    if (MODE == kSwiGLU) {
+        for (int i = tid; i < 8 * M; i += kWarps * 32) {
+            const int token = i / 8, r = i % 8;
+            float gate = 0.0f, up = 0.0f;
+#pragma unroll
+            for (int wi = 0; wi < kWarps; ++wi) { gate += red[wi][r][token]; up += red[wi][r + 8][token]; }
+            out[(size_t)token * inter + blockIdx.x * 8 + r] = from_float<OutT>(gate / (1.0f + expf(-gate)) * up);
+        }
+    } else {
+        for (int i = tid; i < kRows * M; i += kWarps * 32) {
+            const int token = i / kRows, r = i % kRows;
+            float acc = 0.0f;
+#pragma unroll
+            for (int wi = 0; wi < kWarps; ++wi) acc += red[wi][r][token];
+            out[(size_t)token * N + blockIdx.x * kRows + r] = from_float<OutT>(acc);
+        }
+    }
+}
+
+template <int NT>
+int launch(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)w;
+    if (mode == kSwiGLU) {
+        const int inter = N / 2;
+        if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
+        gemm_skinny_kernel<NT, kSwiGLU, bf16><<<inter / 8, kWarps * 32, 0, stream>>>(xp, wp, (bf16*)out, M, N, K, inter);
+    } else if (out_dtype == PB_BF16) {
+        gemm_skinny_kernel<NT, kPlain, bf16><<<N / kRows, kWarps * 32, 0, stream>>>(xp, wp, (bf16*)out, M, N, K, 0);
+    } else {
+        gemm_skinny_kernel<NT, kPlain, float><<<N / kRows, kWarps * 32, 0, stream>>>(xp, wp, (float*)out, M, N, K, 0);
+    }
+    return launch_status();
+}
+
+}  // namespace
+
+// 1 if pb_gemm_skinny takes this problem (bfloat16 operands; else the caller uses the library product).
+PB_EXPORT int pb_gemm_skinny_supported(int mode, int M, int N, int K) {
+    if (M <= 0 || M > 16 || K <= 0 || K % kBlockK) return 0;
+    if (mode == kSwiGLU) return (N % 16 == 0) ? 1 : 0;       // N = 2 * inter, inter % 8 == 0
+    if (mode != kPlain) return 0;
+    return (N % kRows == 0) ? 1 : 0;
+}
+
+// mode 0: out[M, N] (out_dtype bfloat16 or float32).  mode 1: W = [gate rows; up rows] with N = 2 * inter,
+// out[M, inter] = silu(x Wg^T) * (x Wu^T) in bfloat16.  x, W bfloat16, 16-byte aligned.
+PB_EXPORT int pb_gemm_skinny(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K,
+                             cudaStream_t stream) {
+    if (!pb_gemm_skinny_supported(mode, M, N, K)) return PB_ERR_BAD_SIZE;
+    if ((((uintptr_t)x | (uintptr_t)w) & 15) != 0) return PB_ERR_BAD_SIZE;
+    if (out_dtype != PB_BF16 && out_dtype != PB_F32) return PB_ERR_BAD_DTYPE;
+    if (M <= 8) return launch<1>(mode, out_dtype, x, w, out, M, N, K, stream);
+    return launch<2>(mode, out_dtype, x, w, out, M, N, K, stream);
+}

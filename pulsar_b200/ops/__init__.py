@@ -35,6 +35,8 @@ _SIGNATURES = {
     "pb_paged_attention_prefill_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "pb_prefill_tc_supported": [_I, _I, _I, _I, _I],
     "pb_prefill_tc_tile": [],
+    "pb_gemm_skinny": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
+    "pb_gemm_skinny_supported": [_I, _I, _I, _I],
     "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _P, _P],
 }
@@ -195,21 +197,52 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
                           stream()), "sample")
 
 
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> bool:
+    """The weight-streaming product for up to 16 tokens (bfloat16).  ``swiglu``: ``w`` holds
+    gate rows then up rows and ``out`` [M, inter] receives silu(gate) * up.  Returns False,
+    having done nothing, when the sizes are not the kernel's."""
+    m, k = a.shape
+    n = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k:
+        return False
+    mode = 1 if swiglu else 0
+    if not fn("pb_gemm_skinny_supported")(mode, m, n, k):
+        return False
+    _cuda(a, w, out)
+    assert out.shape == (m, n // 2 if swiglu else n)
+    check(fn("pb_gemm_skinny")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream()), "gemm_skinny")
+    return True
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out = a @ w.T.  float32 operands take the float32 CUDA-core product (true 32-bit,
-    no reduced-precision mode).  bfloat16 operands take the library product with
-    float32 accumulation, as the reference does for every projection
-    (pulsar-core/src/model/qwen3.cpp:82-84: at::linear)."""
+    no reduced-precision mode).  bfloat16 operands: up to 16 rows take this library's
+    weight-streaming kernel; more rows take the library product with float32 accumulation,
+    as the reference does for every projection (pulsar-core/src/model/qwen3.cpp:82-84:
+    at::linear)."""
     if a.dtype == torch.float32 and w.dtype == torch.float32:
         gemm_simt(a, w, out)
         return
     _cuda(a, w, out)
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"linear: operand dtypes {a.dtype} / {w.dtype} must both be float32 or both bfloat16")
+    if gemm_skinny(a, w, out):
+        return
     if out.dtype == torch.bfloat16:
         torch.mm(a, w.t(), out=out)
     else:
         out.copy_(torch.mm(a, w.t(), out_dtype=torch.float32))
+
+
+def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out [M, I] = silu(a Wg^T) * (a Wu^T) with ``w_gate_up`` = gate rows then up rows.  Few
+    bfloat16 rows: one kernel that never writes the [M, 2I] intermediate; otherwise the
+    product followed by the gating kernel."""
+    if gemm_skinny(a, w_gate_up, out, swiglu=True):
+        return
+    gate_up = ctx.scratch("mlp.gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
+    linear(a, w_gate_up, gate_up)
+    silu_mul(gate_up, out)
 
 
 def decode_splits(n_seqs: int, n_kv_heads: int) -> int:

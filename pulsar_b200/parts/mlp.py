@@ -39,10 +39,8 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         s, n = self.spec, ctx.n_tokens
-        gate_up = ctx.scratch("mlp.gate_up", (n, 2 * s.intermediate))
-        ops.linear(h, self.w_gate_up, gate_up)
         act = ctx.scratch("mlp.act", (n, s.intermediate))
-        ops.silu_mul(gate_up, act)
+        ops.gated_linear(ctx, h, self.w_gate_up, act)
         out = ctx.scratch("mlp.out", (n, s.hidden))
         ops.linear(act, self.w_down, out)
         return out

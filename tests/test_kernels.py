@@ -169,6 +169,41 @@ def test_gemm_simt_is_true_float32(m, n, k):
         assert torch.equal(out2, out[m - 2:])
 
 
+@pytest.mark.parametrize("m", [1, 2, 7, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(48, 96), (4096, 4096), (1024, 12288), (304, 160)])
+def test_gemm_skinny(m, n, k):
+    """The weight-streaming product for a few tokens against float64, plain and with the
+    SwiGLU epilogue, float32 and bfloat16 outputs; one weight made large so that a wrong
+    k-permutation of the fragments would show."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(13)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).bfloat16()
+    w[n // 3, (5 * k) // 7] = 3.0
+    ref = a.double() @ w.double().T
+    for dt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 1e-2)):
+        out = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
+        assert ops.gemm_skinny(dev(a), dev(w), out)
+        close(out, ref, tol, f"plain {dt}")
+    inter = n // 2
+    gate, up = ref[:, :inter], ref[:, inter:]
+    act = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops.gemm_skinny(dev(a), dev(w), act, swiglu=True)
+    close(act, gate * torch.sigmoid(gate) * up, 1e-2, "swiglu")
+
+
+def test_gemm_skinny_declines_other_sizes():
+    from pulsar_b200 import ops
+    a = torch.zeros(17, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device="cuda")
+    assert not ops.gemm_skinny(a, w, torch.empty(17, 32, dtype=torch.bfloat16, device="cuda"))          # too many rows
+    assert not ops.gemm_skinny(a[:4, :48].contiguous(), w[:, :48].contiguous(), torch.empty(4, 32, dtype=torch.bfloat16, device="cuda"))
+    assert not ops.gemm_skinny(a[:4], w[:24], torch.empty(4, 24, dtype=torch.bfloat16, device="cuda"))  # rows no multiple of 16
+    out = torch.empty(17, 32, dtype=torch.bfloat16, device="cuda")
+    ops.linear(a, w, out)                                                                              # falls to the library product
+    assert float(out.abs().max()) == 0.0
+
+
 def test_gemm_simt_mixed_dtypes():
     from pulsar_b200 import ops
     g = torch.Generator().manual_seed(5)
