@@ -178,25 +178,36 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
     }
 }
 
+// One block per (sequence, head): the weights exp(m_i - m_all) of the splits are computed
+// once, then every thread adds its column over the splits in split order.
 template <typename T>
 __global__ void decode_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int D, int n_splits) {
+    __shared__ float w_s[64];                            // n_splits <= 64 (checked by the launchers)
+    __shared__ float l_s;
     const size_t row = blockIdx.x;                       // s * Hq + h
     const int stride = D + 2;
     const float* base = partial + row * n_splits * stride;
-    float m_all = -INFINITY;
-    for (int i = 0; i < n_splits; ++i) m_all = fmaxf(m_all, base[i * stride + D]);
-    float l_all = 0.0f;
-    for (int i = 0; i < n_splits; ++i) {
-        const float m = base[i * stride + D];
-        if (m > -INFINITY) l_all += base[i * stride + D + 1] * expf(m - m_all);
+    if (threadIdx.x < 32) {
+        float m_all = -INFINITY;
+        for (int i = threadIdx.x; i < n_splits; i += 32) m_all = fmaxf(m_all, base[i * stride + D]);
+        m_all = warp_max(m_all);
+        float l_part = 0.0f;
+        for (int i = threadIdx.x; i < n_splits; i += 32) {
+            const float m = base[i * stride + D];
+            const float w = (m > -INFINITY) ? expf(m - m_all) : 0.0f;
+            w_s[i] = w;
+            l_part += base[i * stride + D + 1] * w;
+        }
+        // lanes hold disjoint splits; add them in lane order for a fixed result
+        for (int o = 16; o > 0; o >>= 1) l_part += __shfl_xor_sync(0xffffffffu, l_part, o);
+        if (threadIdx.x == 0) l_s = l_part;
     }
+    __syncthreads();
+    const float inv = 1.0f / l_s;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float o = 0.0f;
-        for (int i = 0; i < n_splits; ++i) {
-            const float m = base[i * stride + D];
-            if (m > -INFINITY) o += base[i * stride + d] * expf(m - m_all);
-        }
-        out[row * D + d] = from_float<T>(o / l_all);
+        for (int i = 0; i < n_splits; ++i) o = fmaf(base[i * stride + d], w_s[i], o);
+        out[row * D + d] = from_float<T>(o * inv);
     }
 }
 
@@ -218,7 +229,7 @@ PB_EXPORT int pb_paged_attention_decode(int dtype, const void* q, const void* k_
                                         int n_splits, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (D <= 0 || D % 16 || D > kMaxD || Hkv <= 0 || Hq % Hkv || page_size <= 0 || n_splits <= 0) return PB_ERR_BAD_SIZE;
-    if (Hkv > 65535 || n_seqs > 65535) return PB_ERR_TOO_LARGE;
+    if (Hkv > 65535 || n_seqs > 65535 || n_splits > 64) return PB_ERR_TOO_LARGE;
     const size_t smem = split_smem(D);
     dim3 grid(n_splits, Hkv, n_seqs);
     if (dtype == PB_F32) {
@@ -313,6 +324,7 @@ PB_EXPORT int pb_paged_attention_decode_noalloc(int dtype, const void* q, const 
 PB_EXPORT int pb_decode_combine(int dtype, const float* partial, void* out, int rows, int D, int n_splits,
                                 cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (n_splits <= 0 || n_splits > 64) return PB_ERR_TOO_LARGE;
     if (dtype == PB_F32) decode_combine_kernel<float><<<rows, 128, 0, stream>>>(partial, (float*)out, D, n_splits);
     else if (dtype == PB_BF16) decode_combine_kernel<__nv_bfloat16><<<rows, 128, 0, stream>>>(partial, (__nv_bfloat16*)out, D, n_splits);
     else return PB_ERR_BAD_DTYPE;

@@ -28,8 +28,7 @@ template <int D>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                  float* __restrict__ partial, const int* __restrict__ block_table, int table_stride,
-                 const int* __restrict__ kv_len, int Hq, int Hkv, int page_size, float scale, int window, int n_splits) {
-    constexpr int kChunks = D / 8;                    // 16-byte chunks per row
+                 const int* __restrict__ kv_len, int Hq, int Hkv, int page_shift, float scale, int window, int n_splits) {
     constexpr int kTileBytes = kTile * D * 2;
     constexpr int kKSteps = D / 16;                   // k-steps of Q K^T
     constexpr int kNTiles = D / 8;                    // n-tiles of P V
@@ -67,23 +66,9 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
     }
 
     auto issue_tile = [&](int tile_index, int stage) {
-        const int key0 = (tile0 + tile_index) * kTile;
-        const uint32_t k_dst = smem_base + stage * 2 * kTileBytes, v_dst = k_dst + kTileBytes;
-#pragma unroll
-        for (int i = 0; i < kTile * kChunks / (kWarps * 32); ++i) {
-            const int idx = i * kWarps * 32 + tid;
-            const int row = idx / kChunks, c = idx % kChunks;
-            const int key = key0 + row;
-            const bool ok = key >= begin && key < end;
-            size_t at = 0;
-            if (ok) {
-                const int page = table[key / page_size];
-                at = (((size_t)page * Hkv + kvh) * page_size + key % page_size) * D + c * 8;
-            }
-            const uint32_t off = tile_offset<D>(row, c);
-            cp_async16(k_dst + off, k_pool + at, ok);
-            cp_async16(v_dst + off, v_pool + at, ok);
-        }
+        const uint32_t k_dst = smem_base + stage * 2 * kTileBytes;
+        load_kv_tile<D, kWarps * 32>(k_dst, k_dst + kTileBytes, k_pool, v_pool, table, (tile0 + tile_index) * kTile, begin,
+                                     end - 1, kvh, Hkv, page_shift, tid);
     };
 
     float o[kNTiles][4];
@@ -124,15 +109,25 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
         }
         // mask and scale; thread holds keys key_base + n*8 + 2t + {0,1} for rows g (c0,c1) and g+8 (c2,c3)
         float tmax[2] = {-INFINITY, -INFINITY};
+        if (key_base >= begin && key_base + 16 <= end) {                   // every key of the warp is in range
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < 2; ++n)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = key_base + n * 8 + 2 * t + (e & 1);
-                const float v = (key >= begin && key < end) ? sc[n][e] * sl2 : -INFINITY;
-                sc[n][e] = v;
-                tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
-            }
+                for (int e = 0; e < 4; ++e) {
+                    sc[n][e] *= sl2;
+                    tmax[e >> 1] = fmaxf(tmax[e >> 1], sc[n][e]);
+                }
+        } else {
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key_base + n * 8 + 2 * t + (e & 1);
+                    const float v = (key >= begin && key < end) ? sc[n][e] * sl2 : -INFINITY;
+                    sc[n][e] = v;
+                    tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
+                }
+        }
         float corr[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -223,6 +218,7 @@ template <int D>
 int launch_tc(const void* q, const void* k_pool, const void* v_pool, float* partial, const int* block_table,
               int table_stride, const int* kv_len, int n_seqs, int Hq, int Hkv, int page_size, float scale, int window,
               int n_splits, cudaStream_t stream) {
+    const int page_shift = log2_exact(page_size);
     constexpr int pipeline = kStages * 2 * kTile * D * 2;
     constexpr int merge = (kWarps * 16 * D + 2 * kWarps * 16) * 4;
     constexpr int smem = pipeline > merge ? pipeline : merge;
@@ -234,7 +230,7 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, float* part
     }
     dim3 grid(n_splits, Hkv, n_seqs);
     decode_tc_kernel<D><<<grid, kWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, partial,
-                                                             block_table, table_stride, kv_len, Hq, Hkv, page_size, scale,
+                                                             block_table, table_stride, kv_len, Hq, Hkv, page_shift, scale,
                                                              window, n_splits);
     return launch_status();
 }
@@ -247,7 +243,7 @@ PB_EXPORT int pb_decode_combine(int dtype, const float* partial, void* out, int 
 PB_EXPORT int pb_decode_tc_supported(int dtype, int Hq, int Hkv, int D, int page_size) {
     if (dtype != PB_BF16 || Hkv <= 0 || Hq % Hkv || Hq / Hkv > 16) return 0;
     if (D != 64 && D != 128) return 0;
-    if (page_size <= 0 || page_size > kTile || (kTile % page_size)) return 0;
+    if (log2_exact(page_size) < 0 || page_size > kTile) return 0;      // a power of two up to the tile
     return 1;
 }
 

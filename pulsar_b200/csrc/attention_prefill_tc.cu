@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2)
 prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                   bf16* __restrict__ out, const int* __restrict__ block_table, int table_stride,
                   const int* __restrict__ cu_q, const int* __restrict__ kv_len, int n_seqs, int Hq, int Hkv,
-                  int page_size, float scale, int window) {
+                  int page_shift, float scale, int window) {
     constexpr int kChunks = D / 8;
     constexpr int kTileBytes = kBN * D * 2;
     constexpr int kKSteps = D / 16;
@@ -68,23 +68,9 @@ prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, c
     const int* table = block_table + (size_t)s * table_stride;
 
     auto issue_kv = [&](int tile_index, int stage) {
-        const int key0 = (kt0 + tile_index) * kBN;
-        const uint32_t k_dst = smem_base + stage * 2 * kTileBytes, v_dst = k_dst + kTileBytes;
-#pragma unroll
-        for (int i = 0; i < kBN * kChunks / (kWarps * 32); ++i) {
-            const int idx = i * kWarps * 32 + tid;
-            const int row = idx / kChunks, c = idx % kChunks;
-            const int key = key0 + row;
-            const bool ok = key >= lo && key <= pos_last;
-            size_t at = 0;
-            if (ok) {
-                const int page = table[key / page_size];
-                at = (((size_t)page * Hkv + kvh) * page_size + key % page_size) * D + c * 8;
-            }
-            const uint32_t off = tile_offset<D>(row, c);
-            cp_async16(k_dst + off, k_pool + at, ok);
-            cp_async16(v_dst + off, v_pool + at, ok);
-        }
+        const uint32_t k_dst = smem_base + stage * 2 * kTileBytes;
+        load_kv_tile<D, kWarps * 32>(k_dst, k_dst + kTileBytes, k_pool, v_pool, table, (kt0 + tile_index) * kBN, lo, pos_last,
+                                     kvh, Hkv, page_shift, tid);
     };
 
     // Q tile through the second stage's K buffer into registers, while the first K/V tile loads.
@@ -150,17 +136,29 @@ prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, c
                 }
             }
             float tmax[2] = {-INFINITY, -INFINITY};
+            // every row of the warp sees every key of the tile: below the diagonal and inside the window
+            const bool all_visible = key0 + kBN - 1 <= wpos_first && (window <= 0 || key0 > wpos_last - window);
+            if (all_visible) {
 #pragma unroll
-            for (int n = 0; n < kBN / 8; ++n)
+                for (int n = 0; n < kBN / 8; ++n)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + n * 8 + 2 * t + (e & 1);
-                    const int pos = (e >> 1) ? pos1 : pos0;
-                    const bool vis = key <= pos && (window <= 0 || key > pos - window);
-                    const float v = vis ? sc[n][e] * sl2 : -INFINITY;
-                    sc[n][e] = v;
-                    tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
-                }
+                    for (int e = 0; e < 4; ++e) {
+                        sc[n][e] *= sl2;
+                        tmax[e >> 1] = fmaxf(tmax[e >> 1], sc[n][e]);
+                    }
+            } else {
+#pragma unroll
+                for (int n = 0; n < kBN / 8; ++n)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + n * 8 + 2 * t + (e & 1);
+                        const int pos = (e >> 1) ? pos1 : pos0;
+                        const bool vis = key <= pos && (window <= 0 || key > pos - window);
+                        const float v = vis ? sc[n][e] * sl2 : -INFINITY;
+                        sc[n][e] = v;
+                        tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
+                    }
+            }
             float corr[2], m_safe[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
@@ -238,6 +236,7 @@ int launch_prefill(const void* q, const void* k_pool, const void* v_pool, void* 
                    int table_stride, const int* cu_q, const int* kv_len, int n_seqs, int n_q_tiles, int Hq, int Hkv,
                    int page_size, float scale, int window, cudaStream_t stream) {
     constexpr int smem = 2 * 2 * kBN * D * 2;
+    const int page_shift = log2_exact(page_size);
     static bool configured = false;
     if (!configured) {
         cudaError_t rc = cudaFuncSetAttribute(prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -247,7 +246,7 @@ int launch_prefill(const void* q, const void* k_pool, const void* v_pool, void* 
     dim3 grid(n_q_tiles, Hq);
     prefill_tc_kernel<D><<<grid, kWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
                                                               (bf16*)out, block_table, table_stride, cu_q, kv_len, n_seqs,
-                                                              Hq, Hkv, page_size, scale, window);
+                                                              Hq, Hkv, page_shift, scale, window);
     return launch_status();
 }
 
@@ -259,7 +258,7 @@ PB_EXPORT int pb_prefill_tc_tile(void) { return kBM; }
 PB_EXPORT int pb_prefill_tc_supported(int dtype, int Hq, int Hkv, int D, int page_size) {
     if (dtype != PB_BF16 || Hkv <= 0 || Hq % Hkv) return 0;
     if (D != 64 && D != 128) return 0;
-    if (page_size <= 0 || page_size > kBN || (kBN % page_size)) return 0;
+    if (log2_exact(page_size) < 0 || page_size > kBN) return 0;         // a power of two up to the tile
     return 1;
 }
 

@@ -27,7 +27,7 @@ using namespace pb;
 constexpr int kWarps = 8;
 constexpr int kRows = 16;
 constexpr int kBlockK = 32;      // k per two MMAs: 4 threads x 8 contiguous elements
-constexpr int kUnroll = 4;
+constexpr int kUnroll = 8;
 
 __device__ __forceinline__ uint4 load_stream(const void* p) {      // weights: read once, keep them out of L1
     uint4 v;

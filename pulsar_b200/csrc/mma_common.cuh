@@ -49,4 +49,58 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
     return (uint32_t)(row * kChunks + (chunk ^ (row & 7))) * 16u;
 }
 
+// Gathers one 64-key tile of K and of V for kv head `kvh` through the block table into two
+// swizzled shared-memory tiles with 16-byte asynchronous copies.  Keys outside
+// [first_key, last_key] are filled with zeros and their pages are not touched.  Pages hold
+// 2^page_shift keys (a power of two that divides 64); pools are [pages, Hkv, page, D].
+// Each thread keeps one 16-byte column and walks down the rows, so that the swizzle and
+// most of the address are loop constants.
+template <int D, int THREADS>
+__device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, const bf16* __restrict__ k_pool,
+                                             const bf16* __restrict__ v_pool, const int* __restrict__ table, int key0,
+                                             int first_key, int last_key, int kvh, int Hkv, int page_shift, int tid) {
+    constexpr int kChunks = D / 8;
+    constexpr int kRowsPerPass = THREADS / kChunks;       // a multiple of 8: (row & 7) does not change
+    constexpr int kPasses = 64 / kRowsPerPass;
+    static_assert(THREADS % kChunks == 0 && kRowsPerPass % 8 == 0 && 64 % kRowsPerPass == 0, "tile loader shape");
+    const int c = tid % kChunks, r0 = tid / kChunks;
+    const uint32_t off0 = tile_offset<D>(r0, c);
+    const int page_mask = (1 << page_shift) - 1;
+    const size_t page_elems = (size_t)D << page_shift;    // elements of one (page, kv head) block
+    const int col = c * 8;
+    if (key0 >= first_key && key0 + 63 <= last_key) {
+#pragma unroll
+        for (int i = 0; i < kPasses; ++i) {
+            const int key = key0 + r0 + i * kRowsPerPass;
+            const int page = table[key >> page_shift];
+            const size_t at = (size_t)(page * Hkv + kvh) * page_elems + (size_t)((key & page_mask) * D + col);
+            const uint32_t off = off0 + (uint32_t)(i * kRowsPerPass * kChunks * 16);
+            cp_async16(k_dst + off, k_pool + at, true);
+            cp_async16(v_dst + off, v_pool + at, true);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < kPasses; ++i) {
+            const int key = key0 + r0 + i * kRowsPerPass;
+            const bool ok = key >= first_key && key <= last_key;
+            size_t at = 0;
+            if (ok) {
+                const int page = table[key >> page_shift];
+                at = (size_t)(page * Hkv + kvh) * page_elems + (size_t)((key & page_mask) * D + col);
+            }
+            const uint32_t off = off0 + (uint32_t)(i * kRowsPerPass * kChunks * 16);
+            cp_async16(k_dst + off, k_pool + at, ok);
+            cp_async16(v_dst + off, v_pool + at, ok);
+        }
+    }
+}
+
+// log2 of a power of two (host side); -1 otherwise.
+inline int log2_exact(int v) {
+    if (v <= 0 || (v & (v - 1))) return -1;
+    int s = 0;
+    while ((1 << s) < v) ++s;
+    return s;
+}
+
 }  // namespace pb

@@ -150,7 +150,63 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     }
 }
 
+// Greedy rows over many blocks: every block reduces a slice of the row to (value, index) and
+// merges it into the row's 64-bit key with atomicMax.  The key orders by value, then by
+// lower index: high word = float bits made monotone, low word = ~index.
+__device__ __forceinline__ unsigned long long argmax_key(float v, int i) {
+    uint32_t b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)b << 32) | (uint32_t)(~(uint32_t)i);
+}
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, int vocab, unsigned long long* __restrict__ keys) {
+    __shared__ Best best_s[32];
+    const int r = blockIdx.y;
+    const float* row = logits + (size_t)r * vocab;
+    const int per = (vocab + gridDim.x - 1) / gridDim.x;
+    const int begin = blockIdx.x * per, end = min(vocab, begin + per);
+    Best best = {-INFINITY, 0x7fffffff};
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) best = better(best, Best{row[i], i});
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other = {__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) best_s[warp] = best;
+    __syncthreads();
+    if (warp == 0) {
+        best = (lane < (int)(blockDim.x >> 5)) ? best_s[lane] : Best{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other = {__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+            best = better(best, other);
+        }
+        if (lane == 0 && best.i != 0x7fffffff) atomicMax(keys + r, argmax_key(best.v, best.i));
+    }
+}
+
+__global__ void argmax_finish_kernel(const unsigned long long* __restrict__ keys, int* __restrict__ out, int rows) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < rows) out[r] = keys[r] ? (int)(~(uint32_t)(keys[r] & 0xffffffffu)) : 0;
+}
+
 }  // namespace
+
+// Greedy selection for every row with many blocks per row.  `keys` is scratch of `rows`
+// 64-bit words (cleared here, on the stream).
+PB_EXPORT int pb_argmax(const float* logits, int rows, int vocab, unsigned long long* keys, int* out, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (vocab <= 0 || rows > 65535) return PB_ERR_BAD_SIZE;
+    cudaError_t rc = cudaMemsetAsync(keys, 0, sizeof(unsigned long long) * rows, stream);
+    if (rc != cudaSuccess) return (int)rc;
+    int slices = (vocab + 4095) / 4096;
+    if (slices > 64) slices = 64;
+    argmax_partial_kernel<<<dim3(slices, rows), 256, 0, stream>>>(logits, vocab, keys);
+    argmax_finish_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(keys, out, rows);
+    return launch_status();
+}
 
 // temperature, top_k, top_p may be null (greedy / off); uniform may be null only when every row is greedy.
 PB_EXPORT int pb_sample(const float* logits, int rows, int vocab, const float* temperature, const int* top_k,

@@ -39,6 +39,7 @@ _SIGNATURES = {
     "pb_gemm_skinny_supported": [_I, _I, _I, _I],
     "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _P, _P],
+    "pb_argmax": [_P, _I, _I, _P, _P, _P],
 }
 _fns = {}
 
@@ -182,6 +183,9 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
           "gemm_simt")
 
 
+_argmax_keys = {}
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
            top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
            uniform: Optional[torch.Tensor] = None) -> None:
@@ -193,6 +197,12 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
     assert top_k is None or (top_k.dtype == torch.int32 and top_k.numel() == rows)
     assert top_p is None or (top_p.dtype == torch.float32 and top_p.numel() == rows)
     assert uniform is None or (uniform.dtype == torch.float32 and uniform.numel() == rows)
+    if temperature is None:                       # all rows greedy: many blocks per row
+        keys = _argmax_keys.get(logits.device)
+        if keys is None or keys.numel() < rows:
+            keys = _argmax_keys[logits.device] = torch.empty(max(rows, 256), dtype=torch.int64, device=logits.device)
+        check(fn("pb_argmax")(_p(logits), rows, vocab, _p(keys), _p(out), stream()), "argmax", kernels=2)
+        return
     check(fn("pb_sample")(_p(logits), rows, vocab, _p(temperature), _p(top_k), _p(top_p), _p(uniform), _p(out),
                           stream()), "sample")
 
@@ -246,10 +256,10 @@ def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tenso
 
 
 def decode_splits(n_seqs: int, n_kv_heads: int) -> int:
-    """Splits of the keys per (sequence, kv head): enough blocks to fill 148 SMs four
-    times over.  A function of the batch alone, so that a captured step stays valid
-    while its sequences grow."""
-    return max(1, min(64, -(-592 // max(1, n_seqs * n_kv_heads))))
+    """Splits of the keys per (sequence, kv head): as many as fit one wave of two blocks on
+    each of the 148 SMs, at most 16.  A function of the batch alone, so that a captured step
+    stays valid while its sequences grow."""
+    return max(1, min(16, 296 // max(1, n_seqs * n_kv_heads)))
 
 
 def decode_tc_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
