@@ -1,0 +1,334 @@
+// out[M, N] = x[M, K] * W[N, K]^T for many tokens in bfloat16 on the fifth-generation tensor
+// cores: tcgen05.mma with the accumulator in tensor memory, operands brought into shared
+// memory by TMA (cp.async.bulk.tensor) and handed over through mbarriers.
+//
+// One block computes a tile of 128 tokens x 256 features.  Roles inside the block:
+//   warp 0, one thread   TMA producer: per 64-wide slice of K one [128 x 64] box of x and two
+//                        [128 x 64] boxes of W into a 4-stage ring (128-byte swizzle), each
+//                        stage guarded by a "full" barrier that counts the arriving bytes;
+//   warp 1, one thread   MMA issuer: four tcgen05.mma (M 128, N 256, K 16) per stage straight
+//                        from shared memory into 256 columns of tensor memory; a
+//                        tcgen05.commit releases the stage ("empty" barrier) when the tensor
+//                        core has read it, a last one announces the finished accumulator;
+//   all four warps       epilogue: tcgen05.ld of the warp's 32 lanes (= 32 tokens), 32 columns
+//                        at a time, then the rounding and the store.
+// Epilogues: plain (bfloat16 or float32), or SwiGLU: the 256 columns are 128 gate features and
+// the 128 up features that belong to them (two TMA boxes from the two halves of the fused
+// weight), and silu(gate) * up is written, so the [M, 2I] intermediate never exists.
+//
+// Rows of x or W beyond the matrix and the tail of K are zero-filled by TMA; stores are
+// guarded.  Every wait is bounded by a clock limit: a block that gives up sets an error word
+// that the host can read, lets its copies land, frees its tensor memory and returns.
+//
+// The reference calls at::linear (cuBLAS) for all of these (pulsar-core/src/model/qwen3.cpp:82-84,
+// 114, 117-119) and two elementwise kernels for the gating.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+using namespace pb;
+typedef __nv_bfloat16 bf16;
+
+constexpr int kBM = 128;             // tokens per tile   (MMA M, TMEM lanes)
+constexpr int kBN = 256;             // features per tile (MMA N, TMEM columns)
+constexpr int kBK = 64;              // k per stage: one 128-byte swizzle atom of bfloat16
+constexpr int kStages = 4;
+constexpr int kThreads = 128;
+constexpr int kABytes = kBM * kBK * 2;           // 16 KB
+constexpr int kBBytes = kBN * kBK * 2;           // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr long long kWaitLimit = 4000000000LL;   // clock cycles (about two seconds)
+
+enum { kPlain = 0, kSwiGLU = 1 };
+
+__device__ unsigned int g_tc5_error = 0;          // 0 = fine; else 1 + the role that gave up
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitLimit) return false;
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle:
+// start address, leading offset 1 (unused by swizzled K-major layouts), 1024 bytes between
+// groups of 8 rows, descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, N >> 3, M >> 4.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(kInstrDesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void store32(bf16* dst, const float (&f)[32], int n_valid) {
+    if (n_valid >= 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 v = __floats2bfloat162_rn(f[i * 8 + 2 * j], f[i * 8 + 2 * j + 1]);
+                w[j] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {
+        for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = __float2bfloat16_rn(f[i]);
+    }
+}
+__device__ __forceinline__ void store32(float* dst, const float (&f)[32], int n_valid) {
+    if (n_valid >= 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+    } else {
+        for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = f[i];
+    }
+}
+
+// grid = (ceil(N_tile_space / tile), ceil(M / 128)).  Plain: W rows [n0, n0 + 256) of N.  SwiGLU: gate rows
+// [g0, g0 + 128) and up rows [inter + g0, ...): the output has `inter` columns and a tile covers 128 of them.
+template <int MODE, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    OutT* __restrict__ out, int M, int N, int K, int inter) {
+    extern __shared__ unsigned char smem_raw[];
+    // 128-byte swizzled tiles want 1024-byte alignment.
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);     // full[4], empty[4], accum
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.y * kBM;
+    const int n0 = blockIdx.x * (MODE == kSwiGLU ? kBN / 2 : kBN);      // first output column of the tile
+    const int k_tiles = (K + kBK - 1) / kBK;
+    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + kStages), accum_bar = smem_addr(bars + 2 * kStages);
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {            // one warp allocates the 256 accumulator columns and keeps the right to free them
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kBN));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer
+        for (int kt = 0; kt < k_tiles; ++kt) {
+            const int s = kt % kStages;
+            const uint32_t round = kt / kStages;
+            if (!mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicMax(&g_tc5_error, 2u); break; }
+            const uint32_t a_dst = smem_addr(smem + s * kStageBytes), b_dst = a_dst + kABytes;
+            mbar_expect_tx(full0 + 8 * s, kStageBytes);
+            tma_load_2d(a_dst, &map_x, full0 + 8 * s, kt * kBK, m0);
+            if (MODE == kSwiGLU) {
+                tma_load_2d(b_dst, &map_w, full0 + 8 * s, kt * kBK, n0);
+                tma_load_2d(b_dst + kBBytes / 2, &map_w, full0 + 8 * s, kt * kBK, inter + n0);
+            } else {
+                tma_load_2d(b_dst, &map_w, full0 + 8 * s, kt * kBK, n0);
+                tma_load_2d(b_dst + kBBytes / 2, &map_w, full0 + 8 * s, kt * kBK, n0 + kBN / 2);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        bool ok = true;
+        for (int kt = 0; kt < k_tiles && ok; ++kt) {
+            const int s = kt % kStages;
+            const uint32_t round = kt / kStages;
+            if (!mbar_wait(full0 + 8 * s, round & 1, abort_flag)) { *abort_flag = 1; atomicMax(&g_tc5_error, 3u); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_addr = smem_addr(smem + s * kStageBytes), b_addr = a_addr + kABytes;
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+                // 16 bfloat16 = 32 bytes further along the 128-byte row: +2 in units of 16 bytes
+                umma_bf16(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(empty0 + 8 * s);           // the stage is free once the tensor core has read it
+        }
+        if (ok) umma_commit(accum_bar);            // the accumulator is complete once all MMAs have retired
+    }
+    __syncwarp();
+
+    // ---------------- epilogue: every warp takes its 32 lanes of tensor memory
+    const bool done = mbar_wait(accum_bar, 0, abort_flag);
+    if (!done && tid == 0) { *abort_flag = 1; atomicMax(&g_tc5_error, 4u); }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (done) {
+        const int row = m0 + warp * 32 + lane;
+        const uint32_t lane_base = tmem_d + ((uint32_t)(warp * 32) << 16);
+        if (MODE == kSwiGLU) {
+#pragma unroll 1
+            for (int c = 0; c < kBN / 2; c += 32) {
+                uint32_t gv[32], uv[32];
+                tmem_ld32(lane_base + c, gv);
+                tmem_ld32(lane_base + kBN / 2 + c, uv);
+                float f[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float g = __uint_as_float(gv[i]), u = __uint_as_float(uv[i]);
+                    f[i] = g / (1.0f + expf(-g)) * u;
+                }
+                if (row < M && n0 + c < inter) store32(out + (size_t)row * inter + n0 + c, f, inter - (n0 + c));
+            }
+        } else {
+#pragma unroll 1
+            for (int c = 0; c < kBN; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(lane_base + c, v);
+                float f[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+                if (row < M && n0 + c < N) store32(out + (size_t)row * N + n0 + c, f, N - (n0 + c));
+            }
+        }
+    } else {
+        // a role gave up: give copies that are still in flight time to land before this block's memory is reused
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kBN));
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
+// Row-major [rows, K] bfloat16 matrix, boxes of 128 rows x 64 columns, 128-byte swizzle, zero fill outside.
+int make_map(CUtensorMap* map, const void* base, int rows, int K) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {kBK, 128};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS ? 0 : PB_ERR_BAD_SIZE;
+}
+
+template <int MODE, typename OutT>
+int launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int inter, dim3 grid, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t rc = cudaFuncSetAttribute(gemm_tcgen05_kernel<MODE, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (rc != cudaSuccess) return (int)rc;
+        configured = true;
+    }
+    gemm_tcgen05_kernel<MODE, OutT><<<grid, kThreads, kSmemBytes, stream>>>(mx, mw, (OutT*)out, M, N, K, inter);
+    return launch_status();
+}
+
+}  // namespace
+
+// 1 if pb_gemm_tcgen05 takes this problem: K a multiple of 8 (TMA strides are multiples of 16 bytes);
+// SwiGLU additionally needs the gate/up halves to split evenly.
+PB_EXPORT int pb_gemm_tcgen05_supported(int mode, int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0 || (K % 8)) return 0;
+    if (mode == kSwiGLU) return (N % 2 == 0) ? 1 : 0;
+    return mode == kPlain ? 1 : 0;
+}
+
+// The error word of the kernel's bounded waits (0 = no block ever gave up); reading it synchronises.
+PB_EXPORT int pb_gemm_tcgen05_error(void) {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc5_error, sizeof(v)) != cudaSuccess) return -1;
+    return (int)v;
+}
+
+// mode 0: out[M, N] = x W^T (out_dtype bfloat16 or float32).  mode 1: W = [gate rows; up rows], N = 2 * inter,
+// out[M, inter] = silu(x Wg^T) * (x Wu^T) in bfloat16.  x [M, K] and W [N, K] bfloat16, 16-byte aligned.
+PB_EXPORT int pb_gemm_tcgen05(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K,
+                              cudaStream_t stream) {
+    if (!pb_gemm_tcgen05_supported(mode, M, N, K)) return PB_ERR_BAD_SIZE;
+    if ((((uintptr_t)x | (uintptr_t)w) & 15) != 0) return PB_ERR_BAD_SIZE;
+    if (out_dtype != PB_BF16 && out_dtype != PB_F32) return PB_ERR_BAD_DTYPE;
+    CUtensorMap mx, mw;
+    int rc = make_map(&mx, x, M, K);
+    if (rc != 0) return rc;
+    rc = make_map(&mw, w, N, K);
+    if (rc != 0) return rc;
+    const int m_tiles = (M + kBM - 1) / kBM;
+    if (m_tiles > 65535) return PB_ERR_TOO_LARGE;
+    if (mode == kSwiGLU) {
+        if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
+        const int inter = N / 2;
+        dim3 grid((inter + kBN / 2 - 1) / (kBN / 2), m_tiles);
+        return launch<kSwiGLU, bf16>(mx, mw, out, M, N, K, inter, grid, stream);
+    }
+    dim3 grid((N + kBN - 1) / kBN, m_tiles);
+    if (out_dtype == PB_BF16) return launch<kPlain, bf16>(mx, mw, out, M, N, K, 0, grid, stream);
+    return launch<kPlain, float>(mx, mw, out, M, N, K, 0, grid, stream);
+}

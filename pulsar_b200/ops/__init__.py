@@ -37,6 +37,9 @@ _SIGNATURES = {
     "pb_prefill_tc_tile": [],
     "pb_gemm_skinny": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_gemm_skinny_supported": [_I, _I, _I, _I],
+    "pb_gemm_tcgen05": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
+    "pb_gemm_tcgen05_supported": [_I, _I, _I, _I],
+    "pb_gemm_tcgen05_error": [],
     "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _P, _P],
     "pb_argmax": [_P, _I, _I, _P, _P, _P],
@@ -222,6 +225,28 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: boo
     assert out.shape == (m, n // 2 if swiglu else n)
     check(fn("pb_gemm_skinny")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream()), "gemm_skinny")
     return True
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> bool:
+    """The tcgen05 / TMA product for many tokens (bfloat16 operands, float32 accumulation in
+    tensor memory).  ``swiglu`` as in ``gemm_skinny``.  Returns False, having done nothing,
+    when the sizes are not the kernel's (K must be a multiple of 8)."""
+    m, k = a.shape
+    n = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k:
+        return False
+    mode = 1 if swiglu else 0
+    if not fn("pb_gemm_tcgen05_supported")(mode, m, n, k):
+        return False
+    _cuda(a, w, out)
+    assert out.shape == (m, n // 2 if swiglu else n)
+    check(fn("pb_gemm_tcgen05")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream()), "gemm_tcgen05")
+    return True
+
+
+def gemm_tcgen05_error() -> int:
+    """0 unless a block of the tcgen05 product ever gave up a bounded wait (synchronises)."""
+    return int(fn("pb_gemm_tcgen05_error")())
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

@@ -204,6 +204,33 @@ def test_gemm_skinny_declines_other_sizes():
     assert float(out.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("m,n,k", [(17, 256, 64), (128, 512, 128), (100, 320, 72), (300, 1000, 4096), (2048, 1024, 512),
+                                   (129, 264, 200)])
+def test_gemm_tcgen05(m, n, k):
+    """The tcgen05 / TMA product against float64: tiles that hang over every edge (rows of x,
+    rows of W, the tail of K), float32 and bfloat16 outputs, the SwiGLU epilogue; one weight made
+    large so that a wrong swizzle or descriptor would show."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(14)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).bfloat16()
+    w[n // 3, (5 * k) // 7] = 3.0
+    w[n - 1, k - 1] = -2.0
+    ref = a.double() @ w.double().T
+    for dt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 1e-2)):
+        out = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
+        assert ops.gemm_tcgen05(dev(a), dev(w), out)
+        close(out, ref, tol, f"plain {dt}")
+    inter = n // 2
+    gate, up = ref[:, :inter], ref[:, inter:]
+    act = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops.gemm_tcgen05(dev(a), dev(w), act, swiglu=True)
+    close(act, gate * torch.sigmoid(gate) * up, 1e-2, "swiglu")
+    assert ops.gemm_tcgen05_error() == 0
+    assert not ops.gemm_tcgen05(dev(a[:, :k - 4].contiguous()), dev(w[:, :k - 4].contiguous()),
+                                torch.empty(m, n, dtype=torch.bfloat16, device="cuda"))      # K no multiple of 8
+
+
 def test_gemm_simt_mixed_dtypes():
     from pulsar_b200 import ops
     g = torch.Generator().manual_seed(5)
