@@ -2,16 +2,18 @@
 // cores: tcgen05.mma with the accumulator in tensor memory, operands brought into shared
 // memory by TMA (cp.async.bulk.tensor) and handed over through mbarriers.
 //
-// One block computes a tile of 128 tokens x 256 features.  Roles inside the block:
+// A persistent grid of one block per SM walks over tiles of 128 tokens x 256 features (token
+// tiles fastest, so that blocks running together share one tile of W).  Roles inside a block:
 //   warp 0, one thread   TMA producer: per 64-wide slice of K one [128 x 64] box of x and two
 //                        [128 x 64] boxes of W into a 4-stage ring (128-byte swizzle), each
 //                        stage guarded by a "full" barrier that counts the arriving bytes;
 //   warp 1, one thread   MMA issuer: four tcgen05.mma (M 128, N 256, K 16) per stage straight
-//                        from shared memory into 256 columns of tensor memory; a
-//                        tcgen05.commit releases the stage ("empty" barrier) when the tensor
-//                        core has read it, a last one announces the finished accumulator;
-//   all four warps       epilogue: tcgen05.ld of the warp's 32 lanes (= 32 tokens), 32 columns
-//                        at a time, then the rounding and the store.
+//                        from shared memory into one of two 256-column accumulators in tensor
+//                        memory; a tcgen05.commit releases the stage ("empty" barrier) when the
+//                        tensor core has read it, another announces the finished accumulator;
+//   warps 2-5            epilogue: tcgen05.ld of the warp's 32 lanes (= 32 tokens), 32 columns
+//                        at a time, rounding and store, while the MMA warp already fills the
+//                        other accumulator with the next tile.
 // Epilogues: plain (bfloat16 or float32), or SwiGLU: the 256 columns are 128 gate features and
 // the 128 up features that belong to them (two TMA boxes from the two halves of the fused
 // weight), and silu(gate) * up is written, so the [M, 2I] intermediate never exists.
@@ -35,7 +37,9 @@ constexpr int kBM = 128;             // tokens per tile   (MMA M, TMEM lanes)
 constexpr int kBN = 256;             // features per tile (MMA N, TMEM columns)
 constexpr int kBK = 64;              // k per stage: one 128-byte swizzle atom of bfloat16
 constexpr int kStages = 4;
-constexpr int kThreads = 128;
+constexpr int kThreads = 192;         // producer warp, MMA warp, four epilogue warps
+constexpr int kAccumulators = 2;
+constexpr int kTmemColumns = kAccumulators * kBN;   // all 512 columns of the SM's tensor memory
 constexpr int kABytes = kBM * kBK * 2;           // 16 KB
 constexpr int kBBytes = kBN * kBK * 2;           // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -53,6 +57,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -136,116 +143,140 @@ __device__ __forceinline__ void store32(float* dst, const float (&f)[32], int n_
     }
 }
 
-// grid = (ceil(N_tile_space / tile), ceil(M / 128)).  Plain: W rows [n0, n0 + 256) of N.  SwiGLU: gate rows
-// [g0, g0 + 128) and up rows [inter + g0, ...): the output has `inter` columns and a tile covers 128 of them.
+// Tiles are numbered with the token tile fastest; block b takes tiles b, b + gridDim.x, ...
+// Plain: W rows [n0, n0 + 256) of N.  SwiGLU: gate rows [g0, g0 + 128) and up rows [inter + g0, ...): the output
+// has `inter` columns and a tile covers 128 of them.
 template <int MODE, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    OutT* __restrict__ out, int M, int N, int K, int inter) {
+                    OutT* __restrict__ out, int M, int N, int K, int inter, int m_tiles, int n_tiles) {
     extern __shared__ unsigned char smem_raw[];
     // 128-byte swizzled tiles want 1024-byte alignment.
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);     // full[4], empty[4], accum
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);   // full[4], empty[4], acc_full[2], acc_empty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccumulators);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.y * kBM;
-    const int n0 = blockIdx.x * (MODE == kSwiGLU ? kBN / 2 : kBN);      // first output column of the tile
+    constexpr int kTileCols = (MODE == kSwiGLU) ? kBN / 2 : kBN;        // output columns of a tile
     const int k_tiles = (K + kBK - 1) / kBK;
-    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + kStages), accum_bar = smem_addr(bars + 2 * kStages);
+    const int total_tiles = m_tiles * n_tiles;
+    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + kStages);
+    const uint32_t acc_full0 = smem_addr(bars + 2 * kStages), acc_empty0 = smem_addr(bars + 2 * kStages + kAccumulators);
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(accum_bar, 1);
+        for (int a = 0; a < kAccumulators; ++a) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, 4); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {            // one warp allocates the 256 accumulator columns and keeps the right to free them
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kBN));
+    if (warp == 1) {            // one warp allocates the accumulator columns and keeps the right to free them
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemColumns));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0 && lane == 0) {
+    if (warp == 0) {
         // ---------------- TMA producer
-        for (int kt = 0; kt < k_tiles; ++kt) {
-            const int s = kt % kStages;
-            const uint32_t round = kt / kStages;
-            if (!mbar_wait(empty0 + 8 * s, (round & 1) ^ 1, abort_flag)) { *abort_flag = 1; atomicMax(&g_tc5_error, 2u); break; }
-            const uint32_t a_dst = smem_addr(smem + s * kStageBytes), b_dst = a_dst + kABytes;
-            mbar_expect_tx(full0 + 8 * s, kStageBytes);
-            tma_load_2d(a_dst, &map_x, full0 + 8 * s, kt * kBK, m0);
-            if (MODE == kSwiGLU) {
-                tma_load_2d(b_dst, &map_w, full0 + 8 * s, kt * kBK, n0);
-                tma_load_2d(b_dst + kBBytes / 2, &map_w, full0 + 8 * s, kt * kBK, inter + n0);
-            } else {
-                tma_load_2d(b_dst, &map_w, full0 + 8 * s, kt * kBK, n0);
-                tma_load_2d(b_dst + kBBytes / 2, &map_w, full0 + 8 * s, kt * kBK, n0 + kBN / 2);
-            }
-        }
-    } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer
-        bool ok = true;
-        for (int kt = 0; kt < k_tiles && ok; ++kt) {
-            const int s = kt % kStages;
-            const uint32_t round = kt / kStages;
-            if (!mbar_wait(full0 + 8 * s, round & 1, abort_flag)) { *abort_flag = 1; atomicMax(&g_tc5_error, 3u); ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_addr = smem_addr(smem + s * kStageBytes), b_addr = a_addr + kABytes;
-#pragma unroll
-            for (int k = 0; k < kBK / 16; ++k) {
-                // 16 bfloat16 = 32 bytes further along the 128-byte row: +2 in units of 16 bytes
-                umma_bf16(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
-            }
-            umma_commit(empty0 + 8 * s);           // the stage is free once the tensor core has read it
-        }
-        if (ok) umma_commit(accum_bar);            // the accumulator is complete once all MMAs have retired
-    }
-    __syncwarp();
-
-    // ---------------- epilogue: every warp takes its 32 lanes of tensor memory
-    const bool done = mbar_wait(accum_bar, 0, abort_flag);
-    if (!done && tid == 0) { *abort_flag = 1; atomicMax(&g_tc5_error, 4u); }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (done) {
-        const int row = m0 + warp * 32 + lane;
-        const uint32_t lane_base = tmem_d + ((uint32_t)(warp * 32) << 16);
-        if (MODE == kSwiGLU) {
-#pragma unroll 1
-            for (int c = 0; c < kBN / 2; c += 32) {
-                uint32_t gv[32], uv[32];
-                tmem_ld32(lane_base + c, gv);
-                tmem_ld32(lane_base + kBN / 2 + c, uv);
-                float f[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float g = __uint_as_float(gv[i]), u = __uint_as_float(uv[i]);
-                    f[i] = g / (1.0f + expf(-g)) * u;
+        if (lane == 0) {
+            uint32_t it = 0;                                  // k-slices issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * kTileCols;
+                bool ok = true;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(empty0 + 8 * s, ((it / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t a_dst = smem_addr(smem + s * kStageBytes), b_dst = a_dst + kABytes;
+                    mbar_expect_tx(full0 + 8 * s, kStageBytes);
+                    tma_load_2d(a_dst, &map_x, full0 + 8 * s, kt * kBK, m0);
+                    tma_load_2d(b_dst, &map_w, full0 + 8 * s, kt * kBK, n0);
+                    tma_load_2d(b_dst + kBBytes / 2, &map_w, full0 + 8 * s, kt * kBK, (MODE == kSwiGLU ? inter : kBN / 2) + n0);
                 }
-                if (row < M && n0 + c < inter) store32(out + (size_t)row * inter + n0 + c, f, inter - (n0 + c));
+                if (!ok) { *abort_flag = 1; atomicMax(&g_tc5_error, 2u); break; }
             }
-        } else {
-#pragma unroll 1
-            for (int c = 0; c < kBN; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(lane_base + c, v);
-                float f[32];
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0;
+            int j = 0;                                        // tiles done by this block
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
+                const int acc = j & 1;
+                bool ok = mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, abort_flag);   // the epilogue has drained it
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + acc * kBN;
+                for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait(full0 + 8 * s, (it / kStages) & 1, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_addr(smem + s * kStageBytes), b_addr = a_addr + kABytes;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
-                if (row < M && n0 + c < N) store32(out + (size_t)row * N + n0 + c, f, N - (n0 + c));
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        // 16 bfloat16 = 32 bytes further along the 128-byte row
+                        umma_bf16(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * s);          // the stage is free once the tensor core has read it
+                }
+                if (!ok) { *abort_flag = 1; atomicMax(&g_tc5_error, 3u); break; }
+                umma_commit(acc_full0 + 8 * acc);        // the accumulator is complete once its MMAs have retired
             }
         }
     } else {
+        // ---------------- epilogue: warp w reads the lanes of tensor memory it may touch (32 * (w % 4) ...)
+        const int quarter = warp & 3;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
+            const int acc = j & 1;
+            const int m0 = (tile % m_tiles) * kBM, n0 = (tile / m_tiles) * kTileCols;
+            if (!mbar_wait(acc_full0 + 8 * acc, (j >> 1) & 1, abort_flag)) {
+                if (lane == 0) { *abort_flag = 1; atomicMax(&g_tc5_error, 4u); }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t lane_base = tmem_base + acc * kBN + ((uint32_t)(quarter * 32) << 16);
+            if (MODE == kSwiGLU) {
+#pragma unroll 1
+                for (int c = 0; c < kBN / 2; c += 32) {
+                    uint32_t gv[32], uv[32];
+                    tmem_ld32(lane_base + c, gv);
+                    tmem_ld32(lane_base + kBN / 2 + c, uv);
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float g = __uint_as_float(gv[i]), u = __uint_as_float(uv[i]);
+                        f[i] = g / (1.0f + expf(-g)) * u;
+                    }
+                    if (row < M && n0 + c < inter) store32(out + (size_t)row * inter + n0 + c, f, inter - (n0 + c));
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < kBN; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_base + c, v);
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+                    if (row < M && n0 + c < N) store32(out + (size_t)row * N + n0 + c, f, N - (n0 + c));
+                }
+            }
+            // this warp has read its part of the accumulator: one of the four arrivals that free it
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);
+        }
+    }
+    __syncwarp();
+    if (*abort_flag) {
         // a role gave up: give copies that are still in flight time to land before this block's memory is reused
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kBN));
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
@@ -279,15 +310,27 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K) {
     return rc == CUDA_SUCCESS ? 0 : PB_ERR_BAD_SIZE;
 }
 
+int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) v = 0;
+        return v > 0 ? v : 148;
+    }();
+    return n;
+}
+
 template <int MODE, typename OutT>
-int launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int inter, dim3 grid, cudaStream_t stream) {
+int launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N, int K, int inter, int m_tiles, int n_tiles,
+           cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t rc = cudaFuncSetAttribute(gemm_tcgen05_kernel<MODE, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (rc != cudaSuccess) return (int)rc;
         configured = true;
     }
-    gemm_tcgen05_kernel<MODE, OutT><<<grid, kThreads, kSmemBytes, stream>>>(mx, mw, (OutT*)out, M, N, K, inter);
+    const long long tiles = (long long)m_tiles * n_tiles;
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());       // persistent: one block per SM
+    gemm_tcgen05_kernel<MODE, OutT><<<grid, kThreads, kSmemBytes, stream>>>(mx, mw, (OutT*)out, M, N, K, inter, m_tiles, n_tiles);
     return launch_status();
 }
 
@@ -321,14 +364,12 @@ PB_EXPORT int pb_gemm_tcgen05(int mode, int out_dtype, const void* x, const void
     rc = make_map(&mw, w, N, K);
     if (rc != 0) return rc;
     const int m_tiles = (M + kBM - 1) / kBM;
-    if (m_tiles > 65535) return PB_ERR_TOO_LARGE;
     if (mode == kSwiGLU) {
         if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
         const int inter = N / 2;
-        dim3 grid((inter + kBN / 2 - 1) / (kBN / 2), m_tiles);
-        return launch<kSwiGLU, bf16>(mx, mw, out, M, N, K, inter, grid, stream);
+        return launch<kSwiGLU, bf16>(mx, mw, out, M, N, K, inter, m_tiles, (inter + kBN / 2 - 1) / (kBN / 2), stream);
     }
-    dim3 grid((N + kBN - 1) / kBN, m_tiles);
-    if (out_dtype == PB_BF16) return launch<kPlain, bf16>(mx, mw, out, M, N, K, 0, grid, stream);
-    return launch<kPlain, float>(mx, mw, out, M, N, K, 0, grid, stream);
+    const int n_tiles = (N + kBN - 1) / kBN;
+    if (out_dtype == PB_BF16) return launch<kPlain, bf16>(mx, mw, out, M, N, K, 0, m_tiles, n_tiles, stream);
+    return launch<kPlain, float>(mx, mw, out, M, N, K, 0, m_tiles, n_tiles, stream);
 }

@@ -17,7 +17,13 @@ import torch
 
 from ..csrc.build import library
 
+import os
+
 F32, BF16 = 0, 1
+# Which product serves bfloat16 projections of more than 16 rows: "library" (cuBLAS through torch.mm,
+# as the reference does) or "tcgen05" (this library's TMA / tensor-memory kernel, with the SwiGLU
+# gating fused into the gate/up product).  Up to 16 rows always take the weight-streaming kernel.
+GEMM_BACKEND = os.environ.get("PULSAR_GEMM", "library")
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 _ERRORS = {-2: "unsupported dtype", -3: "unsupported size or argument", -4: "size exceeds the kernel's limit"}
 
@@ -263,6 +269,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError(f"linear: operand dtypes {a.dtype} / {w.dtype} must both be float32 or both bfloat16")
     if gemm_skinny(a, w, out):
         return
+    if GEMM_BACKEND == "tcgen05" and gemm_tcgen05(a, w, out):
+        return
     if out.dtype == torch.bfloat16:
         torch.mm(a, w.t(), out=out)
     else:
@@ -274,6 +282,8 @@ def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tenso
     bfloat16 rows: one kernel that never writes the [M, 2I] intermediate; otherwise the
     product followed by the gating kernel."""
     if gemm_skinny(a, w_gate_up, out, swiglu=True):
+        return
+    if GEMM_BACKEND == "tcgen05" and gemm_tcgen05(a, w_gate_up, out, swiglu=True):
         return
     gate_up = ctx.scratch("mlp.gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
     linear(a, w_gate_up, gate_up)

@@ -115,6 +115,22 @@ def test_mixed_with_page_reuse(folders, name, dtype):
     _compare(got, ref, dtype)
 
 
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_portions_with_the_tcgen05_products(folders, name, monkeypatch):
+    """The same replay with every projection of more than 16 rows on the tcgen05 / TMA kernel
+    (SwiGLU fused into the gate/up product) instead of the library product."""
+    from pulsar_b200 import ops
+    monkeypatch.setattr(ops, "GEMM_BACKEND", "tcgen05")
+    raw, seed, page = TINY[name]
+    rng = random.Random(seed + 40)
+    toks = helpers.random_tokens(rng, 150, raw["vocab_size"])
+    ref = _reference(folders[name], "bfloat16", {"a": toks})
+    got = _replay(folders[name], "bfloat16", helpers.trace_portions(toks, [70, 3, 40, 17, 20]), _round64(len(toks)), page)
+    assert len(got) == len(toks)
+    _compare(got, ref, "bfloat16")
+    assert ops.gemm_tcgen05_error() == 0
+
+
 def test_trace_run_program(folders, tmp_path):
     """The program itself: stdin records, done lines, .f32 files."""
     raw, seed, page = TINY["A"]
