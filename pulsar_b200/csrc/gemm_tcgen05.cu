@@ -28,6 +28,8 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
+
 namespace {
 
 using namespace pb;
@@ -141,6 +143,183 @@ __device__ __forceinline__ void store32(float* dst, const float (&f)[32], int n_
     } else {
         for (int i = 0; i < 32 && i < n_valid; ++i) dst[i] = f[i];
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same product with pairs of blocks (a cluster of two on the two SMs of a TPC) working on a
+// tile of 256 tokens x 256 features: tcgen05.mma.cta_group::2.  Each block of the pair loads its
+// own 128 token rows of x and one half of the tile's 256 weight rows (so W crosses L2 -> shared
+// memory once per pair, not once per block), and holds the accumulator of its own 128 tokens in
+// its own tensor memory.  The block of rank 0 issues the MMAs for both.  Barriers:
+//   full[s]       in rank 0, one arrival (rank 0's producer) that expects the bytes of both blocks;
+//                 the TMA loads of both blocks complete their bytes on it;
+//   empty[s]      in both blocks; released by a multicast tcgen05.commit when the MMAs have read it;
+//   acc_full[a]   in both blocks; multicast commit after the tile's last MMA;
+//   acc_empty[a]  in rank 0, eight arrivals: the four epilogue warps of each block.
+// Shared-memory addresses of the two blocks differ in one bit (0x01000000) of the cluster window;
+// clearing it turns a block's own barrier address into the address of rank 0's barrier.
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = kABytes + kBBytes / 2;          // per block: 128 rows of x, 128 rows of W
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
+constexpr uint32_t kPairInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)((2 * kBM) >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {            // `bar` is an address in the cluster window
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_rank0, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_rank0), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(kPairInstrDesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {               // arrives on `bar` in both blocks
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+
+template <int MODE, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                         OutT* __restrict__ out, int M, int N, int K, int inter, int m_tiles, int n_tiles) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);   // full, empty, acc_full, acc_empty
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 2 * kAccumulators);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    constexpr int kTileCols = (MODE == kSwiGLU) ? kBN / 2 : kBN;
+    const int k_tiles = (K + kBK - 1) / kBK;
+    const int total_tiles = m_tiles * n_tiles;                  // m_tiles counts tiles of 256 tokens here
+    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + kPairStages);
+    const uint32_t acc_full0 = smem_addr(bars + 2 * kPairStages), acc_empty0 = smem_addr(bars + 2 * kPairStages + kAccumulators);
+
+    if (tid == 0) {
+        for (int s = 0; s < kPairStages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < kAccumulators; ++a) { mbar_init(acc_full0 + 8 * a, 1); mbar_init(acc_empty0 + 8 * a, 8); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemColumns));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                       // the peer's barriers exist before anything arrives on them
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (in both blocks; bytes land on rank 0's full barrier)
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = pair; tile < total_tiles; tile += n_pairs) {
+                const int m0 = (tile % m_tiles) * (2 * kBM) + (int)rank * kBM, n0 = (tile / m_tiles) * kTileCols;
+                const int w_row = (MODE == kSwiGLU) ? (rank == 0 ? n0 : inter + n0) : n0 + (int)rank * (kBN / 2);
+                bool ok = true;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % kPairStages;
+                    if (!mbar_wait(empty0 + 8 * s, ((it / kPairStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t a_dst = smem_addr(smem + s * kPairStageBytes), b_dst = a_dst + kABytes;
+                    const uint32_t full_rank0 = (full0 + 8 * s) & kPeerBitMask;
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * kPairStageBytes);
+                    tma_load_2d_pair(a_dst, &map_x, full_rank0, kt * kBK, m0);
+                    tma_load_2d_pair(b_dst, &map_w, full_rank0, kt * kBK, w_row);
+                }
+                if (!ok) { *abort_flag = 1; atomicMax(&g_tc5_error, 2u); break; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: rank 0 only, for both blocks
+        if (lane == 0 && rank == 0) {
+            uint32_t it = 0;
+            int j = 0;
+            for (int tile = pair; tile < total_tiles; tile += n_pairs, ++j) {
+                const int acc = j & 1;
+                bool ok = mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, abort_flag);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + acc * kBN;
+                for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
+                    const int s = it % kPairStages;
+                    if (!mbar_wait(full0 + 8 * s, (it / kPairStages) & 1, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_addr(smem + s * kPairStageBytes), b_addr = a_addr + kABytes;
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k)
+                        umma_bf16_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(empty0 + 8 * s);
+                }
+                if (!ok) { *abort_flag = 1; atomicMax(&g_tc5_error, 3u); break; }
+                umma_commit_pair(acc_full0 + 8 * acc);
+            }
+        }
+    } else {
+        // ---------------- epilogue of this block's 128 tokens
+        const int quarter = warp & 3;
+        int j = 0;
+        for (int tile = pair; tile < total_tiles; tile += n_pairs, ++j) {
+            const int acc = j & 1;
+            const int m0 = (tile % m_tiles) * (2 * kBM) + (int)rank * kBM, n0 = (tile / m_tiles) * kTileCols;
+            if (!mbar_wait(acc_full0 + 8 * acc, (j >> 1) & 1, abort_flag)) {
+                if (lane == 0) { *abort_flag = 1; atomicMax(&g_tc5_error, 4u); }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t lane_base = tmem_base + acc * kBN + ((uint32_t)(quarter * 32) << 16);
+            if (MODE == kSwiGLU) {
+#pragma unroll 1
+                for (int c = 0; c < kBN / 2; c += 32) {
+                    uint32_t gv[32], uv[32];
+                    tmem_ld32(lane_base + c, gv);
+                    tmem_ld32(lane_base + kBN / 2 + c, uv);
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float g = __uint_as_float(gv[i]), u = __uint_as_float(uv[i]);
+                        f[i] = g / (1.0f + expf(-g)) * u;
+                    }
+                    if (row < M && n0 + c < inter) store32(out + (size_t)row * inter + n0 + c, f, inter - (n0 + c));
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < kBN; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_base + c, v);
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+                    if (row < M && n0 + c < N) store32(out + (size_t)row * N + n0 + c, f, N - (n0 + c));
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster((acc_empty0 + 8 * acc) & kPeerBitMask);
+        }
+    }
+    __syncwarp();
+    if (*abort_flag) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                       // neither block leaves while the other may still touch its memory
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
 }
 
 // Tiles are numbered with the token tile fastest; block b takes tiles b, b + gridDim.x, ...
@@ -310,6 +489,14 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K) {
     return rc == CUDA_SUCCESS ? 0 : PB_ERR_BAD_SIZE;
 }
 
+bool pair_enabled() {      // PULSAR_TCGEN05_PAIR=0 keeps every product on single blocks
+    static const bool on = [] {
+        const char* v = getenv("PULSAR_TCGEN05_PAIR");
+        return !(v && v[0] == '0' && v[1] == 0);
+    }();
+    return on;
+}
+
 int sm_count() {
     static int n = [] {
         int dev = 0, v = 0;
@@ -327,6 +514,31 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, int M, int N
         cudaError_t rc = cudaFuncSetAttribute(gemm_tcgen05_kernel<MODE, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (rc != cudaSuccess) return (int)rc;
         configured = true;
+    }
+    if (M > kBM && pair_enabled()) {
+        // more than one tile of tokens: pairs of blocks on tiles of 256 tokens
+        static bool pair_configured = false;
+        if (!pair_configured) {
+            cudaError_t rc = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<MODE, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+            if (rc != cudaSuccess) return (int)rc;
+            pair_configured = true;
+        }
+        const int pm_tiles = (M + 2 * kBM - 1) / (2 * kBM);
+        const long long ptiles = (long long)pm_tiles * n_tiles;
+        const int pairs = (int)(ptiles < sm_count() / 2 ? ptiles : sm_count() / 2);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * pairs);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kPairSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return (int)cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<MODE, OutT>, mx, mw, (OutT*)out, M, N, K, inter, pm_tiles, n_tiles);
     }
     const long long tiles = (long long)m_tiles * n_tiles;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());       // persistent: one block per SM

@@ -20,10 +20,14 @@ from ..csrc.build import library
 import os
 
 F32, BF16 = 0, 1
-# Which product serves bfloat16 projections of more than 16 rows: "library" (cuBLAS through torch.mm,
-# as the reference does) or "tcgen05" (this library's TMA / tensor-memory kernel, with the SwiGLU
-# gating fused into the gate/up product).  Up to 16 rows always take the weight-streaming kernel.
-GEMM_BACKEND = os.environ.get("PULSAR_GEMM", "library")
+# Which product serves bfloat16 projections of more than 16 rows:
+#   "auto"     the gate/up product with its SwiGLU gating fused runs on this library's tcgen05 / TMA
+#              kernel (faster than the library product plus a gating kernel); the plain projections
+#              take the library product (cuBLAS through torch.mm, as the reference does);
+#   "tcgen05"  every projection on the tcgen05 kernel;
+#   "library"  every projection on the library product, gating in a kernel of its own.
+# Up to 16 rows always take the weight-streaming kernel.
+GEMM_BACKEND = os.environ.get("PULSAR_GEMM", "auto")
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 _ERRORS = {-2: "unsupported dtype", -3: "unsupported size or argument", -4: "size exceeds the kernel's limit"}
 
@@ -283,7 +287,7 @@ def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tenso
     product followed by the gating kernel."""
     if gemm_skinny(a, w_gate_up, out, swiglu=True):
         return
-    if GEMM_BACKEND == "tcgen05" and gemm_tcgen05(a, w_gate_up, out, swiglu=True):
+    if GEMM_BACKEND in ("auto", "tcgen05") and gemm_tcgen05(a, w_gate_up, out, swiglu=True):
         return
     gate_up = ctx.scratch("mlp.gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
     linear(a, w_gate_up, gate_up)
