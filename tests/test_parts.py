@@ -317,3 +317,142 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     finally:
         MIXERS.unregister("toy_recurrent")
         ARCHITECTURES.unregister("ToyRecurrentForCausalLM")
+
+
+# ------------------------------------------------------------------ a toy routed feed-forward and another position encoding
+def _register_routed():
+    """A feed-forward that routes each token to one of several small experts (float32 router
+    logits, top-1) and a rotary encoding with linearly scaled positions, both defined here."""
+    from pulsar_b200.config import (ARCHITECTURES, FEED_FORWARDS, POSITIONS, BlockSpec, FeedForwardSpec, LayerCall,
+                                    MixerSpec, ModelSpec, NormSpec, PositionSpec)
+    from pulsar_b200.parts.base import FeedForward, PositionEncoding, WeightSpec
+
+    class ToyRouted(FeedForward):
+        def __init__(self, spec, prefix, dtype):
+            self.spec, self.prefix, self.dtype = spec, prefix, dtype
+            self.n_experts = spec.option("n_experts")
+
+        def weight_specs(self):
+            s, p = self.spec, self.prefix
+            out = [WeightSpec(p + "router.weight", (self.n_experts, s.hidden))]
+            for e in range(self.n_experts):
+                out += [WeightSpec(p + f"experts.{e}.up.weight", (s.intermediate, s.hidden)),
+                        WeightSpec(p + f"experts.{e}.down.weight", (s.hidden, s.intermediate))]
+            return out
+
+        def load(self, tensors):
+            p = self.prefix
+            self.router = tensors[p + "router.weight"].float()
+            self.up = [tensors[p + f"experts.{e}.up.weight"] for e in range(self.n_experts)]
+            self.down = [tensors[p + f"experts.{e}.down.weight"] for e in range(self.n_experts)]
+
+        def forward(self, ctx, h):
+            logits = h.float() @ self.router.T                        # router logits in float32
+            choice = logits.argmax(-1)
+            out = torch.zeros_like(h)
+            for e in range(self.n_experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    x = h[rows]
+                    out[rows] = (torch.relu(x @ self.up[e].T) @ self.down[e].T).to(h.dtype)
+            return out
+
+    class ScaledRope(PositionEncoding):
+        """cos/sin of (position / 4) * theta^(-2j/d): what the attention kernels consume, computed here."""
+
+        def __init__(self, spec):
+            self.spec = spec
+
+        def tables(self, ctx):
+            key = ("scaled", self.spec)
+            if key not in ctx.shared:
+                half = self.spec.rotary_dim // 2
+                inv = torch.tensor([self.spec.theta ** (-2.0 * j / self.spec.rotary_dim) for j in range(half)],
+                                   dtype=torch.float64, device=ctx.device)
+                ang = (ctx.positions.double() / 4.0)[:, None] * inv[None, :]
+                ctx.shared[key] = (torch.cos(ang).float().contiguous(), torch.sin(ang).float().contiguous())
+            return ctx.shared[key]
+
+    @dataclass(frozen=True)
+    class RoutedConfig:
+        vocab_size: int
+        hidden_size: int
+        n_experts: int
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["vocab_size"], raw["hidden_size"], raw["n_experts"])
+
+        def to_dict(self):
+            return dict(architectures=["ToyRoutedForCausalLM"], vocab_size=self.vocab_size, hidden_size=self.hidden_size,
+                        n_experts=self.n_experts)
+
+        def model_spec(self):
+            norm = NormSpec("rmsnorm", self.hidden_size, 1e-5)
+            mixer = MixerSpec("attention", self.hidden_size, n_heads=4, n_kv_heads=4, head_dim=16, scale=0.25,
+                              qk_norm_eps=None, position=PositionSpec("toy_scaled_rope", 16, 16, 100.0))
+            ffn = FeedForwardSpec("toy_routed", self.hidden_size, 40, extra=(("n_experts", self.n_experts),))
+            blocks = tuple(BlockSpec("prenorm", mixer, ffn, norm, norm, f"m.{i}.",
+                                     (("mixer", "attn."), ("feed_forward", "moe."), ("mixer_norm", "n1."),
+                                      ("feed_forward_norm", "n2."))) for i in range(2))
+            return ModelSpec("ToyRoutedForCausalLM", self.vocab_size, self.hidden_size, blocks,
+                             (LayerCall(0, 0), LayerCall(1, 1)), norm, embed_name="m.embed.weight",
+                             final_norm_name="m.norm.weight", head_name=None, init_std=0.3)
+
+    FEED_FORWARDS.register("toy_routed", ToyRouted, replace=True)
+    POSITIONS.register("toy_scaled_rope", ScaledRope, replace=True)
+    ARCHITECTURES.register("ToyRoutedForCausalLM", RoutedConfig.from_dict, replace=True)
+
+
+def _plain_routed(raw, w, tokens):
+    t = len(tokens)
+    x = w["m.embed.weight"][torch.tensor(tokens)]
+    inv = torch.tensor([100.0 ** (-2.0 * j / 16) for j in range(8)], dtype=torch.float64)
+    ang = (torch.arange(t).double() / 4.0)[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rot(z):
+        a, b = z[..., :8], z[..., 8:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+    for i in range(2):
+        p = f"m.{i}."
+        h = plain.rmsnorm(x, w[p + "n1.weight"], 1e-5)
+        q = (h @ w[p + "attn.q_proj.weight"].T).view(t, 4, 16)
+        k = (h @ w[p + "attn.k_proj.weight"].T).view(t, 4, 16)
+        v = (h @ w[p + "attn.v_proj.weight"].T).view(t, 4, 16)
+        x = x + plain.attention(rot(q), rot(k), v, 0.25).reshape(t, 64) @ w[p + "attn.o_proj.weight"].T
+        h2 = plain.rmsnorm(x, w[p + "n2.weight"], 1e-5)
+        choice = (h2 @ w[p + "moe.router.weight"].T).argmax(-1)
+        y = torch.zeros_like(h2)
+        for j in range(t):
+            e = int(choice[j])
+            y[j] = torch.relu(h2[j] @ w[p + f"moe.experts.{e}.up.weight"].T) @ w[p + f"moe.experts.{e}.down.weight"].T
+        x = x + y
+    return plain.rmsnorm(x, w["m.norm.weight"], 1e-5) @ w["m.embed.weight"].T
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
+    from pulsar_b200.config import ARCHITECTURES, FEED_FORWARDS, POSITIONS, config_from_dict
+    from pulsar_b200.replay import Replay
+    from pulsar_b200.weights import write_model_folder
+    _register_routed()
+    try:
+        raw = dict(architectures=["ToyRoutedForCausalLM"], vocab_size=83, hidden_size=64, n_experts=3)
+        folder = write_model_folder(config_from_dict(raw), str(tmp_path), 11)
+        _, weights = helpers.read_folder(folder)
+        w = {k: v.double() for k, v in weights.items()}
+        rng = random.Random(8)
+        toks = helpers.random_tokens(rng, 45, 83)
+        ref = _plain_routed(raw, w, toks)
+        rp = Replay(folder, "float32", 64, page_size=8)
+        trace = helpers.trace_portions(toks, [9, 2, 1, 14, 3])
+        rows = []
+        for rec in trace.records:
+            rows.append(rp.run_step(rec))
+        got = torch.cat(rows)
+        # a token whose two best router logits nearly tie could pick another expert in float32: none does here
+        assert helpers.rel_err(got, ref) < TOL["float32"]
+    finally:
+        FEED_FORWARDS.unregister("toy_routed")
+        POSITIONS.unregister("toy_scaled_rope")
+        ARCHITECTURES.unregister("ToyRoutedForCausalLM")
