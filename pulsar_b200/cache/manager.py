@@ -136,6 +136,7 @@ class CacheManager:
             if device is not None:
                 grp.pool = torch.zeros((len(grp.entries), 2, c, grp.need.n_kv_heads, self.page_size, grp.need.head_dim),
                                        dtype=dtype, device=device)
+        self._windowed = any(grp.need.window is not None for grp in self.groups)
         self.max_requests = int(max_requests)
         self._slots = PageAllocator(self.max_requests)
         self.state: Dict[int, torch.Tensor] = {}
@@ -170,6 +171,11 @@ class CacheManager:
 
     def length(self, rid: Hashable) -> int:
         return self._req(rid).length
+
+    def n_logical_pages(self, rid: Hashable) -> int:
+        """Logical pages the request's tables cover (the fewest over the groups)."""
+        r = self._req(rid)
+        return min(len(t) for t in r.tables) if r.tables else 0
 
     def state_slot(self, rid: Hashable) -> int:
         return self._req(rid).state_slot
@@ -213,6 +219,8 @@ class CacheManager:
 
     def release_passed(self, rid: Hashable) -> int:
         """Give back the pages of windowed groups that every future query has passed."""
+        if not self._windowed:
+            return 0
         r = self._req(rid)
         n = 0
         for g, grp in enumerate(self.groups):
@@ -230,6 +238,20 @@ class CacheManager:
         if n_new <= 0:
             raise CacheError("append needs n_new > 0")
         r = self._req(rid)
+        if not self._windowed:
+            # no group gives pages back early: one pass, check every group before taking anything
+            need = -(-(r.length + n_new) // self.page_size)
+            for g, grp in enumerate(self.groups):
+                if need - len(r.tables[g]) > grp.allocator.n_free:
+                    raise OutOfPages(f"request {rid!r}: {self.pages_to_append(rid, n_new)} new pages needed, "
+                                     f"{[x.allocator.n_free for x in self.groups]} free")
+            for g, grp in enumerate(self.groups):
+                table = r.tables[g]
+                for _ in range(need - len(table)):
+                    table.append(grp.allocator.take())
+            start = r.length
+            r.length += n_new
+            return start
         if not self.can_append(rid, n_new):
             raise OutOfPages(f"request {rid!r}: {self.pages_to_append(rid, n_new)} new pages needed, "
                              f"{[g.allocator.n_free for g in self.groups]} free")

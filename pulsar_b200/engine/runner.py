@@ -13,6 +13,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -56,6 +57,7 @@ class ModelRunner:
         self._staging_events: List[Optional[torch.cuda.Event]] = [None] * self.N_STAGING
         self._staging_next = 0
         self._index_buf: Optional[torch.Tensor] = None
+        self._views: Dict[tuple, list] = {}
         self.steps_run = 0
         # Decode steps (one token per request) are launch-bound: their kernel sequence is
         # captured once per (batch size, block-table width) and replayed.
@@ -118,14 +120,15 @@ class ModelRunner:
             if e.rid in seen:
                 raise StepError(f"request {e.rid!r} appears twice in one step")
             seen.add(e.rid)
-            if len(e.tokens) == 0:
+            n_tok = len(e.tokens)
+            if n_tok == 0:
                 raise StepError(f"request {e.rid!r}: a step entry needs at least one token")
-            for t in e.tokens:
-                if not (0 <= int(t) < self.vocab):
-                    raise StepError(f"request {e.rid!r}: token id {t} outside the vocabulary [0, {self.vocab})")
-            for w in e.want:
-                if not (0 <= int(w) < len(e.tokens)):
-                    raise StepError(f"request {e.rid!r}: wanted index {w} outside its {len(e.tokens)} tokens")
+            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
+                bad = [t for t in e.tokens if not (0 <= int(t) < self.vocab)][0]
+                raise StepError(f"request {e.rid!r}: token id {bad} outside the vocabulary [0, {self.vocab})")
+            if len(e.want) and (min(e.want) < 0 or max(e.want) >= n_tok):
+                bad = [w for w in e.want if not (0 <= int(w) < n_tok)][0]
+                raise StepError(f"request {e.rid!r}: wanted index {bad} outside its {n_tok} tokens")
         # Page check for the whole batch before any change.
         fresh = [e for e in entries if not cache.has(e.rid)]
         if len(fresh) > cache.n_free_slots():
@@ -156,14 +159,9 @@ class ModelRunner:
         n, s = sum(q_lens), len(entries)
         ctx = StepContext(self, n, s, host)
 
-        token_ids, positions, seq_of_token, logit_rows, cu_q = [], [], [], [], [0]
-        for i, e in enumerate(entries):
-            base = cu_q[-1]
-            token_ids.extend(int(t) for t in e.tokens)
-            positions.extend(range(starts[i], starts[i] + q_lens[i]))
-            seq_of_token.extend([i] * q_lens[i])
-            logit_rows.extend(base + int(w) for w in e.want)
-            cu_q.append(base + q_lens[i])
+        # Lengths of the step's index arrays, each padded to 16 bytes, in one pinned buffer:
+        # token_ids, positions, seq_of_token [N]; cu_q [S+1]; kv_len, state_slots [S]; logit_rows [R];
+        # per group slots [N] and the block table [S, width].
         widths = []
         for g in range(n_groups):
             w = max(1, max(len(cache.table(e.rid, g)) for e in entries))
@@ -171,47 +169,79 @@ class ModelRunner:
                 w = -(-w // self.TABLE_BUCKET) * self.TABLE_BUCKET
             widths.append(w)
         ctx.table_widths = tuple(widths)
-        segments: List[Tuple[str, List[int]]] = [
-            ("token_ids", token_ids), ("positions", positions), ("seq_of_token", seq_of_token), ("cu_q", cu_q),
-            ("kv_len", kv_lens), ("state_slots", state_slots), ("logit_rows", logit_rows)]
+        n_rows = sum(len(e.want) for e in entries)
+        lengths = [n, n, n, s + 1, s, s, n_rows]
         for g in range(n_groups):
-            slots: List[int] = []
-            table: List[int] = []
-            for i, e in enumerate(entries):
-                slots.extend(cache.slots(e.rid, g, starts[i], q_lens[i]))
-                row = cache.table(e.rid, g)
-                table.extend(row)
-                table.extend([-1] * (widths[g] - len(row)))
-            segments.append((f"slots{g}", slots))
-            segments.append((f"table{g}", table))
-        offsets, total = {}, 0
-        for name, values in segments:
-            offsets[name] = (total, len(values))
-            total += _align(max(len(values), 1))
+            lengths += [n, s * widths[g]]
+        offsets, total = [], 0
+        for ln in lengths:
+            offsets.append(total)
+            total += _align(max(ln, 1))
         stage = self._stage(total)
-        flat: List[int] = []
-        for name, values in segments:
-            flat.extend(values)
-            flat.extend([0] * (_align(max(len(values), 1)) - len(values)))
-        stage[:total] = torch.tensor(flat, dtype=torch.int32)
+        buf = stage.numpy()
+        o_tok, o_pos, o_seq, o_cu, o_kv, o_slot, o_rows = offsets[:7]
+        at, row_at = 0, 0
+        buf[o_cu] = 0
+        for i, e in enumerate(entries):
+            q = q_lens[i]
+            buf[o_tok + at:o_tok + at + q] = e.tokens
+            if q == 1:
+                buf[o_pos + at] = starts[i]
+            else:
+                buf[o_pos + at:o_pos + at + q] = np.arange(starts[i], starts[i] + q, dtype=np.int32)
+            buf[o_seq + at:o_seq + at + q] = i
+            for w in e.want:
+                buf[o_rows + row_at] = at + int(w)
+                row_at += 1
+            at += q
+            buf[o_cu + i + 1] = at
+        buf[o_kv:o_kv + s] = kv_lens
+        buf[o_slot:o_slot + s] = state_slots
+        ps = cache.page_size
+        for g in range(n_groups):
+            o_s, o_t = offsets[7 + 2 * g], offsets[8 + 2 * g]
+            w = widths[g]
+            buf[o_t:o_t + s * w] = -1
+            at = 0
+            for i, e in enumerate(entries):
+                row = cache.table(e.rid, g)
+                q = q_lens[i]
+                if q == 1:
+                    p = starts[i]
+                    page = row[p // ps]
+                    if page < 0:
+                        raise StepError(f"request {e.rid!r}: position {p} lies in a released page")
+                    buf[o_s + at] = page * ps + p % ps
+                else:
+                    buf[o_s + at:o_s + at + q] = cache.slots(e.rid, g, starts[i], q)
+                buf[o_t + i * w:o_t + i * w + len(row)] = row
+                at += q
         if self._index_buf is None or self._index_buf.numel() < total:
             self._index_buf = torch.empty(max(total, 4096) * 2, dtype=torch.int32, device=self.device)
             self.scratch_epoch += 1
+            self._views.clear()
         dev = self._index_buf
         dev[:total].copy_(stage[:total], non_blocking=True)
         self.h2d_bytes += total * 4
-        ev = torch.cuda.Event()
+        ev = self._staging_events[self._staging_slot]
+        if ev is None:
+            ev = self._staging_events[self._staging_slot] = torch.cuda.Event()
         ev.record()
-        self._staging_events[self._staging_slot] = ev
 
-        def seg(name: str) -> torch.Tensor:
-            o, ln = offsets[name]
-            return dev[o:o + ln]
-        ctx.token_ids, ctx.positions, ctx.seq_of_token = seg("token_ids"), seg("positions"), seg("seq_of_token")
-        ctx.cu_q, ctx.kv_len, ctx.state_slots, ctx.logit_rows = seg("cu_q"), seg("kv_len"), seg("state_slots"), seg("logit_rows")
+        # Views of the device buffer; steady decoding has the same layout every step, so they are kept.
+        key = (tuple(lengths), tuple(widths))
+        views = self._views.get(key)
+        if views is None:
+            if len(self._views) > 64:
+                self._views.clear()
+            views = [dev[o:o + ln] for o, ln in zip(offsets, lengths)]
+            for g in range(n_groups):
+                views[8 + 2 * g] = views[8 + 2 * g].view(s, widths[g])
+            self._views[key] = views
+        (ctx.token_ids, ctx.positions, ctx.seq_of_token, ctx.cu_q, ctx.kv_len, ctx.state_slots, ctx.logit_rows) = views[:7]
         for g in range(n_groups):
-            ctx.group_slots.append(seg(f"slots{g}"))
-            ctx.group_tables.append(seg(f"table{g}").view(s, widths[g]))
+            ctx.group_slots.append(views[7 + 2 * g])
+            ctx.group_tables.append(views[8 + 2 * g])
         return ctx
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:

@@ -136,16 +136,22 @@ class Scheduler:
         step function takes the pages when it runs the entries."""
         budget = self.max_chunk_size
         out: List[Scheduled] = []
+        planned: set = set()         # requests that already have an entry in this step
         planned_pages = 0            # pages this step's entries will take
+        ps = self.cache.page_size
+
+        def pages_for(rid, n_new) -> int:
+            if self.cache.has(rid) and self.cache.groups:
+                # pages to reach the new length, beyond the logical pages the request already has
+                return max(0, -(-(self.cache.length(rid) + n_new) // ps) - self.cache.n_logical_pages(rid))
+            return self._pages(n_new)
 
         def room_for(rid, n_new) -> bool:
-            need = max(self.cache.pages_to_append(rid, n_new)) if self.cache.has(rid) and self.cache.groups else self._pages(n_new)
-            return need <= self._free_pages() - planned_pages
+            return pages_for(rid, n_new) <= self._free_pages() - planned_pages
 
         def take(rid, n_new) -> None:
             nonlocal planned_pages
-            planned_pages += (max(self.cache.pages_to_append(rid, n_new)) if self.cache.has(rid) and self.cache.groups
-                              else self._pages(n_new))
+            planned_pages += pages_for(rid, n_new)
 
         def fits(rid) -> int:
             """Most new tokens of ``rid`` that the free pages allow in this step."""
@@ -165,8 +171,9 @@ class Scheduler:
                 was_planned = [e for e in out if e.rid == victim]
                 for e in was_planned:          # its planned entry (and pages) leave the step
                     out.remove(e)
+                    planned.discard(victim)
                     budget += len(e.tokens)
-                    planned_pages -= max(self.cache.pages_to_append(victim, len(e.tokens))) if self.cache.groups else 0
+                    planned_pages -= pages_for(victim, len(e.tokens))
                 self._preempt(victim)
                 if victim == rid:
                     break
@@ -174,6 +181,7 @@ class Scheduler:
                 continue
             s = self.seqs[rid]
             out.append(Scheduled(rid, [s.tokens[-1]], True))
+            planned.add(rid)
             take(rid, 1)
             budget -= 1
 
@@ -182,7 +190,7 @@ class Scheduler:
             s = self.seqs[rid]
             if budget <= 0:
                 break
-            if any(e.rid == rid for e in out) or s.pending == 0:
+            if rid in planned or s.pending == 0:
                 continue
             if s.pending == 1 and s.n_cached > 0:
                 continue                      # a decoder that found no budget above
@@ -190,6 +198,7 @@ class Scheduler:
             if n <= 0:
                 continue
             out.append(Scheduled(rid, s.tokens[s.n_cached:s.n_cached + n], n == s.pending))
+            planned.add(rid)
             take(rid, n)
             budget -= n
 
@@ -204,6 +213,7 @@ class Scheduler:
                 break                          # head of the queue waits; nobody overtakes it
             if not self.cache.has(rid) and self.cache.n_free_slots() - sum(1 for e in out if not self.cache.has(e.rid)) <= 0:
                 break
+            planned.add(rid)
             self.waiting.popleft()
             self.running.append(rid)
             s.admitted_at = self._admissions
