@@ -28,7 +28,8 @@ template <int D>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                  float* __restrict__ partial, const int* __restrict__ block_table, int table_stride,
-                 const int* __restrict__ kv_len, int Hq, int Hkv, int page_shift, float scale, int window, int n_splits) {
+                 const int* __restrict__ kv_len, int Hq, int Hkv, int page_shift, float scale, int window, int n_splits,
+                 bf16* __restrict__ out, unsigned int* __restrict__ tickets) {
     constexpr int kTileBytes = kTile * D * 2;
     constexpr int kKSteps = D / 16;                   // k-steps of Q K^T
     constexpr int kNTiles = D / 8;                    // n-tiles of P V
@@ -196,6 +197,10 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
     }
     __syncthreads();
     const int stride = D + 2;
+    // With `tickets` the kernel finishes the job itself: a single split writes the result at once; of
+    // several splits the one that draws the last ticket of its (sequence, kv head) merges all partials
+    // in split order (no block waits for another).  Without tickets a combine kernel follows.
+    const bool direct = tickets != nullptr && n_splits == 1;
     for (int i = tid; i < G * D; i += kWarps * 32) {
         const int h = i / D, d = i - h * D;
         float m_all = -INFINITY;
@@ -208,16 +213,53 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
             acc += o_s[(w * 16 + h) * D + d] * f;
             l_all += l_s[w * 16 + h] * f;
         }
-        float* dst = partial + (((size_t)s * Hq + (size_t)kvh * G + h) * n_splits + split) * stride;
-        dst[d] = acc;
-        if (d == 0) { dst[D] = m_all * kLn2; dst[D + 1] = l_all; }   // maximum back in natural-log units
+        if (direct) {
+            out[((size_t)s * Hq + (size_t)kvh * G + h) * D + d] = __float2bfloat16_rn(acc / l_all);
+        } else {
+            float* dst = partial + (((size_t)s * Hq + (size_t)kvh * G + h) * n_splits + split) * stride;
+            __stcg(dst + d, acc);
+            if (d == 0) { __stcg(dst + D, m_all * kLn2); __stcg(dst + D + 1, l_all); }   // maximum back in natural-log units
+        }
+    }
+    if (tickets == nullptr || direct) return;
+    __shared__ unsigned int ticket_s;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) ticket_s = atomicAdd(tickets + (size_t)s * Hkv + kvh, 1u);
+    __syncthreads();
+    if (ticket_s != (unsigned)(n_splits - 1)) return;
+    __threadfence();
+    float* w_s = reinterpret_cast<float*>(smem);            // [G][n_splits] weights, then [G] sums (the tiles are done with)
+    float* lsum_s = w_s + G * n_splits;
+    const float* base = partial + ((size_t)s * Hq + (size_t)kvh * G) * n_splits * stride;
+    if (tid < G) {
+        const float* hb = base + (size_t)tid * n_splits * stride;
+        float m_all = -INFINITY;
+        for (int i = 0; i < n_splits; ++i) m_all = fmaxf(m_all, __ldcg(hb + i * stride + D));
+        float l_all = 0.0f;
+        for (int i = 0; i < n_splits; ++i) {
+            const float m = __ldcg(hb + i * stride + D);
+            const float wgt = (m > -INFINITY) ? expf(m - m_all) : 0.0f;
+            w_s[tid * n_splits + i] = wgt;
+            l_all += __ldcg(hb + i * stride + D + 1) * wgt;
+        }
+        lsum_s[tid] = l_all;
+    }
+    if (tid == 0) tickets[(size_t)s * Hkv + kvh] = 0;        // ready for the next launch
+    __syncthreads();
+    for (int i = tid; i < G * D; i += kWarps * 32) {
+        const int h = i / D, d = i - h * D;
+        const float* hb = base + (size_t)h * n_splits * stride;
+        float acc = 0.0f;
+        for (int sp = 0; sp < n_splits; ++sp) acc = fmaf(__ldcg(hb + sp * stride + d), w_s[h * n_splits + sp], acc);
+        out[((size_t)s * Hq + (size_t)kvh * G + h) * D + d] = __float2bfloat16_rn(acc / lsum_s[h]);
     }
 }
 
 template <int D>
 int launch_tc(const void* q, const void* k_pool, const void* v_pool, float* partial, const int* block_table,
               int table_stride, const int* kv_len, int n_seqs, int Hq, int Hkv, int page_size, float scale, int window,
-              int n_splits, cudaStream_t stream) {
+              int n_splits, void* out, unsigned int* tickets, cudaStream_t stream) {
     const int page_shift = log2_exact(page_size);
     constexpr int pipeline = kStages * 2 * kTile * D * 2;
     constexpr int merge = (kWarps * 16 * D + 2 * kWarps * 16) * 4;
@@ -231,7 +273,7 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, float* part
     dim3 grid(n_splits, Hkv, n_seqs);
     decode_tc_kernel<D><<<grid, kWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, partial,
                                                              block_table, table_stride, kv_len, Hq, Hkv, page_shift, scale,
-                                                             window, n_splits);
+                                                             window, n_splits, (bf16*)out, tickets);
     return launch_status();
 }
 
@@ -258,10 +300,26 @@ PB_EXPORT int pb_paged_attention_decode_tc(int dtype, const void* q, const void*
     int rc;
     if (D == 64)
         rc = launch_tc<64>(q, k_pool, v_pool, partial, block_table, table_stride, kv_len, n_seqs, Hq, Hkv, page_size, scale,
-                           window, n_splits, stream);
+                           window, n_splits, nullptr, nullptr, stream);
     else
         rc = launch_tc<128>(q, k_pool, v_pool, partial, block_table, table_stride, kv_len, n_seqs, Hq, Hkv, page_size, scale,
-                            window, n_splits, stream);
+                            window, n_splits, nullptr, nullptr, stream);
     if (rc != 0) return rc;
     return pb_decode_combine(dtype, partial, out, n_seqs * Hq, D, n_splits, stream);
+}
+
+// The same in one launch: the split that finishes last merges.  `tickets`: n_seqs * Hkv 32-bit words that are
+// zero before the first launch (every launch leaves them zero); n_splits <= 64.
+PB_EXPORT int pb_paged_attention_decode_tc_fused(int dtype, const void* q, const void* k_pool, const void* v_pool, void* out,
+                                                 float* partial, unsigned int* tickets, const int* block_table,
+                                                 int table_stride, const int* kv_len, int n_seqs, int Hq, int Hkv, int D,
+                                                 int page_size, float scale, int window, int n_splits, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (!pb_decode_tc_supported(dtype, Hq, Hkv, D, page_size) || n_splits <= 0 || tickets == nullptr) return PB_ERR_BAD_SIZE;
+    if (Hkv > 65535 || n_seqs > 65535 || n_splits > 64) return PB_ERR_TOO_LARGE;
+    if (D == 64)
+        return launch_tc<64>(q, k_pool, v_pool, partial, block_table, table_stride, kv_len, n_seqs, Hq, Hkv, page_size, scale,
+                             window, n_splits, out, tickets, stream);
+    return launch_tc<128>(q, k_pool, v_pool, partial, block_table, table_stride, kv_len, n_seqs, Hq, Hkv, page_size, scale,
+                          window, n_splits, out, tickets, stream);
 }

@@ -358,15 +358,17 @@ def test_attention_decode_tensor_cores(hq, hkv, d, page, window, n_splits):
     case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype, spike=(9, 5, hq - 1))
     scale = 1.0 / math.sqrt(d)
     outs = []
-    for tc in (True, False):
+    for tc, fused in ((True, True), (True, False), (False, False), (True, True)):      # fused twice: its tickets reset themselves
         out = torch.full((len(lens_kv), hq, d), float("nan"), dtype=dtype, device="cuda")
         partial = torch.full((len(lens_kv) * hq * n_splits * (d + 2),), float("nan"), dtype=torch.float32, device="cuda")
         ops.paged_attention_decode(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, partial, dev(case["table"]),
-                                   dev(case["kv"]), scale, window, n_splits, tensor_cores=tc)
+                                   dev(case["kv"]), scale, window, n_splits, tensor_cores=tc, fused=fused)
         outs.append(out)
     ref = _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window)
-    close(outs[0], ref, TOL[dtype], "tensor cores vs plain")
-    close(outs[0], outs[1].double(), TOL[dtype], "tensor cores vs CUDA cores")
+    close(outs[0], ref, TOL[dtype], "tensor cores, merged in the kernel, vs plain")
+    close(outs[1], ref, TOL[dtype], "tensor cores + combine kernel vs plain")
+    close(outs[0], outs[2].double(), TOL[dtype], "tensor cores vs CUDA cores")
+    assert torch.equal(outs[0], outs[3]), "second fused launch on the same tickets"
 
 
 @pytest.mark.parametrize("hq,hkv,d,page", TC_SHAPES)
