@@ -179,3 +179,44 @@ def test_command_line(folders, tmp_path):
     assert out.returncode == 0, out.stderr
     got = json.loads(out.stdout.strip().splitlines()[-1])["outputs"]
     assert got == [plain.greedy_generate(cfg, weights, p, 5) for p in ([1, 2, 3, 4], [9, 8, 7])]
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_layer_sizes_of_qwen3_8b(tmp_path_factory, dtype):
+    """Two layers with the real layer sizes (hidden 4096, 32/8 heads of 128, intermediate 12288) and a
+    vocabulary that is no power of two: the sizes at which the weight-streaming, tcgen05 and
+    tensor-core attention kernels run in the benchmark.  A prompt in portions, then single tokens,
+    beside a second request; logits against the plain implementation (float32 on the CPU here)."""
+    from pulsar_b200.replay import Replay
+    raw = dict(helpers.TINY_B, vocab_size=15193, hidden_size=4096, intermediate_size=12288, num_hidden_layers=2,
+               num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=1000000.0, rms_norm_eps=1e-6,
+               max_window_layers=2, initializer_range=0.02)
+    folder = helpers.make_folder(tmp_path_factory.mktemp("layers8b"), raw, 5)
+    cfg, weights = helpers.read_folder(folder)
+    if dtype == "bfloat16":
+        weights = helpers.as_bf16_matrices(weights)
+    rng = random.Random(12)
+    reqs = {"a": helpers.random_tokens(rng, 150, 15193), "b": helpers.random_tokens(rng, 41, 15193)}
+    ref = {rid: plain.forward(cfg, weights, toks, torch.float32) for rid, toks in reqs.items()}
+    rp = Replay(folder, dtype, 256, page_size=16)
+    got = {}
+
+    def run(step, entries, end=()):
+        logits = rp.run_step({"step": step, "entries": [{"id": r, "tokens": t, "want": list(range(len(t)))} for r, t in entries],
+                              "end": list(end)})
+        i = 0
+        for r, t in entries:
+            for k in range(len(t)):
+                got[(r, fed[r] + k)] = logits[i]
+                i += 1
+            fed[r] += len(t)
+    fed = {"a": 0, "b": 0}
+    a, b = reqs["a"], reqs["b"]
+    run(0, [("a", a[:100])])
+    run(1, [("a", a[100:130]), ("b", b[:33])])                  # a later portion beside a first portion
+    for i in range(8):                                          # single tokens of both
+        run(2 + i, [("a", a[130 + i:131 + i]), ("b", b[33 + i:34 + i])])
+    run(10, [("a", a[138:150])], end=["a", "b"])
+    assert len(got) == 150 + 41
+    worst = max(helpers.rel_err(row, ref[rid][pos]) for (rid, pos), row in got.items())
+    assert worst < TOL[dtype], f"worst relative error {worst:.3e}"
