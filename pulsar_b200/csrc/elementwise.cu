@@ -251,6 +251,65 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
     }
 }
 
+// The common case (bfloat16, head size 128, the whole head rotates) with more work per warp:
+// a warp takes four heads of one token, issues all of its loads first, and shares the token's
+// cos/sin and the norm weights between the heads.  Lane l holds elements 2l, 2l+1 of both halves.
+constexpr int kRopeHeadsPerWarp = 4;
+__global__ void __launch_bounds__(128)
+qk_norm_rope_write_bf16_d128_kernel(const uint32_t* __restrict__ qkv, uint32_t* __restrict__ q_out,
+                                    uint32_t* __restrict__ k_pool, uint32_t* __restrict__ v_pool,
+                                    const int* __restrict__ slots, const float2* __restrict__ cos_t,
+                                    const float2* __restrict__ sin_t, const float2* __restrict__ q_weight,
+                                    const float2* __restrict__ k_weight, float eps, int Hq, int Hkv, int page_size) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    const int heads = Hq + 2 * Hkv;
+    const int head0 = (blockIdx.y * 4 + (threadIdx.x >> 5)) * kRopeHeadsPerWarp;
+    if (head0 >= heads) return;
+    uint32_t a[kRopeHeadsPerWarp], b[kRopeHeadsPerWarp];
+#pragma unroll
+    for (int h = 0; h < kRopeHeadsPerWarp; ++h) {
+        const int head = head0 + h;
+        if (head < heads) {
+            const uint32_t* src = qkv + ((size_t)t * heads + head) * 64;
+            a[h] = src[lane];
+            b[h] = src[lane + 32];
+        }
+    }
+    const float2 c = cos_t[(size_t)t * 32 + lane], sn = sin_t[(size_t)t * 32 + lane];
+    const int slot = Hkv ? slots[t] : -1;
+#pragma unroll
+    for (int h = 0; h < kRopeHeadsPerWarp; ++h) {
+        const int head = head0 + h;
+        if (head >= heads) break;
+        const bool is_q = head < Hq, is_k = !is_q && head < Hq + Hkv;
+        uint32_t* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)t * Hq + head) * 64;
+        } else {
+            if (slot < 0) continue;
+            const int kvh = is_k ? head - Hq : head - Hq - Hkv;
+            dst = (is_k ? k_pool : v_pool) + (((size_t)(slot / page_size) * Hkv + kvh) * page_size + slot % page_size) * 64;
+        }
+        if (!is_q && !is_k) {
+            dst[lane] = a[h];
+            dst[lane + 32] = b[h];
+            continue;
+        }
+        float a0 = __uint_as_float(a[h] << 16), a1 = __uint_as_float(a[h] & 0xffff0000u);
+        float b0 = __uint_as_float(b[h] << 16), b1 = __uint_as_float(b[h] & 0xffff0000u);
+        const float2* w = is_q ? q_weight : k_weight;
+        if (w) {
+            const float inv = rsqrtf(warp_sum(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1) / 128.0f + eps);
+            const float2 wa = w[lane], wb = w[lane + 32];
+            a0 *= inv * wa.x; a1 *= inv * wa.y; b0 *= inv * wb.x; b1 *= inv * wb.y;
+        }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
+        dst[lane] = *reinterpret_cast<const uint32_t*>(&lo);
+        dst[lane + 32] = *reinterpret_cast<const uint32_t*>(&hi);
+    }
+}
+
 // ---------------------------------------------------------------- SwiGLU gating
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z / (1 + exp(-z)); one rounding.
 template <typename T>
@@ -347,6 +406,13 @@ PB_EXPORT int pb_qk_norm_rope_write(int dtype, const void* qkv, void* q_out, voi
     if (rotary < 0 || rotary > D || (rotary & 1) || page_size <= 0) return PB_ERR_BAD_SIZE;
     const int heads = Hq + 2 * Hkv;
     const int warps = 4;
+    if (dtype == PB_BF16 && D == 128 && rotary == 128) {
+        dim3 fast_grid(n, (heads + warps * kRopeHeadsPerWarp - 1) / (warps * kRopeHeadsPerWarp));
+        qk_norm_rope_write_bf16_d128_kernel<<<fast_grid, warps * 32, 0, stream>>>((const uint32_t*)qkv, (uint32_t*)q_out,
+            (uint32_t*)k_pool, (uint32_t*)v_pool, slots, (const float2*)cos_t, (const float2*)sin_t, (const float2*)q_weight,
+            (const float2*)k_weight, eps, Hq, Hkv, page_size);
+        return launch_status();
+    }
     dim3 grid(n, (heads + warps - 1) / warps);
     if (dtype == PB_F32)
         qk_norm_rope_write_kernel<float><<<grid, warps * 32, 0, stream>>>((const float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool,
