@@ -154,7 +154,7 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int, sampl
     return seconds, launches, clocks
 
 
-def time_prefill(engine, tokens: int, reps: int = 3):
+def time_prefill(engine, tokens: int, reps: int = 7):
     import torch
     from pulsar_b200.engine.runner import StepEntry
     gen = torch.Generator().manual_seed(2)

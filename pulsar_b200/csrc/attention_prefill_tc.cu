@@ -30,6 +30,13 @@ constexpr int kBM = 64;          // query rows per block
 constexpr int kBN = 64;          // keys per pipeline stage
 constexpr int kWarps = 4;
 
+// 2^x by the special-function unit (ex2.approx: relative error 2^-22, 2^-inf = 0).
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int D>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
@@ -142,10 +149,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, c
 #pragma unroll
                 for (int n = 0; n < kBN / 8; ++n)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        sc[n][e] *= sl2;
-                        tmax[e >> 1] = fmaxf(tmax[e >> 1], sc[n][e]);
-                    }
+                    for (int e = 0; e < 4; ++e) tmax[e >> 1] = fmaxf(tmax[e >> 1], sc[n][e]);
             } else {
 #pragma unroll
                 for (int n = 0; n < kBN / 8; ++n)
@@ -154,26 +158,31 @@ prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, c
                         const int key = key0 + n * 8 + 2 * t + (e & 1);
                         const int pos = (e >> 1) ? pos1 : pos0;
                         const bool vis = key <= pos && (window <= 0 || key > pos - window);
-                        const float v = vis ? sc[n][e] * sl2 : -INFINITY;
+                        const float v = vis ? sc[n][e] : -INFINITY;
                         sc[n][e] = v;
                         tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
                     }
             }
-            float corr[2], m_safe[2];
+            // Running maxima are kept on the raw scores (sl2 > 0 keeps the order); the scale enters
+            // only the exponent: p = 2^(s * sl2 - m * sl2), one multiply-add and one ex2 per score.
+            float corr[2], neg_ms[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 float mx = tmax[r];
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 const float m_new = fmaxf(m_run[r], mx);
-                m_safe[r] = (m_new == -INFINITY) ? 0.0f : m_new;     // a row that has seen no key yet
-                corr[r] = exp2f(m_run[r] - m_safe[r]);
+                const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;     // a row that has seen no key yet
+                corr[r] = ex2((m_run[r] - m_safe) * sl2);
+                neg_ms[r] = -m_safe * sl2;
                 m_run[r] = m_new;
                 l_run[r] *= corr[r];
             }
+            if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {    // the maxima rarely move after the first tiles
 #pragma unroll
-            for (int i = 0; i < kNTiles; ++i) {
-                o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+                for (int i = 0; i < kNTiles; ++i) {
+                    o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+                }
             }
 #pragma unroll
             for (int kk = 0; kk < kBN / 16; ++kk) {
@@ -183,7 +192,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, c
                 for (int n = 0; n < 2; ++n)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        pv[n][e] = exp2f(sc[2 * kk + n][e] - m_safe[e >> 1]);
+                        pv[n][e] = ex2(fmaf(sc[2 * kk + n][e], sl2, neg_ms[e >> 1]));
                         l_run[e >> 1] += pv[n][e];
                     }
                 pa[0] = pack_bf16(pv[0][0], pv[0][1]);
