@@ -184,6 +184,7 @@ template <typename T>
 __global__ void decode_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int D, int n_splits) {
     __shared__ float w_s[64];                            // n_splits <= 64 (checked by the launchers)
     __shared__ float l_s;
+    pdl_wait();
     const size_t row = blockIdx.x;                       // s * Hq + h
     const int stride = D + 2;
     const float* base = partial + row * n_splits * stride;
@@ -203,6 +204,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ partial, T* __re
         if (threadIdx.x == 0) l_s = l_part;
     }
     __syncthreads();
+    pdl_trigger();
     const float inv = 1.0f / l_s;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float o = 0.0f;
@@ -325,8 +327,7 @@ PB_EXPORT int pb_decode_combine(int dtype, const float* partial, void* out, int 
                                 cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (n_splits <= 0 || n_splits > 64) return PB_ERR_TOO_LARGE;
-    if (dtype == PB_F32) decode_combine_kernel<float><<<rows, 128, 0, stream>>>(partial, (float*)out, D, n_splits);
-    else if (dtype == PB_BF16) decode_combine_kernel<__nv_bfloat16><<<rows, 128, 0, stream>>>(partial, (__nv_bfloat16*)out, D, n_splits);
-    else return PB_ERR_BAD_DTYPE;
-    return launch_status();
+    if (dtype == PB_F32) return launch_pdl(decode_combine_kernel<float>, rows, 128, 0, stream, partial, (float*)out, D, n_splits);
+    if (dtype == PB_BF16) return launch_pdl(decode_combine_kernel<__nv_bfloat16>, rows, 128, 0, stream, partial, (__nv_bfloat16*)out, D, n_splits);
+    return PB_ERR_BAD_DTYPE;
 }

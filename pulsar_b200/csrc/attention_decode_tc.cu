@@ -37,6 +37,7 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
     // [stage][K tile | V tile]; after the main loop the same memory holds the warps' partial results
     const uint32_t smem_base = smem_u32(smem);
 
+    pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -173,6 +174,7 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
     }
     cp_async_wait<0>();
     __syncthreads();
+    pdl_trigger();
 
     // Merge the four warps (each saw a quarter of the keys) and write the split's partial.
 #pragma unroll
@@ -271,10 +273,8 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, float* part
         configured = true;
     }
     dim3 grid(n_splits, Hkv, n_seqs);
-    decode_tc_kernel<D><<<grid, kWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, partial,
-                                                             block_table, table_stride, kv_len, Hq, Hkv, page_shift, scale,
-                                                             window, n_splits, (bf16*)out, tickets);
-    return launch_status();
+    return launch_pdl(decode_tc_kernel<D>, grid, kWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
+                      partial, block_table, table_stride, kv_len, Hq, Hkv, page_shift, scale, window, n_splits, (bf16*)out, tickets);
 }
 
 }  // namespace

@@ -57,4 +57,32 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 inline int launch_status() { return (int)cudaPeekAtLastError(); }
 
+// Programmatic dependent launch.  A kernel launched through launch_pdl may be brought onto the
+// SMs while the kernel before it on the stream is finishing: as soon as every block of that
+// kernel has called pdl_trigger (or exited).  It must call pdl_wait before it touches anything
+// an earlier kernel writes (or reads and later overwrites); pdl_wait returns once the preceding
+// kernel has completed and its writes are visible.  Every kernel of the chain waits first thing,
+// so completion is transitive; kernels trigger late, after their main loop, so that the next
+// kernel's launch overlaps only this kernel's tail.  Both calls do nothing in a kernel that was
+// launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();      // PULSAR_PDL=0 launches every kernel the ordinary way
+
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 }  // namespace pb

@@ -15,6 +15,19 @@
 //   embedding      pulsar-core/src/model/paged_forward.cpp:89 (index_select)
 #include "common.cuh"
 
+#include <cstdlib>
+#include <cstring>
+
+namespace pb {
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("PULSAR_PDL");
+        return !(v && std::strcmp(v, "0") == 0);
+    }();
+    return on;
+}
+}  // namespace pb
+
 namespace {
 
 using namespace pb;
@@ -88,6 +101,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
                                        const float* __restrict__ weight, T* __restrict__ out,
                                        const int* __restrict__ rows, int width, float eps, int write_back) {
     __shared__ float scratch[32];
+    pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* res = residual + (size_t)src * width;
@@ -110,6 +124,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
             for (int e = 0; e < 4; ++e) local += x[v][e] * x[v][e];
         }
     }
+    pdl_trigger();
     const float total = block_sum(local, scratch);
     const float inv = rsqrtf(total / (float)width + eps);
     T* o = out + (size_t)r * width;
@@ -261,6 +276,7 @@ qk_norm_rope_write_bf16_d128_kernel(const uint32_t* __restrict__ qkv, uint32_t* 
                                     const int* __restrict__ slots, const float2* __restrict__ cos_t,
                                     const float2* __restrict__ sin_t, const float2* __restrict__ q_weight,
                                     const float2* __restrict__ k_weight, float eps, int Hq, int Hkv, int page_size) {
+    pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31;
     const int heads = Hq + 2 * Hkv;
     const int head0 = (blockIdx.y * 4 + (threadIdx.x >> 5)) * kRopeHeadsPerWarp;
@@ -277,6 +293,7 @@ qk_norm_rope_write_bf16_d128_kernel(const uint32_t* __restrict__ qkv, uint32_t* 
     }
     const float2 c = cos_t[(size_t)t * 32 + lane], sn = sin_t[(size_t)t * 32 + lane];
     const int slot = Hkv ? slots[t] : -1;
+    pdl_trigger();
 #pragma unroll
     for (int h = 0; h < kRopeHeadsPerWarp; ++h) {
         const int head = head0 + h;
@@ -373,13 +390,11 @@ PB_EXPORT int pb_add_rmsnorm(int dtype, float* residual, const void* delta, cons
         const int vpt = vecs <= 1024 ? 1 : 2;
         int threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;
         if (dtype == PB_F32) {
-            if (vpt == 1) add_rmsnorm_vec_kernel<float, 1><<<n_out, threads, 0, stream>>>(residual, (const float*)delta, weight, (float*)out, rows, width, eps, write_back);
-            else add_rmsnorm_vec_kernel<float, 2><<<n_out, threads, 0, stream>>>(residual, (const float*)delta, weight, (float*)out, rows, width, eps, write_back);
-        } else {
-            if (vpt == 1) add_rmsnorm_vec_kernel<__nv_bfloat16, 1><<<n_out, threads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, width, eps, write_back);
-            else add_rmsnorm_vec_kernel<__nv_bfloat16, 2><<<n_out, threads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, width, eps, write_back);
+            if (vpt == 1) return launch_pdl(add_rmsnorm_vec_kernel<float, 1>, n_out, threads, 0, stream, residual, (const float*)delta, weight, (float*)out, rows, width, eps, write_back);
+            return launch_pdl(add_rmsnorm_vec_kernel<float, 2>, n_out, threads, 0, stream, residual, (const float*)delta, weight, (float*)out, rows, width, eps, write_back);
         }
-        return launch_status();
+        if (vpt == 1) return launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16, 1>, n_out, threads, 0, stream, residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, width, eps, write_back);
+        return launch_pdl(add_rmsnorm_vec_kernel<__nv_bfloat16, 2>, n_out, threads, 0, stream, residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, width, eps, write_back);
     }
     const int b = block_for(width);
     if (dtype == PB_F32)
@@ -408,10 +423,9 @@ PB_EXPORT int pb_qk_norm_rope_write(int dtype, const void* qkv, void* q_out, voi
     const int warps = 4;
     if (dtype == PB_BF16 && D == 128 && rotary == 128) {
         dim3 fast_grid(n, (heads + warps * kRopeHeadsPerWarp - 1) / (warps * kRopeHeadsPerWarp));
-        qk_norm_rope_write_bf16_d128_kernel<<<fast_grid, warps * 32, 0, stream>>>((const uint32_t*)qkv, (uint32_t*)q_out,
+        return launch_pdl(qk_norm_rope_write_bf16_d128_kernel, fast_grid, warps * 32, 0, stream, (const uint32_t*)qkv, (uint32_t*)q_out,
             (uint32_t*)k_pool, (uint32_t*)v_pool, slots, (const float2*)cos_t, (const float2*)sin_t, (const float2*)q_weight,
             (const float2*)k_weight, eps, Hq, Hkv, page_size);
-        return launch_status();
     }
     dim3 grid(n, (heads + warps - 1) / warps);
     if (dtype == PB_F32)

@@ -66,12 +66,26 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT*
     const int blocks = K / kBlockK;
     const int kb_begin = (int)((long long)blocks * warp / kWarps), kb_end = (int)((long long)blocks * (warp + 1) / kWarps);
     int kb = kb_begin;
-    for (; kb + kUnroll <= kb_end; kb += kUnroll) {
-        uint4 wa[kUnroll], wb[kUnroll], xv[kUnroll][NT];
+    // The weights depend on no earlier kernel: the first batch of loads is issued before this kernel
+    // waits for the one that produces x (it may have been brought onto the SM while that one finishes).
+    uint4 wa[kUnroll], wb[kUnroll];
+    const bool first = kb + kUnroll <= kb_end;
+    if (first) {
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             wa[u] = load_stream(wa_p + (size_t)(kb + u) * kBlockK);
             wb[u] = load_stream(wb_p + (size_t)(kb + u) * kBlockK);
+        }
+    }
+    pdl_wait();
+    for (bool loaded = first; kb + kUnroll <= kb_end; kb += kUnroll, loaded = false) {
+        uint4 xv[kUnroll][NT];
+        if (!loaded) {
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                wa[u] = load_stream(wa_p + (size_t)(kb + u) * kBlockK);
+                wb[u] = load_stream(wb_p + (size_t)(kb + u) * kBlockK);
+            }
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u)
@@ -100,6 +114,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT*
             mma_bf16(c[n], a2, xv.z, xv.w);
         }
     }
+    pdl_trigger();
     // accumulator (row g | g+8, token n*8 + 2t | +1) -> shared memory, then the warps are added in order
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
@@ -135,13 +150,11 @@ int launch(int mode, int out_dtype, const void* x, const void* w, void* out, int
     if (mode == kSwiGLU) {
         const int inter = N / 2;
         if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
-        gemm_skinny_kernel<NT, kSwiGLU, bf16><<<inter / 8, kWarps * 32, 0, stream>>>(xp, wp, (bf16*)out, M, N, K, inter);
-    } else if (out_dtype == PB_BF16) {
-        gemm_skinny_kernel<NT, kPlain, bf16><<<N / kRows, kWarps * 32, 0, stream>>>(xp, wp, (bf16*)out, M, N, K, 0);
-    } else {
-        gemm_skinny_kernel<NT, kPlain, float><<<N / kRows, kWarps * 32, 0, stream>>>(xp, wp, (float*)out, M, N, K, 0);
+        return launch_pdl(gemm_skinny_kernel<NT, kSwiGLU, bf16>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
     }
-    return launch_status();
+    if (out_dtype == PB_BF16)
+        return launch_pdl(gemm_skinny_kernel<NT, kPlain, bf16>, N / kRows, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, 0);
+    return launch_pdl(gemm_skinny_kernel<NT, kPlain, float>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
 }
 
 }  // namespace
