@@ -37,7 +37,6 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
     // [stage][K tile | V tile]; after the main loop the same memory holds the warps' partial results
     const uint32_t smem_base = smem_u32(smem);
 
-    pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -53,6 +52,22 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
     const int tile0 = begin / kTile;                  // tiles are aligned to absolute key indices (whole pages)
     const int n_tiles = begin < end ? (end - 1) / kTile - tile0 + 1 : 0;
 
+    auto issue_tile = [&](int tile_index, int stage) {
+        const uint32_t k_dst = smem_base + stage * 2 * kTileBytes;
+        load_kv_tile<D, kWarps * 32>(k_dst, k_dst + kTileBytes, k_pool, v_pool, table, (tile0 + tile_index) * kTile, begin,
+                                     end - 1, kvh, Hkv, page_shift, tid);
+    };
+
+    // The kernel before this one writes only the newest key and value (position p).  Tiles that lie wholly
+    // below p are requested before waiting for it; kv_len and the block table come from the host.
+    bool early[kStages - 1];
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) {
+        early[i] = i < n_tiles && (tile0 + i) * kTile + kTile - 1 < p;
+        if (early[i]) { issue_tile(i, i); cp_async_commit(); }
+    }
+    pdl_wait();
+
     // Q fragments: rows = query heads of the group (zero beyond G), straight from global memory.
     uint32_t qa[kKSteps][4];
     {
@@ -67,12 +82,6 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
         }
     }
 
-    auto issue_tile = [&](int tile_index, int stage) {
-        const uint32_t k_dst = smem_base + stage * 2 * kTileBytes;
-        load_kv_tile<D, kWarps * 32>(k_dst, k_dst + kTileBytes, k_pool, v_pool, table, (tile0 + tile_index) * kTile, begin,
-                                     end - 1, kvh, Hkv, page_shift, tid);
-    };
-
     float o[kNTiles][4];
 #pragma unroll
     for (int i = 0; i < kNTiles; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
@@ -81,6 +90,7 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
 
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i) {
+        if (early[i]) continue;                       // requested above (early tiles come first, so the order of groups holds)
         if (i < n_tiles) issue_tile(i, i);
         cp_async_commit();
     }

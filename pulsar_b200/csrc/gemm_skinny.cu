@@ -27,7 +27,6 @@ using namespace pb;
 constexpr int kWarps = 8;
 constexpr int kRows = 16;
 constexpr int kBlockK = 32;      // k per two MMAs: 4 threads x 8 contiguous elements
-constexpr int kUnroll = 8;
 
 __device__ __forceinline__ uint4 load_stream(const void* p) {      // weights: read once, keep them out of L1
     uint4 v;
@@ -40,7 +39,7 @@ enum { kPlain = 0, kSwiGLU = 1 };
 
 // NT: n-tiles of 8 tokens.  Mode kSwiGLU: rows r of the block are gate rows 8*b + r (r < 8) and up rows
 // inter + 8*b + (r - 8); the output has `inter` columns.
-template <int NT, int MODE, typename OutT>
+template <int NT, int MODE, typename OutT, int kUnroll>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
                    int inter) {
@@ -143,18 +142,28 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT*
     }
 }
 
-template <int NT>
-int launch(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
+// kUnroll: k-blocks whose weight loads a thread keeps in flight.  Few blocks on the machine (the
+// per-layer projections): 8, which costs 128 registers; thousands of blocks (gate/up, lm_head): 4, so
+// that more blocks are resident per SM.
+template <int NT, int kUnroll>
+int launch_u(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)w;
     if (mode == kSwiGLU) {
         const int inter = N / 2;
         if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
-        return launch_pdl(gemm_skinny_kernel<NT, kSwiGLU, bf16>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
+        return launch_pdl(gemm_skinny_kernel<NT, kSwiGLU, bf16, kUnroll>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
     }
     if (out_dtype == PB_BF16)
-        return launch_pdl(gemm_skinny_kernel<NT, kPlain, bf16>, N / kRows, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, 0);
-    return launch_pdl(gemm_skinny_kernel<NT, kPlain, float>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
+        return launch_pdl(gemm_skinny_kernel<NT, kPlain, bf16, kUnroll>, N / kRows, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, 0);
+    return launch_pdl(gemm_skinny_kernel<NT, kPlain, float, kUnroll>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
+}
+
+template <int NT>
+int launch(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
+    const int tiles = (mode == kSwiGLU) ? N / 2 / 8 : N / kRows;
+    if (tiles >= 1024) return launch_u<NT, 4>(mode, out_dtype, x, w, out, M, N, K, stream);
+    return launch_u<NT, 8>(mode, out_dtype, x, w, out, M, N, K, stream);
 }
 
 }  // namespace
