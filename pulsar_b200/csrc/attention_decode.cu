@@ -184,6 +184,7 @@ template <typename T>
 __global__ void decode_combine_kernel(const float* __restrict__ partial, T* __restrict__ out, int D, int n_splits) {
     __shared__ float w_s[64];                            // n_splits <= 64 (checked by the launchers)
     __shared__ float l_s;
+    pdl_trigger();
     pdl_wait();
     const size_t row = blockIdx.x;                       // s * Hq + h
     const int stride = D + 2;
@@ -204,7 +205,6 @@ __global__ void decode_combine_kernel(const float* __restrict__ partial, T* __re
         if (threadIdx.x == 0) l_s = l_part;
     }
     __syncthreads();
-    pdl_trigger();
     const float inv = 1.0f / l_s;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float o = 0.0f;

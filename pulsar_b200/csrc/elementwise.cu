@@ -101,6 +101,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
                                        const float* __restrict__ weight, T* __restrict__ out,
                                        const int* __restrict__ rows, int width, float eps, int write_back) {
     __shared__ float scratch[32];
+    pdl_trigger();      // a short kernel: let the next one (a weight-streaming product) start fetching its weights now
     pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -124,7 +125,6 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
             for (int e = 0; e < 4; ++e) local += x[v][e] * x[v][e];
         }
     }
-    pdl_trigger();
     const float total = block_sum(local, scratch);
     const float inv = rsqrtf(total / (float)width + eps);
     T* o = out + (size_t)r * width;
@@ -276,6 +276,7 @@ qk_norm_rope_write_bf16_d128_kernel(const uint32_t* __restrict__ qkv, uint32_t* 
                                     const int* __restrict__ slots, const float2* __restrict__ cos_t,
                                     const float2* __restrict__ sin_t, const float2* __restrict__ q_weight,
                                     const float2* __restrict__ k_weight, float eps, int Hq, int Hkv, int page_size) {
+    pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31;
     const int heads = Hq + 2 * Hkv;
@@ -293,7 +294,6 @@ qk_norm_rope_write_bf16_d128_kernel(const uint32_t* __restrict__ qkv, uint32_t* 
     }
     const float2 c = cos_t[(size_t)t * 32 + lane], sn = sin_t[(size_t)t * 32 + lane];
     const int slot = Hkv ? slots[t] : -1;
-    pdl_trigger();
 #pragma unroll
     for (int h = 0; h < kRopeHeadsPerWarp; ++h) {
         const int head = head0 + h;
