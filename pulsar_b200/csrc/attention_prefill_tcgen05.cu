@@ -1,0 +1,443 @@
+// Paged attention for prompt portions on the fifth-generation tensor cores: causal, ragged
+// batch, optional window, grouped heads, bfloat16 pages, head size 128.
+//
+// One block per (tile of 128 query tokens of one sequence, query head); two blocks share an
+// SM (96 KB of shared memory and 256 of the 512 tensor-memory columns each), so that the tensor
+// core works for one while the other computes its softmax.  Roles inside a block:
+//   warps 0-3   softmax: thread r owns query row r (tensor-memory lane r).  It reads its row of
+//               S = Q K^T from tensor memory (tcgen05.ld), keeps the running maximum and sum in
+//               float32, writes P = 2^(s*c - m*c) rounded to bfloat16 back over the first half
+//               of S's columns (tcgen05.st), and at the end normalises and stores its row of O;
+//   warp 4      TMA producer: the query tile once, then per tile of 128 keys the pages that the
+//               block table names, each as two boxes of [page x 64] into 128-byte-swizzled
+//               tiles (one lane per box);
+//   warp 5      one thread issues the MMAs: S = Q K^T (operands in shared memory, eight
+//               tcgen05.mma of K 16), then O += P V with P read from tensor memory and V as an
+//               MN-major operand straight from the page layout (keys along K).
+// K and V have one buffer each: the load of K[j+1] starts when S[j] has been computed and runs
+// during softmax j; the load of V[j+1] starts when O += P[j] V[j] has retired.
+//
+// The running maximum is only moved when a row's new maximum exceeds it by more than 2^8 in the
+// exponent: P then stays below 256, which bfloat16 holds with the same relative rounding, and O
+// (in tensor memory) is rescaled only then.  Sum and output use the same maximum, so the result
+// is the exact softmax up to rounding.
+//
+// Keys above the diagonal, below the window or beyond the sequence are masked to -inf before the
+// maximum is taken; pages that hold no visible key are not loaded.  What such a page's place in
+// the V buffer holds must be finite (0 * NaN would poison the row): the buffer is zeroed at the
+// start and afterwards only ever receives pages of the pool, which the engine allocates zeroed.
+//
+// Every wait is bounded by a clock limit; a role that gives up sets an error word that the host
+// can read, the block lets its copies land, frees its tensor memory and returns.
+//
+// Role in the reference: pulsar-core/inc/pulsar/kernels/paged_prefill.cuh:35-346 (mma.sync tiles
+// of 16 queries with a host-built tile list).
+#include "tcgen05_common.cuh"
+
+namespace {
+
+using namespace pb;
+typedef __nv_bfloat16 bf16;
+
+constexpr int kD = 128;              // head size
+constexpr int kBM = 128;             // query rows per block (MMA M, tensor-memory lanes)
+constexpr int kBN = 128;             // keys per tile
+constexpr int kThreads = 192;
+constexpr int kHalfBytes = 128 * 64 * 2;       // one [128 x 64] swizzled half tile: 16 KB
+constexpr int kTileBytes = 2 * kHalfBytes;     // 32 KB
+constexpr int kSmemBytes = 3 * kTileBytes + 1024 /* alignment slack */ + 128 /* barriers */;
+constexpr int kTmemColumns = 256;              // S (P over its first 64) | O
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLazyRescale = 8.0f;           // move the maximum when it grew by more than 2^8
+
+__device__ unsigned int g_attn5_error = 0;     // 0 = fine; else 1 + the role that gave up
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// K-major operand with 128-byte rows, 128-byte swizzle, 1024 bytes between groups of 8 rows.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// MN-major operand: 64 elements of the N dimension lie along a 128-byte row, the K dimension
+// runs over the rows (8 rows = 1024 bytes per group), the next 64 of N lie one half tile further.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);
+    d |= (uint64_t)(kHalfBytes >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// float32 accumulator, bfloat16 operands, M 128, N 128; bit 16 = B is MN-major.
+constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kD >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+
+__device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+                   "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+                   "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Barrier slots.
+enum { kBarQ = 0, kBarKFull, kBarKEmpty, kBarVFull, kBarVEmpty, kBarSFull, kBarPFull, kBarOFull, kNumBars };
+
+__global__ void __launch_bounds__(kThreads, 2)
+prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
+                       const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
+                       const int* __restrict__ kv_len, int n_seqs, int Hq, int Hkv, int page_shift, int rows_per_load,
+                       float scale, int window) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = smem;
+    unsigned char* k_s = smem + kTileBytes;
+    unsigned char* v_s = smem + 2 * kTileBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int head = blockIdx.x;
+    const int kvh = head / (Hq / Hkv);
+
+    // Which sequence and which of its query tiles.  Heads are the fast grid index and the tiles run
+    // backwards, so that the tiles with the longest key ranges (ends of long portions) start first.
+    int tile = gridDim.y - 1 - blockIdx.y;
+    int s = 0, q0 = 0, q_len = 0;
+    for (; s < n_seqs; ++s) {
+        q0 = cu_q[s];
+        q_len = cu_q[s + 1] - q0;
+        const int nt = (q_len + kBM - 1) / kBM;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (s >= n_seqs) return;
+    const int m0 = tile * kBM;
+    const int rows = min(kBM, q_len - m0);
+    const int ctx0 = kv_len[s] - q_len;
+    const int pos_first = ctx0 + m0, pos_last = ctx0 + m0 + rows - 1;
+    const int lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const int kt0 = lo / kBN, n_tiles = pos_last / kBN - kt0 + 1;
+    const int* table = block_table + (size_t)s * table_stride;
+
+    const uint32_t bar0 = smem_addr(bars);
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+
+    // V's buffer starts finite (see the header); 16 bytes per thread and step.
+    for (int i = tid; i < kTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+    if (tid == 0) {
+        mbar_init(bar(kBarQ), 1);
+        mbar_init(bar(kBarKFull), 1);
+        mbar_init(bar(kBarKEmpty), 1);
+        mbar_init(bar(kBarVFull), 1);
+        mbar_init(bar(kBarVEmpty), 1);
+        mbar_init(bar(kBarSFull), 1);
+        mbar_init(bar(kBarPFull), 4);
+        mbar_init(bar(kBarOFull), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the zeros are visible to the TMA/MMA proxy
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemColumns));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + kBN;
+
+    if (warp == 4) {
+        // ---------------- TMA producer: lane i issues box i of a tile
+        if (lane == 0) {
+            mbar_expect_tx(bar(kBarQ), kTileBytes);
+            tma_load_2d(smem_addr(q_s), &map_q, bar(kBarQ), head * kD, q0 + m0);
+            tma_load_2d(smem_addr(q_s) + kHalfBytes, &map_q, bar(kBarQ), head * kD + 64, q0 + m0);
+        }
+        const int loads = kBN / rows_per_load;                 // pages (or parts of a page) per tile
+        const uint32_t load_bytes = (uint32_t)rows_per_load * 128u;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int key0 = (kt0 + j) * kBN;
+            // lane -> (page slot, half)
+            const int slot = lane >> 1, half = lane & 1;
+            const int key = key0 + slot * rows_per_load;
+            const bool want = slot < loads && key + rows_per_load > lo && key <= pos_last;
+            int row = 0;
+            if (want) {
+                const int page = table[key >> page_shift];
+                row = ((page * Hkv + kvh) << page_shift) + (key & ((1 << page_shift) - 1));
+            }
+            const uint32_t n_want = __popc(__ballot_sync(0xffffffffu, want));
+            const uint32_t dst_off = (uint32_t)half * kHalfBytes + (uint32_t)(slot * rows_per_load) * 128u;
+            // K[j]: when S[j-1] has read the buffer
+            if (lane == 0) {
+                ok = mbar_wait(bar(kBarKEmpty), (j & 1) ^ 1, abort_flag);
+                if (ok) mbar_expect_tx(bar(kBarKFull), n_want * load_bytes);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (want) tma_load_2d(smem_addr(k_s) + dst_off, &map_k, bar(kBarKFull), half * 64, row);
+            // V[j]: when O += P[j-1] V[j-1] has read the buffer
+            if (lane == 0) {
+                ok = mbar_wait(bar(kBarVEmpty), (j & 1) ^ 1, abort_flag);
+                if (ok) mbar_expect_tx(bar(kBarVFull), n_want * load_bytes);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (want) tma_load_2d(smem_addr(v_s) + dst_off, &map_v, bar(kBarVFull), half * 64, row);
+        }
+        if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_attn5_error, 2u); }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            bool ok = mbar_wait(bar(kBarQ), 0, abort_flag);
+            const uint32_t q_addr = smem_addr(q_s), k_addr = smem_addr(k_s), v_addr = smem_addr(v_s);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (!mbar_wait(bar(kBarKFull), j & 1, abort_flag)) { ok = false; break; }
+                // S[j] overwrites the columns that O += P[j-1] V[j-1] reads P from; the MMAs of one thread
+                // run in the order of their issue, so that product has read P before S[j] writes
+                fence_after();
+#pragma unroll
+                for (int ks = 0; ks < kD / 16; ++ks) {
+                    const uint32_t off = (uint32_t)(ks >> 2) * kHalfBytes + (uint32_t)(ks & 3) * 32u;
+                    umma_ss(tmem_s, desc_k_major(q_addr + off), desc_k_major(k_addr + off), kIdescS, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(bar(kBarKEmpty));
+                umma_commit(bar(kBarSFull));
+                if (!mbar_wait(bar(kBarVFull), j & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(bar(kBarPFull), j & 1, abort_flag)) { ok = false; break; }
+                fence_after();
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk)
+                    umma_ts(tmem_o, tmem_s + (uint32_t)kk * 8u, desc_mn_major(v_addr + (uint32_t)kk * 2048u), kIdescPV,
+                            (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(bar(kBarVEmpty));
+                umma_commit(bar(kBarOFull));
+            }
+            if (!ok) { *abort_flag = 1; atomicMax(&g_attn5_error, 3u); }
+        }
+    } else {
+        // ---------------- softmax: thread `r` owns query row r
+        const int r = warp * 32 + lane;
+        const int pos = pos_first + min(r, rows - 1);             // rows beyond the tile's end repeat the last one
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        const float sl2 = scale * kLog2e;
+        float m_used = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            ok = mbar_wait(bar(kBarSFull), j & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after();
+            const int key0 = (kt0 + j) * kBN;
+            // every row of the block sees every key of the tile?
+            const bool all_visible = key0 + kBN - 1 <= pos_first && (window <= 0 || key0 > pos_last - window);
+            // the whole row of S into registers: four loads in flight, one wait
+            uint32_t v[kBN];
+#pragma unroll
+            for (int c = 0; c < kBN; c += 32) tmem_ld32_nowait(tmem_s + lane_addr + c, *reinterpret_cast<uint32_t(*)[32]>(&v[c]));
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < kBN; c += 32) tmem_landed(*reinterpret_cast<uint32_t(*)[32]>(&v[c]));
+            if (!all_visible) {
+#pragma unroll
+                for (int i = 0; i < kBN; ++i) {
+                    const int key = key0 + i;
+                    if (!(key <= pos && (window <= 0 || key > pos - window))) v[i] = __float_as_uint(-INFINITY);
+                }
+            }
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kBN; ++i) tmax = fmaxf(tmax, __uint_as_float(v[i]));
+            // move the maximum only when it grew by more than the lazy threshold
+            float corr = 1.0f;
+            if ((tmax - m_used) * sl2 > kLazyRescale) {      // also the first visible key: m_used = -inf
+                corr = ex2((m_used - tmax) * sl2);            // 0 when m_used = -inf
+                m_used = tmax;
+                l_run *= corr;
+            }
+            const float neg_ms = (m_used == -INFINITY) ? 0.0f : -m_used * sl2;
+            // P over the first half of S's columns
+            float l0 = 0.0f, l1 = 0.0f;
+#pragma unroll
+            for (int c = 0; c < kBN; c += 32) {
+                uint32_t p[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = ex2(fmaf(__uint_as_float(v[c + i]), sl2, neg_ms));
+                    const float p1 = ex2(fmaf(__uint_as_float(v[c + i + 1]), sl2, neg_ms));
+                    l0 += p0;
+                    l1 += p1;
+                    p[i >> 1] = pack_bf16x2(p0, p1);
+                }
+                tmem_st16(tmem_s + lane_addr + (c >> 1), p);
+            }
+            l_run += l0 + l1;
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                // S[j] is complete, so O += P[j-1] V[j-1] has retired too: O may be rescaled in place
+#pragma unroll 1
+                for (int c = 0; c < kD; c += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_o + lane_addr + c, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                    tmem_st32(tmem_o + lane_addr + c, o);
+                }
+            }
+            tmem_wait_st();
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kBarPFull));
+        }
+        if (ok) {
+            ok = mbar_wait(bar(kBarOFull), (n_tiles - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            fence_after();
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            bf16* dst = out + ((size_t)(q0 + m0 + r) * Hq + head) * kD;
+#pragma unroll 1
+            for (int c = 0; c < kD; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_o + lane_addr + c, v);
+                if (r < rows) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            w[k] = pack_bf16x2(__uint_as_float(v[i * 8 + 2 * k]) * inv, __uint_as_float(v[i * 8 + 2 * k + 1]) * inv);
+                        reinterpret_cast<uint4*>(dst + c)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            *abort_flag = 1;
+            atomicMax(&g_attn5_error, 4u);
+        }
+    }
+    __syncwarp();
+    if (*abort_flag) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);       // copies in flight land before the memory is reused
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
+}
+
+// Row-major [rows, cols] bfloat16 matrix, boxes of box_rows x 64 columns, 128-byte swizzle, zero fill outside.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS ? 0 : PB_ERR_BAD_SIZE;
+}
+
+int log2_exact(int v) {
+    if (v <= 0 || (v & (v - 1))) return -1;
+    int s = 0;
+    while ((1 << s) < v) ++s;
+    return s;
+}
+
+}  // namespace
+
+// Query rows per block: the caller sizes the grid as the sum over sequences of ceil(q_len / this).
+PB_EXPORT int pb_prefill_tcgen05_tile(void) { return kBM; }
+
+PB_EXPORT int pb_prefill_tcgen05_supported(int dtype, int Hq, int Hkv, int D, int page_size) {
+    if (dtype != PB_BF16 || Hkv <= 0 || Hq % Hkv) return 0;
+    if (D != kD) return 0;
+    if (log2_exact(page_size) < 0 || page_size < 8) return 0;           // whole groups of 8 swizzled rows per page
+    return 1;
+}
+
+// The error word of the kernel's bounded waits (0 = no block ever gave up); reading it synchronises.
+PB_EXPORT int pb_prefill_tcgen05_error(void) {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn5_error, sizeof(v)) != cudaSuccess) return -1;
+    return (int)v;
+}
+
+// q, out [N, Hq, D] bfloat16; pools [n_pages, Hkv, page_size, D] bfloat16 with finite contents;
+// n_q_tiles = sum over sequences of ceil(q_len / pb_prefill_tcgen05_tile()).
+PB_EXPORT int pb_paged_attention_prefill_tcgen05(int dtype, const void* q, const void* k_pool, const void* v_pool, void* out,
+                                                 const int* block_table, int table_stride, const int* cu_q,
+                                                 const int* kv_len, int n_tokens, int n_seqs, int n_q_tiles, int n_pages,
+                                                 int Hq, int Hkv, int D, int page_size, float scale, int window,
+                                                 cudaStream_t stream) {
+    if (n_seqs <= 0 || n_q_tiles <= 0 || n_tokens <= 0) return 0;
+    if (!pb_prefill_tcgen05_supported(dtype, Hq, Hkv, D, page_size)) return PB_ERR_BAD_SIZE;
+    if (n_q_tiles > 65535) return PB_ERR_TOO_LARGE;
+    if ((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) != 0) return PB_ERR_BAD_SIZE;
+    const long long pool_rows = (long long)n_pages * Hkv * page_size;
+    if (pool_rows >= (1LL << 31)) return PB_ERR_TOO_LARGE;
+    const int rows_per_load = page_size < kBN ? page_size : kBN;
+    CUtensorMap mq, mk, mv;
+    int rc = make_map(&mq, q, n_tokens, (long long)Hq * D, kBM);
+    if (rc != 0) return rc;
+    rc = make_map(&mk, k_pool, pool_rows, D, rows_per_load);
+    if (rc != 0) return rc;
+    rc = make_map(&mv, v_pool, pool_rows, D, rows_per_load);
+    if (rc != 0) return rc;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(Hq, n_q_tiles);
+    prefill_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, (bf16*)out, block_table, table_stride, cu_q, kv_len,
+                                                                  n_seqs, Hq, Hkv, log2_exact(page_size), rows_per_load, scale,
+                                                                  window);
+    return launch_status();
+}

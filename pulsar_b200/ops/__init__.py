@@ -28,6 +28,8 @@ F32, BF16 = 0, 1
 #   "library"  every projection on the library product, gating in a kernel of its own.
 # Up to 16 rows always take the weight-streaming kernel.
 GEMM_BACKEND = os.environ.get("PULSAR_GEMM", "auto")
+# Attention of prompt portions in bfloat16: "auto" = the tcgen05 kernel where it applies, "mma" = never.
+ATTENTION_BACKEND = os.environ.get("PULSAR_ATTENTION", "auto")
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 _ERRORS = {-2: "unsupported dtype", -3: "unsupported size or argument", -4: "size exceeds the kernel's limit"}
 
@@ -46,6 +48,10 @@ _SIGNATURES = {
     "pb_paged_attention_prefill_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "pb_prefill_tc_supported": [_I, _I, _I, _I, _I],
     "pb_prefill_tc_tile": [],
+    "pb_paged_attention_prefill_tcgen05": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "pb_prefill_tcgen05_supported": [_I, _I, _I, _I, _I],
+    "pb_prefill_tcgen05_tile": [],
+    "pb_prefill_tcgen05_error": [],
     "pb_gemm_skinny": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_gemm_skinny_supported": [_I, _I, _I, _I],
     "pb_gemm_tcgen05": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
@@ -381,11 +387,49 @@ def paged_attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: to
           "paged_attention_prefill_tc")
 
 
+def prefill_tcgen05_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    if dtype != torch.bfloat16:
+        return False
+    return bool(fn("pb_prefill_tcgen05_supported")(BF16, n_heads, n_kv_heads, head_dim, page_size))
+
+
+def prefill_tcgen05_tiles(q_lens) -> int:
+    """Blocks along the query axis: each sequence's new tokens in tiles of 128."""
+    tile = fn("pb_prefill_tcgen05_tile")()
+    return sum(-(-int(n) // tile) for n in q_lens)
+
+
+def prefill_tcgen05_error() -> int:
+    """0 unless a block of the tcgen05 attention ever gave up a bounded wait (synchronises)."""
+    return int(fn("pb_prefill_tcgen05_error")())
+
+
+def paged_attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                                    block_table: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, n_q_tiles: int,
+                                    scale: float, window: Optional[int]) -> None:
+    """tcgen05 attention for a ragged batch of portions (bfloat16, head size 128, pages of 8 or more
+    tokens).  Pool rows that were never written must hold finite values."""
+    _cuda(q, k_pool, v_pool, out, block_table, cu_q, kv_len)
+    n, hq, d = q.shape
+    pages, hkv, page_size, d2 = k_pool.shape
+    assert d2 == d and v_pool.shape == k_pool.shape and out.shape == q.shape
+    assert q.is_contiguous() and k_pool.is_contiguous() and v_pool.is_contiguous() and out.is_contiguous()
+    assert k_pool.dtype == q.dtype and v_pool.dtype == q.dtype and out.dtype == q.dtype
+    assert block_table.dtype == torch.int32 and cu_q.dtype == torch.int32 and kv_len.dtype == torch.int32
+    s = kv_len.numel()
+    assert cu_q.numel() == s + 1 and block_table.shape[0] == s
+    check(fn("pb_paged_attention_prefill_tcgen05")(code(q.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(block_table),
+                                                   block_table.shape[1], _p(cu_q), _p(kv_len), n, s, n_q_tiles, pages, hq,
+                                                   hkv, d, page_size, float(scale), int(window or 0), stream()),
+          "paged_attention_prefill_tcgen05")
+
+
 def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, window: Optional[int]) -> None:
     """Attention of the step's query tokens over their pages.  ``cache`` is a CacheView
     (pools, block table), ``ctx`` the StepContext (cu_q, kv_len, seq_of_token).  A step of
-    single tokens only takes a split-key decode kernel; anything else the tensor-core prefill
-    kernel where it applies (bfloat16, head size 64 or 128), else the generic kernel."""
+    single tokens only takes a split-key decode kernel; anything else the tcgen05 kernel where it
+    applies (bfloat16, head size 128, pages of 8 or more), else the mma.sync kernel (bfloat16, head
+    size 64 or 128), else the generic kernel.  ``PULSAR_ATTENTION=mma`` leaves the tcgen05 kernel out."""
     if ctx.all_decode:
         n_splits = decode_splits(ctx.n_seqs, cache.k_pool.shape[1])
         partial = ctx.scratch("attn.partial", (ctx.n_seqs * q.shape[1] * n_splits * (q.shape[2] + 2),), torch.float32)
@@ -393,6 +437,10 @@ def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, wind
                                window, n_splits)
         return
     hkv, page_size = cache.k_pool.shape[1], cache.k_pool.shape[2]
+    if ATTENTION_BACKEND != "mma" and prefill_tcgen05_supported(q.dtype, q.shape[1], hkv, q.shape[2], page_size):
+        paged_attention_prefill_tcgen05(q, cache.k_pool, cache.v_pool, out, cache.block_table, ctx.cu_q, ctx.kv_len,
+                                        prefill_tcgen05_tiles(ctx.host.q_lens), scale, window)
+        return
     if prefill_tc_supported(q.dtype, q.shape[1], hkv, q.shape[2], page_size):
         paged_attention_prefill_tc(q, cache.k_pool, cache.v_pool, out, cache.block_table, ctx.cu_q, ctx.kv_len,
                                    prefill_tc_tiles(ctx.host.q_lens), scale, window)

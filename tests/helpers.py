@@ -39,7 +39,15 @@ TINY_D = dict(
     rms_norm_eps=2e-6, tie_word_embeddings=True, use_sliding_window=True, sliding_window=40,
     max_window_layers=1, hidden_act="silu", attention_bias=False, initializer_range=0.03, eos_token_id=3)
 
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 4), "D": (TINY_D, 3, 16)}     # config, seed, page size
+# Head size 128: the size at which prompt portions run the tcgen05 attention kernel (pages of 8 or more).
+TINY_E = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=272, hidden_size=96, intermediate_size=160,
+    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128, rope_theta=250000.0,
+    rms_norm_eps=4e-6, tie_word_embeddings=False, use_sliding_window=True, sliding_window=150,
+    max_window_layers=1, hidden_act="silu", attention_bias=False, initializer_range=0.03, eos_token_id=9)
+
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 4), "D": (TINY_D, 3, 16),
+        "E": (TINY_E, 4, 8)}     # config, seed, page size
 
 
 def make_folder(tmpdir: str, raw: dict, seed: int, store_dtype=torch.float32, std: Optional[float] = None) -> str:

@@ -390,6 +390,70 @@ def test_attention_prefill_tensor_cores(hq, hkv, d, page, window):
     close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window), TOL[dtype])
 
 
+TCGEN05_ATTN_SHAPES = [(32, 8, 128, 16), (16, 1, 128, 32), (12, 4, 128, 64), (7, 7, 128, 8), (6, 3, 128, 128), (4, 2, 128, 256)]
+
+
+@pytest.mark.parametrize("hq,hkv,d,page", TCGEN05_ATTN_SHAPES)
+@pytest.mark.parametrize("window", [None, 37, 200])
+def test_attention_prefill_tcgen05(hq, hkv, d, page, window):
+    """The tcgen05 prefill kernel on a ragged batch: first portions, later portions that start inside
+    a page and a tile, single tokens, lengths around the 128-row tile (127, 128, 129, 300), a context of
+    several key tiles, one far key that stands out; pool rows that no sequence owns hold zeros."""
+    from pulsar_b200 import ops
+    dtype = torch.bfloat16
+    assert ops.prefill_tcgen05_supported(dtype, hq, hkv, d, page)
+    g = torch.Generator().manual_seed(13)
+    lens_q = [16, 7, 33, 1, 1, 2, 128, 127, 129, 300, 5]
+    lens_kv = [16, 40, 33, 65, 1, 129, 200, 127, 400, 300, 517]
+    case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype, spike=(10, 3, hq - 1))
+    out = torch.full((sum(lens_q), hq, d), float("nan"), dtype=dtype, device="cuda")
+    scale = 1.0 / math.sqrt(d)
+    ops.paged_attention_prefill_tcgen05(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, dev(case["table"]),
+                                        dev(case["cu"]), dev(case["kv"]), ops.prefill_tcgen05_tiles(lens_q), scale, window)
+    assert ops.prefill_tcgen05_error() == 0
+    close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window), TOL[dtype])
+
+
+def test_attention_prefill_tcgen05_growing_scores():
+    """Scores that grow along the keys force the running maximum to move again and again (the output
+    in tensor memory is rescaled each time); scores that fall never move it after the first tile."""
+    from pulsar_b200 import ops
+    dtype, hq, hkv, d, page = torch.bfloat16, 4, 2, 128, 16
+    g = torch.Generator().manual_seed(14)
+    lens_q, lens_kv = [520, 260], [520, 700]
+    case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype)
+    # key j of sequence 0 gets a component along a fixed direction that grows with j; sequence 1: falls
+    direction = torch.randn(d, generator=g)
+    direction /= direction.norm()
+    q = case["q"].float()
+    q += 4.0 * direction
+    case["q"] = q.to(dtype)
+    kp = case["kp"].float()
+    for si, sign in ((0, 1.0), (1, -1.0)):
+        ramp = sign * torch.arange(lens_kv[si]).float() * 0.25
+        case["k_seq"][si] = (case["k_seq"][si].float() + ramp[:, None, None] * direction).to(dtype).double()
+        for lp in range(-(-lens_kv[si] // page)):
+            pg = int(case["table"][si, lp])
+            lo, hi = lp * page, min(lens_kv[si], (lp + 1) * page)
+            kp[pg, :, :hi - lo] = case["k_seq"][si][lo:hi].permute(1, 0, 2).float()
+    case["kp"] = kp.to(dtype)
+    out = torch.full((sum(lens_q), hq, d), float("nan"), dtype=dtype, device="cuda")
+    scale = 1.0 / math.sqrt(d)
+    ops.paged_attention_prefill_tcgen05(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, dev(case["table"]),
+                                        dev(case["cu"]), dev(case["kv"]), ops.prefill_tcgen05_tiles(lens_q), scale, None)
+    assert ops.prefill_tcgen05_error() == 0
+    close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, None), TOL[dtype])
+
+
+def test_attention_prefill_tcgen05_applicability():
+    from pulsar_b200 import ops
+    assert not ops.prefill_tcgen05_supported(torch.float32, 32, 8, 128, 16)
+    assert not ops.prefill_tcgen05_supported(torch.bfloat16, 32, 8, 64, 16)        # head size
+    assert not ops.prefill_tcgen05_supported(torch.bfloat16, 32, 8, 128, 4)        # page below a swizzle group
+    assert not ops.prefill_tcgen05_supported(torch.bfloat16, 32, 8, 128, 24)       # page no power of two
+    assert not ops.prefill_tcgen05_supported(torch.bfloat16, 32, 5, 128, 16)       # groups do not divide the heads
+
+
 def test_decode_tensor_cores_applicability():
     from pulsar_b200 import ops
     assert not ops.decode_tc_supported(torch.float32, 32, 8, 128, 16)

@@ -64,7 +64,7 @@ def _round64(n):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole(folders, name, dtype):
     raw, seed, page = TINY[name]
     rng = random.Random(seed)
@@ -75,7 +75,7 @@ def test_whole(folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_tail_decoded_one_by_one(folders, name, dtype):
     raw, seed, page = TINY[name]
     rng = random.Random(seed + 10)
@@ -87,7 +87,7 @@ def test_tail_decoded_one_by_one(folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_portions_of_changing_size(folders, name, dtype):
     raw, seed, page = TINY[name]
     rng = random.Random(seed + 20)
@@ -99,7 +99,7 @@ def test_portions_of_changing_size(folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_mixed_with_page_reuse(folders, name, dtype):
     raw, seed, page = TINY[name]
     rng = random.Random(seed + 30)
@@ -129,6 +129,23 @@ def test_portions_with_the_tcgen05_products(folders, name, monkeypatch):
     assert len(got) == len(toks)
     _compare(got, ref, "bfloat16")
     assert ops.gemm_tcgen05_error() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_portions_head_size_128(folders, dtype):
+    """Head size 128 (bfloat16: the tcgen05 attention kernel): portions that cross its 128-row and
+    128-key tiles and the window of the upper layer, a long tail decoded one by one."""
+    from pulsar_b200 import ops
+    raw, seed, page = TINY["E"]
+    rng = random.Random(seed + 50)
+    toks = helpers.random_tokens(rng, 420, raw["vocab_size"])
+    ref = _reference(folders["E"], dtype, {"a": toks})
+    got = _replay(folders["E"], dtype, helpers.trace_portions(toks, [130, 2, 127, 129, 5]), _round64(len(toks)), page)
+    assert len(got) == len(toks)
+    _compare(got, ref, dtype)
+    got = _replay(folders["E"], dtype, helpers.trace_tail(toks[:300], 32), _round64(300), page)
+    _compare(got, ref, dtype)
+    assert ops.prefill_tcgen05_error() == 0
 
 
 def test_trace_run_program(folders, tmp_path):
