@@ -1,21 +1,22 @@
 // Paged attention for prompt portions on the fifth-generation tensor cores: causal, ragged
 // batch, optional window, grouped heads, bfloat16 pages, head size 128.
 //
-// One block per (tile of 128 query tokens of one sequence, query head); two blocks share an
-// SM (96 KB of shared memory and 256 of the 512 tensor-memory columns each), so that the tensor
-// core works for one while the other computes its softmax.  Roles inside a block:
+// One block per (tile of 128 query tokens of one sequence, query head), one block per SM (160 KB of
+// shared memory, all 512 tensor-memory columns: two S tiles and O).  Roles inside a block:
 //   warps 0-3   softmax: thread r owns query row r (tensor-memory lane r).  It reads its row of
 //               S = Q K^T from tensor memory (tcgen05.ld), keeps the running maximum and sum in
 //               float32, writes P = 2^(s*c - m*c) rounded to bfloat16 back over the first half
 //               of S's columns (tcgen05.st), and at the end normalises and stores its row of O;
-//   warp 4      TMA producer: the query tile once, then per tile of 128 keys the pages that the
+//   warp 4      one thread issues the MMAs: S = Q K^T (operands in shared memory, eight
+//               tcgen05.mma of K 16), and O += P V with P read from tensor memory and V as an
+//               MN-major operand straight from the page layout (keys along K);
+//   warps 5-7   TMA producers: the query tile once, then per tile of 128 keys the pages that the
 //               block table names, each as two boxes of [page x 64] into 128-byte-swizzled
-//               tiles (one lane per box);
-//   warp 5      one thread issues the MMAs: S = Q K^T (operands in shared memory, eight
-//               tcgen05.mma of K 16), then O += P V with P read from tensor memory and V as an
-//               MN-major operand straight from the page layout (keys along K).
-// K and V have one buffer each: the load of K[j+1] starts when S[j] has been computed and runs
-// during softmax j; the load of V[j+1] starts when O += P[j] V[j] has retired.
+//               tiles, two stages each for K and V.  A warp issues the copies of its lanes one
+//               after the other, so a tile's boxes are dealt out over the three warps.
+// S has two buffers: S[j+1] is issued before O += P[j] V[j], so that it is complete when the
+// softmax warps finish tile j, and the tensor core works on tile j+1 and on P[j] V[j] while they
+// compute tile j+1's exponentials.
 //
 // The running maximum is only moved when a row's new maximum exceeds it by more than 2^8 in the
 // exponent: P then stays below 256, which bfloat16 holds with the same relative rounding, and O
@@ -42,11 +43,13 @@ typedef __nv_bfloat16 bf16;
 constexpr int kD = 128;              // head size
 constexpr int kBM = 128;             // query rows per block (MMA M, tensor-memory lanes)
 constexpr int kBN = 128;             // keys per tile
-constexpr int kThreads = 192;
+constexpr int kThreads = 256;             // 4 softmax warps, the MMA warp, 3 producer warps
+constexpr int kProducers = 3;
 constexpr int kHalfBytes = 128 * 64 * 2;       // one [128 x 64] swizzled half tile: 16 KB
 constexpr int kTileBytes = 2 * kHalfBytes;     // 32 KB
-constexpr int kSmemBytes = 3 * kTileBytes + 1024 /* alignment slack */ + 128 /* barriers */;
-constexpr int kTmemColumns = 256;              // S (P over its first 64) | O
+constexpr int kStages = 2;                     // K and V tiles in flight
+constexpr int kSmemBytes = (1 + 2 * kStages) * kTileBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int kTmemColumns = 512;              // S[0] | S[1] (P over the first 64 of each) | O
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLazyRescale = 8.0f;           // move the maximum when it grew by more than 2^8
 
@@ -118,10 +121,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Barrier slots.
-enum { kBarQ = 0, kBarKFull, kBarKEmpty, kBarVFull, kBarVEmpty, kBarSFull, kBarPFull, kBarOFull, kNumBars };
+// Barrier slots; those of K, V, S and P exist once per stage.
+enum { kBarQ = 0, kBarOFull, kBarKFull, kBarKEmpty = kBarKFull + kStages, kBarVFull = kBarKEmpty + kStages,
+       kBarVEmpty = kBarVFull + kStages, kBarSFull = kBarVEmpty + kStages, kBarPFull = kBarSFull + 2, kNumBars = kBarPFull + 2 };
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                        const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
@@ -130,9 +134,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;
-    unsigned char* k_s = smem + kTileBytes;
-    unsigned char* v_s = smem + 2 * kTileBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes);
+    unsigned char* k_s = smem + kTileBytes;                    // kStages tiles
+    unsigned char* v_s = smem + (1 + kStages) * kTileBytes;    // kStages tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (1 + 2 * kStages) * kTileBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -163,22 +167,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t bar0 = smem_addr(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
-    // V's buffer starts finite (see the header); 16 bytes per thread and step.
-    for (int i = tid; i < kTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+    // V's buffers start finite (see the header); 16 bytes per thread and step.
+    for (int i = tid; i < kStages * kTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
     if (tid == 0) {
-        mbar_init(bar(kBarQ), 1);
-        mbar_init(bar(kBarKFull), 1);
-        mbar_init(bar(kBarKEmpty), 1);
-        mbar_init(bar(kBarVFull), 1);
-        mbar_init(bar(kBarVEmpty), 1);
-        mbar_init(bar(kBarSFull), 1);
-        mbar_init(bar(kBarPFull), 4);
-        mbar_init(bar(kBarOFull), 1);
+        for (int i = 0; i < kNumBars; ++i)
+            mbar_init(bar(i), i >= kBarPFull ? 4 : (i >= kBarKFull && i < kBarKEmpty) || (i >= kBarVFull && i < kBarVEmpty) ? kProducers : 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the zeros are visible to the TMA/MMA proxy
-    if (warp == 5) {
+    if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemColumns));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
@@ -186,22 +184,26 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + kBN;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kBN;      // S[0] | S[1] | O
 
-    if (warp == 4) {
-        // ---------------- TMA producer: lane i issues box i of a tile
-        if (lane == 0) {
+    if (warp >= 5) {
+        // ---------------- TMA producers: a tile's boxes are dealt out over the lanes of three warps (a warp issues
+        // the copies of its lanes one after the other, so few lanes per warp keep a tile's issue time short)
+        const int pw = warp - 5;
+        if (pw == 0 && lane == 0) {
             mbar_expect_tx(bar(kBarQ), kTileBytes);
             tma_load_2d(smem_addr(q_s), &map_q, bar(kBarQ), head * kD, q0 + m0);
             tma_load_2d(smem_addr(q_s) + kHalfBytes, &map_q, bar(kBarQ), head * kD + 64, q0 + m0);
         }
         const int loads = kBN / rows_per_load;                 // pages (or parts of a page) per tile
         const uint32_t load_bytes = (uint32_t)rows_per_load * 128u;
+        const int box = pw + kProducers * lane;                // box -> (page slot, half)
+        const int slot = box >> 1, half = box & 1;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int key0 = (kt0 + j) * kBN;
-            // lane -> (page slot, half)
-            const int slot = lane >> 1, half = lane & 1;
+            const int st = j % kStages;
+            const uint32_t free_parity = ((j / kStages) & 1) ^ 1;
             const int key = key0 + slot * rows_per_load;
             const bool want = slot < loads && key + rows_per_load > lo && key <= pos_last;
             int row = 0;
@@ -210,50 +212,59 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 row = ((page * Hkv + kvh) << page_shift) + (key & ((1 << page_shift) - 1));
             }
             const uint32_t n_want = __popc(__ballot_sync(0xffffffffu, want));
-            const uint32_t dst_off = (uint32_t)half * kHalfBytes + (uint32_t)(slot * rows_per_load) * 128u;
-            // K[j]: when S[j-1] has read the buffer
+            const uint32_t dst_off = (uint32_t)st * kTileBytes + (uint32_t)half * kHalfBytes + (uint32_t)(slot * rows_per_load) * 128u;
+            // K[j]: when S[j - kStages] has read the stage
             if (lane == 0) {
-                ok = mbar_wait(bar(kBarKEmpty), (j & 1) ^ 1, abort_flag);
-                if (ok) mbar_expect_tx(bar(kBarKFull), n_want * load_bytes);
+                ok = mbar_wait(bar(kBarKEmpty + st), free_parity, abort_flag);
+                if (ok) mbar_expect_tx(bar(kBarKFull + st), n_want * load_bytes);
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            if (want) tma_load_2d(smem_addr(k_s) + dst_off, &map_k, bar(kBarKFull), half * 64, row);
-            // V[j]: when O += P[j-1] V[j-1] has read the buffer
+            if (want) tma_load_2d(smem_addr(k_s) + dst_off, &map_k, bar(kBarKFull + st), half * 64, row);
+            // V[j]: when O += P V of tile j - kStages has read the stage
             if (lane == 0) {
-                ok = mbar_wait(bar(kBarVEmpty), (j & 1) ^ 1, abort_flag);
-                if (ok) mbar_expect_tx(bar(kBarVFull), n_want * load_bytes);
+                ok = mbar_wait(bar(kBarVEmpty + st), free_parity, abort_flag);
+                if (ok) mbar_expect_tx(bar(kBarVFull + st), n_want * load_bytes);
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            if (want) tma_load_2d(smem_addr(v_s) + dst_off, &map_v, bar(kBarVFull), half * 64, row);
+            if (want) tma_load_2d(smem_addr(v_s) + dst_off, &map_v, bar(kBarVFull + st), half * 64, row);
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_attn5_error, 2u); }
-    } else if (warp == 5) {
-        // ---------------- MMA issuer
+    } else if (warp == 4) {
+        // ---------------- MMA issuer: S[0]; then per tile S[j+1] (so that it is ready when softmax j ends) and O += P[j] V[j].
+        // S[j+1] overwrites the columns that held S[j-1] and P[j-1]: O += P[j-1] V[j-1] was issued before it, and
+        // the MMAs of one thread run in the order of their issue.
         if (lane == 0) {
-            bool ok = mbar_wait(bar(kBarQ), 0, abort_flag);
             const uint32_t q_addr = smem_addr(q_s), k_addr = smem_addr(k_s), v_addr = smem_addr(v_s);
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                if (!mbar_wait(bar(kBarKFull), j & 1, abort_flag)) { ok = false; break; }
-                // S[j] overwrites the columns that O += P[j-1] V[j-1] reads P from; the MMAs of one thread
-                // run in the order of their issue, so that product has read P before S[j] writes
+            auto issue_s = [&](int j) -> bool {
+                const int st = j % kStages, sb = j & 1;
+                if (!mbar_wait(bar(kBarKFull + st), (j / kStages) & 1, abort_flag)) return false;
                 fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
                     const uint32_t off = (uint32_t)(ks >> 2) * kHalfBytes + (uint32_t)(ks & 3) * 32u;
-                    umma_ss(tmem_s, desc_k_major(q_addr + off), desc_k_major(k_addr + off), kIdescS, ks > 0 ? 1u : 0u);
+                    umma_ss(tmem_s + (uint32_t)sb * kBN, desc_k_major(q_addr + off),
+                            desc_k_major(k_addr + (uint32_t)st * kTileBytes + off), kIdescS, ks > 0 ? 1u : 0u);
                 }
-                umma_commit(bar(kBarKEmpty));
-                umma_commit(bar(kBarSFull));
-                if (!mbar_wait(bar(kBarVFull), j & 1, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(bar(kBarPFull), j & 1, abort_flag)) { ok = false; break; }
+                umma_commit(bar(kBarKEmpty + st));
+                umma_commit(bar(kBarSFull + sb));
+                return true;
+            };
+            bool ok = mbar_wait(bar(kBarQ), 0, abort_flag);
+            ok = ok && issue_s(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int st = j % kStages, sb = j & 1;
+                if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
+                if (!mbar_wait(bar(kBarVFull + st), (j / kStages) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(bar(kBarPFull + sb), (j >> 1) & 1, abort_flag)) { ok = false; break; }
                 fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk)
-                    umma_ts(tmem_o, tmem_s + (uint32_t)kk * 8u, desc_mn_major(v_addr + (uint32_t)kk * 2048u), kIdescPV,
+                    umma_ts(tmem_o, tmem_s + (uint32_t)sb * kBN + (uint32_t)kk * 8u,
+                            desc_mn_major(v_addr + (uint32_t)st * kTileBytes + (uint32_t)kk * 2048u), kIdescPV,
                             (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(bar(kBarVEmpty));
+                umma_commit(bar(kBarVEmpty + st));
                 umma_commit(bar(kBarOFull));
             }
             if (!ok) { *abort_flag = 1; atomicMax(&g_attn5_error, 3u); }
@@ -267,7 +278,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         float m_used = -INFINITY, l_run = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
-            ok = mbar_wait(bar(kBarSFull), j & 1, abort_flag);
+            const int st = j & 1;
+            const uint32_t tmem_sj = tmem_s + (uint32_t)st * kBN + lane_addr;
+            ok = mbar_wait(bar(kBarSFull + st), (j >> 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             fence_after();
@@ -277,7 +290,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // the whole row of S into registers: four loads in flight, one wait
             uint32_t v[kBN];
 #pragma unroll
-            for (int c = 0; c < kBN; c += 32) tmem_ld32_nowait(tmem_s + lane_addr + c, *reinterpret_cast<uint32_t(*)[32]>(&v[c]));
+            for (int c = 0; c < kBN; c += 32) tmem_ld32_nowait(tmem_sj + c, *reinterpret_cast<uint32_t(*)[32]>(&v[c]));
             tmem_wait_ld();
 #pragma unroll
             for (int c = 0; c < kBN; c += 32) tmem_landed(*reinterpret_cast<uint32_t(*)[32]>(&v[c]));
@@ -288,9 +301,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     if (!(key <= pos && (window <= 0 || key > pos - window))) v[i] = __float_as_uint(-INFINITY);
                 }
             }
-            float tmax = -INFINITY;
+            float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < kBN; ++i) tmax = fmaxf(tmax, __uint_as_float(v[i]));
+            for (int i = 0; i < kBN; i += 4) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) tm[e] = fmaxf(tm[e], __uint_as_float(v[i + e]));
+            }
+            const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
             // move the maximum only when it grew by more than the lazy threshold
             float corr = 1.0f;
             if ((tmax - m_used) * sl2 > kLazyRescale) {      // also the first visible key: m_used = -inf
@@ -312,11 +329,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     l1 += p1;
                     p[i >> 1] = pack_bf16x2(p0, p1);
                 }
-                tmem_st16(tmem_s + lane_addr + (c >> 1), p);
+                tmem_st16(tmem_sj + (c >> 1), p);
             }
             l_run += l0 + l1;
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                // S[j] is complete, so O += P[j-1] V[j-1] has retired too: O may be rescaled in place
+                // O is rescaled in place once O += P[j-1] V[j-1] has retired (O += P[j] V[j] waits for this warp)
+                ok = mbar_wait(bar(kBarOFull), (j - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                fence_after();
 #pragma unroll 1
                 for (int c = 0; c < kD; c += 32) {
                     uint32_t o[32];
@@ -329,7 +350,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tmem_wait_st();
             fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(kBarPFull));
+            if (lane == 0) mbar_arrive(bar(kBarPFull + st));
         }
         if (ok) {
             ok = mbar_wait(bar(kBarOFull), (n_tiles - 1) & 1, abort_flag);
@@ -341,15 +362,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             bf16* dst = out + ((size_t)(q0 + m0 + r) * Hq + head) * kD;
 #pragma unroll 1
             for (int c = 0; c < kD; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(tmem_o + lane_addr + c, v);
+                uint32_t o[32];
+                tmem_ld32(tmem_o + lane_addr + c, o);
                 if (r < rows) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint32_t w[4];
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            w[k] = pack_bf16x2(__uint_as_float(v[i * 8 + 2 * k]) * inv, __uint_as_float(v[i * 8 + 2 * k + 1]) * inv);
+                            w[k] = pack_bf16x2(__uint_as_float(o[i * 8 + 2 * k]) * inv, __uint_as_float(o[i * 8 + 2 * k + 1]) * inv);
                         reinterpret_cast<uint4*>(dst + c)[i] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
@@ -365,7 +386,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     fence_before();
     __syncthreads();
-    if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
+    if (warp == 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
 }
 
 // Row-major [rows, cols] bfloat16 matrix, boxes of box_rows x 64 columns, 128-byte swizzle, zero fill outside.
