@@ -1,19 +1,23 @@
 // Paged attention for prompt portions on the fifth-generation tensor cores: causal, ragged
 // batch, optional window, grouped heads, bfloat16 pages, head size 128.
 //
-// One block per (tile of 128 query tokens of one sequence, query head), one block per SM (160 KB of
-// shared memory, all 512 tensor-memory columns: two S tiles and O).  Roles inside a block:
+// A persistent grid of one block per SM (192 KB of shared memory, all 512 tensor-memory columns: two
+// S tiles and two O tiles) walks over work items, each a tile of 128 query tokens of one sequence
+// and one query head.  Roles inside a block:
 //   warps 0-3   softmax: thread r owns query row r (tensor-memory lane r).  It reads its row of
 //               S = Q K^T from tensor memory (tcgen05.ld), keeps the running maximum and sum in
 //               float32, writes P = 2^(s*c - m*c) rounded to bfloat16 back over the first half
-//               of S's columns (tcgen05.st), and at the end normalises and stores its row of O;
+//               of S's columns (tcgen05.st), and at the item's end normalises and stores its row of O;
 //   warp 4      one thread issues the MMAs: S = Q K^T (operands in shared memory, eight
 //               tcgen05.mma of K 16), and O += P V with P read from tensor memory and V as an
 //               MN-major operand straight from the page layout (keys along K);
-//   warps 5-7   TMA producers: the query tile once, then per tile of 128 keys the pages that the
+//   warps 5-7   TMA producers: an item's query tile, then per tile of 128 keys the pages that the
 //               block table names, each as two boxes of [page x 64] into 128-byte-swizzled
 //               tiles, two stages each for K and V.  A warp issues the copies of its lanes one
 //               after the other, so a tile's boxes are dealt out over the three warps.
+// The roles run ahead of one another across items: the producers load the next item's Q, K and V
+// while the current one is computed (two Q buffers), and O has two buffers, so that the next item's
+// products start while the softmax warps still write the last item's output.
 // S has two buffers: S[j+1] is issued before O += P[j] V[j], so that it is complete when the
 // softmax warps finish tile j, and the tensor core works on tile j+1 and on P[j] V[j] while they
 // compute tile j+1's exponentials.
@@ -48,8 +52,8 @@ constexpr int kProducers = 3;
 constexpr int kHalfBytes = 128 * 64 * 2;       // one [128 x 64] swizzled half tile: 16 KB
 constexpr int kTileBytes = 2 * kHalfBytes;     // 32 KB
 constexpr int kStages = 2;                     // K and V tiles in flight
-constexpr int kSmemBytes = (1 + 2 * kStages) * kTileBytes + 1024 /* alignment slack */ + 256 /* barriers */;
-constexpr int kTmemColumns = 512;              // S[0] | S[1] (P over the first 64 of each) | O
+constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int kTmemColumns = 512;              // S[0] | S[1] (P over the first 64 of each) | O[0] | O[1]
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLazyRescale = 8.0f;           // move the maximum when it grew by more than 2^8
 
@@ -121,57 +125,86 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Barrier slots; those of K, V, S and P exist once per stage.
-enum { kBarQ = 0, kBarOFull, kBarKFull, kBarKEmpty = kBarKFull + kStages, kBarVFull = kBarKEmpty + kStages,
-       kBarVEmpty = kBarVFull + kStages, kBarSFull = kBarVEmpty + kStages, kBarPFull = kBarSFull + 2, kNumBars = kBarPFull + 2 };
+// Barrier slots; those of K and V exist once per stage, those of Q, S, P and O once per buffer.
+enum { kBarOFull = 0, kBarQFull, kBarQEmpty = kBarQFull + 2, kBarOEmpty = kBarQEmpty + 2, kBarSFull = kBarOEmpty + 2,
+       kBarPFull = kBarSFull + 2, kBarKFull = kBarPFull + 2, kBarKEmpty = kBarKFull + kStages,
+       kBarVFull = kBarKEmpty + kStages, kBarVEmpty = kBarVFull + kStages, kNumBars = kBarVEmpty + kStages };
 
-__global__ void __launch_bounds__(kThreads, 1)
-prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
-                       const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
-                       const int* __restrict__ kv_len, int n_seqs, int Hq, int Hkv, int page_shift, int rows_per_load,
-                       float scale, int window) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_s = smem;
-    unsigned char* k_s = smem + kTileBytes;                    // kStages tiles
-    unsigned char* v_s = smem + (1 + kStages) * kTileBytes;    // kStages tiles
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (1 + 2 * kStages) * kTileBytes);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+struct Args {
+    bf16* out;
+    const int* block_table;
+    const int* cu_q;
+    const int* kv_len;
+    int table_stride, n_seqs, n_items, Hq, Hkv, page_shift, rows_per_load, window;
+    float scale;
+};
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int head = blockIdx.x;
-    const int kvh = head / (Hq / Hkv);
+// One work item: a tile of 128 query rows of one sequence and one query head.  Every role of a block
+// walks the same list of items: item k of block b is number k*G + b (k even) or k*G + G-1-b (k odd) of
+// the grid's G blocks, the items being numbered with the head fastest and the tiles backwards (longest
+// key ranges first), so that each block gets about the same number of key tiles.
+struct Work {
+    int t;                     // items of this block so far
+    int head, kvh, q_row0, rows, pos_first, pos_last, lo, kt0, n_tiles;
+    const int* table;
+};
 
-    // Which sequence and which of its query tiles.  Heads are the fast grid index and the tiles run
-    // backwards, so that the tiles with the longest key ranges (ends of long portions) start first.
-    int tile = gridDim.y - 1 - blockIdx.y;
+__device__ __forceinline__ bool next_item(Work& w, const Args& a) {
+    const int k = w.t;
+    const int G = gridDim.x, b = blockIdx.x;
+    const int idx = k * G + ((k & 1) ? G - 1 - b : b);
+    if (idx >= a.n_items) return false;
+    const int n_q_tiles = a.n_items / a.Hq;
+    w.head = idx % a.Hq;
+    w.kvh = w.head / (a.Hq / a.Hkv);
+    int tile = n_q_tiles - 1 - idx / a.Hq;
     int s = 0, q0 = 0, q_len = 0;
-    for (; s < n_seqs; ++s) {
-        q0 = cu_q[s];
-        q_len = cu_q[s + 1] - q0;
+    for (; s < a.n_seqs; ++s) {
+        q0 = a.cu_q[s];
+        q_len = a.cu_q[s + 1] - q0;
         const int nt = (q_len + kBM - 1) / kBM;
         if (tile < nt) break;
         tile -= nt;
     }
-    if (s >= n_seqs) return;
+    if (s >= a.n_seqs) return false;                            // the caller's tile count does not match cu_q
     const int m0 = tile * kBM;
-    const int rows = min(kBM, q_len - m0);
-    const int ctx0 = kv_len[s] - q_len;
-    const int pos_first = ctx0 + m0, pos_last = ctx0 + m0 + rows - 1;
-    const int lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
-    const int kt0 = lo / kBN, n_tiles = pos_last / kBN - kt0 + 1;
-    const int* table = block_table + (size_t)s * table_stride;
+    w.rows = min(kBM, q_len - m0);
+    w.q_row0 = q0 + m0;
+    const int ctx0 = a.kv_len[s] - q_len;
+    w.pos_first = ctx0 + m0;
+    w.pos_last = ctx0 + m0 + w.rows - 1;
+    w.lo = (a.window > 0 && w.pos_first - a.window + 1 > 0) ? w.pos_first - a.window + 1 : 0;
+    w.kt0 = w.lo / kBN;
+    w.n_tiles = w.pos_last / kBN - w.kt0 + 1;
+    w.table = a.block_table + (size_t)s * a.table_stride;
+    w.t = k + 1;
+    return true;
+}
 
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const Args a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = smem;                                 // two tiles
+    unsigned char* k_s = smem + 2 * kTileBytes;                // kStages tiles
+    unsigned char* v_s = smem + (2 + kStages) * kTileBytes;    // kStages tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * kStages) * kTileBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t bar0 = smem_addr(bars);
     auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     // V's buffers start finite (see the header); 16 bytes per thread and step.
     for (int i = tid; i < kStages * kTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
     if (tid == 0) {
-        for (int i = 0; i < kNumBars; ++i)
-            mbar_init(bar(i), i >= kBarPFull ? 4 : (i >= kBarKFull && i < kBarKEmpty) || (i >= kBarVFull && i < kBarVEmpty) ? kProducers : 1);
+        for (int i = 0; i < kNumBars; ++i) {
+            const bool from_softmax = (i >= kBarPFull && i < kBarPFull + 2) || (i >= kBarOEmpty && i < kBarOEmpty + 2);
+            const bool from_producers = (i >= kBarKFull && i < kBarKEmpty) || (i >= kBarVFull && i < kBarVEmpty);
+            mbar_init(bar(i), from_softmax ? 4 : from_producers ? kProducers : 1);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -184,198 +217,247 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kBN;      // S[0] | S[1] | O
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kBN;      // S[0] | S[1] | O[0] | O[1]
 
     if (warp >= 5) {
         // ---------------- TMA producers: a tile's boxes are dealt out over the lanes of three warps (a warp issues
         // the copies of its lanes one after the other, so few lanes per warp keep a tile's issue time short)
         const int pw = warp - 5;
-        if (pw == 0 && lane == 0) {
-            mbar_expect_tx(bar(kBarQ), kTileBytes);
-            tma_load_2d(smem_addr(q_s), &map_q, bar(kBarQ), head * kD, q0 + m0);
-            tma_load_2d(smem_addr(q_s) + kHalfBytes, &map_q, bar(kBarQ), head * kD + 64, q0 + m0);
-        }
-        const int loads = kBN / rows_per_load;                 // pages (or parts of a page) per tile
-        const uint32_t load_bytes = (uint32_t)rows_per_load * 128u;
+        const int loads = kBN / a.rows_per_load;               // pages (or parts of a page) per tile
+        const uint32_t load_bytes = (uint32_t)a.rows_per_load * 128u;
         const int box = pw + kProducers * lane;                // box -> (page slot, half)
         const int slot = box >> 1, half = box & 1;
         bool ok = true;
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            const int key0 = (kt0 + j) * kBN;
-            const int st = j % kStages;
-            const uint32_t free_parity = ((j / kStages) & 1) ^ 1;
-            const int key = key0 + slot * rows_per_load;
-            const bool want = slot < loads && key + rows_per_load > lo && key <= pos_last;
-            int row = 0;
-            if (want) {
-                const int page = table[key >> page_shift];
-                row = ((page * Hkv + kvh) << page_shift) + (key & ((1 << page_shift) - 1));
+        uint32_t g = 0;                                        // key tiles so far, over all items
+        Work w;
+        w.t = 0;
+        while (ok && next_item(w, a)) {
+            const int t = w.t - 1, qb = t & 1;
+            if (pw == 0) {
+                if (lane == 0) {
+                    ok = mbar_wait(bar(kBarQEmpty + qb), ((t >> 1) & 1) ^ 1, abort_flag);      // the item before last has used it
+                    if (ok) {
+                        const uint32_t dst = smem_addr(q_s) + (uint32_t)qb * kTileBytes;
+                        mbar_expect_tx(bar(kBarQFull + qb), kTileBytes);
+                        tma_load_2d(dst, &map_q, bar(kBarQFull + qb), w.head * kD, w.q_row0);
+                        tma_load_2d(dst + kHalfBytes, &map_q, bar(kBarQFull + qb), w.head * kD + 64, w.q_row0);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
             }
-            const uint32_t n_want = __popc(__ballot_sync(0xffffffffu, want));
-            const uint32_t dst_off = (uint32_t)st * kTileBytes + (uint32_t)half * kHalfBytes + (uint32_t)(slot * rows_per_load) * 128u;
-            // K[j]: when S[j - kStages] has read the stage
-            if (lane == 0) {
-                ok = mbar_wait(bar(kBarKEmpty + st), free_parity, abort_flag);
-                if (ok) mbar_expect_tx(bar(kBarKFull + st), n_want * load_bytes);
+            for (int j = 0; j < w.n_tiles && ok; ++j, ++g) {
+                const int key0 = (w.kt0 + j) * kBN;
+                const int st = g % kStages;
+                const uint32_t free_parity = ((g / kStages) & 1) ^ 1;
+                const int key = key0 + slot * a.rows_per_load;
+                const bool want = slot < loads && key + a.rows_per_load > w.lo && key <= w.pos_last;
+                int row = 0;
+                if (want) {
+                    const int page = w.table[key >> a.page_shift];
+                    row = ((page * a.Hkv + w.kvh) << a.page_shift) + (key & ((1 << a.page_shift) - 1));
+                }
+                const uint32_t n_want = __popc(__ballot_sync(0xffffffffu, want));
+                const uint32_t dst_off = (uint32_t)st * kTileBytes + (uint32_t)half * kHalfBytes + (uint32_t)(slot * a.rows_per_load) * 128u;
+                // K: when the S product that read the stage last has retired
+                if (lane == 0) {
+                    ok = mbar_wait(bar(kBarKEmpty + st), free_parity, abort_flag);
+                    if (ok) mbar_expect_tx(bar(kBarKFull + st), n_want * load_bytes);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                if (want) tma_load_2d(smem_addr(k_s) + dst_off, &map_k, bar(kBarKFull + st), half * 64, row);
+                // V: when the P V product that read the stage last has retired
+                if (lane == 0) {
+                    ok = mbar_wait(bar(kBarVEmpty + st), free_parity, abort_flag);
+                    if (ok) mbar_expect_tx(bar(kBarVFull + st), n_want * load_bytes);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                if (want) tma_load_2d(smem_addr(v_s) + dst_off, &map_v, bar(kBarVFull + st), half * 64, row);
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            if (want) tma_load_2d(smem_addr(k_s) + dst_off, &map_k, bar(kBarKFull + st), half * 64, row);
-            // V[j]: when O += P V of tile j - kStages has read the stage
-            if (lane == 0) {
-                ok = mbar_wait(bar(kBarVEmpty + st), free_parity, abort_flag);
-                if (ok) mbar_expect_tx(bar(kBarVFull + st), n_want * load_bytes);
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            if (want) tma_load_2d(smem_addr(v_s) + dst_off, &map_v, bar(kBarVFull + st), half * 64, row);
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_attn5_error, 2u); }
     } else if (warp == 4) {
-        // ---------------- MMA issuer: S[0]; then per tile S[j+1] (so that it is ready when softmax j ends) and O += P[j] V[j].
-        // S[j+1] overwrites the columns that held S[j-1] and P[j-1]: O += P[j-1] V[j-1] was issued before it, and
-        // the MMAs of one thread run in the order of their issue.
+        // ---------------- MMA issuer.  Two cursors walk the block's key tiles: S is issued one tile ahead of
+        // O += P V (also across items), so that the next S is complete when the softmax warps finish a tile.
+        // S of tile g+1 overwrites the columns that held S and P of tile g-1: O += P V of tile g-1 was issued
+        // before it, and the MMAs of one thread run in the order of their issue.
         if (lane == 0) {
             const uint32_t q_addr = smem_addr(q_s), k_addr = smem_addr(k_s), v_addr = smem_addr(v_s);
-            auto issue_s = [&](int j) -> bool {
-                const int st = j % kStages, sb = j & 1;
-                if (!mbar_wait(bar(kBarKFull + st), (j / kStages) & 1, abort_flag)) return false;
+            Work ws, wp;                                       // the items of the S cursor and of the P V cursor
+            ws.t = wp.t = 0;
+            int js = 0, jp = 0;                                // tile within the item
+            uint32_t gs = 0, gp = 0;                           // tile over all items
+            bool more_s = next_item(ws, a), more_p = next_item(wp, a);
+            bool ok = true;
+            auto issue_s = [&]() -> bool {
+                const int t = ws.t - 1, qb = t & 1;
+                const int st = gs % kStages, sb = gs & 1;
+                if (js == 0 && !mbar_wait(bar(kBarQFull + qb), (t >> 1) & 1, abort_flag)) return false;
+                if (!mbar_wait(bar(kBarKFull + st), (gs / kStages) & 1, abort_flag)) return false;
                 fence_after();
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
                     const uint32_t off = (uint32_t)(ks >> 2) * kHalfBytes + (uint32_t)(ks & 3) * 32u;
-                    umma_ss(tmem_s + (uint32_t)sb * kBN, desc_k_major(q_addr + off),
+                    umma_ss(tmem_s + (uint32_t)sb * kBN, desc_k_major(q_addr + (uint32_t)qb * kTileBytes + off),
                             desc_k_major(k_addr + (uint32_t)st * kTileBytes + off), kIdescS, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(kBarKEmpty + st));
                 umma_commit(bar(kBarSFull + sb));
+                ++js;
+                ++gs;
+                if (js == ws.n_tiles) {                        // the item's last S: its Q buffer is free once it has retired
+                    umma_commit(bar(kBarQEmpty + qb));
+                    js = 0;
+                    more_s = next_item(ws, a);
+                }
                 return true;
             };
-            bool ok = mbar_wait(bar(kBarQ), 0, abort_flag);
-            ok = ok && issue_s(0);
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int st = j % kStages, sb = j & 1;
-                if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
-                if (!mbar_wait(bar(kBarVFull + st), (j / kStages) & 1, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(bar(kBarPFull + sb), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+            if (more_s) ok = issue_s();
+            while (ok && more_p) {
+                if (more_s && !issue_s()) { ok = false; break; }
+                const int t = wp.t - 1, ob = t & 1;
+                const int st = gp % kStages, sb = gp & 1;
+                // the item before last has been read out of this O buffer
+                if (jp == 0 && !mbar_wait(bar(kBarOEmpty + ob), ((t >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(bar(kBarVFull + st), (gp / kStages) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(bar(kBarPFull + sb), (gp >> 1) & 1, abort_flag)) { ok = false; break; }
                 fence_after();
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk)
-                    umma_ts(tmem_o, tmem_s + (uint32_t)sb * kBN + (uint32_t)kk * 8u,
+                    umma_ts(tmem_o + (uint32_t)ob * kD, tmem_s + (uint32_t)sb * kBN + (uint32_t)kk * 8u,
                             desc_mn_major(v_addr + (uint32_t)st * kTileBytes + (uint32_t)kk * 2048u), kIdescPV,
-                            (j > 0 || kk > 0) ? 1u : 0u);
+                            (jp > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(bar(kBarVEmpty + st));
                 umma_commit(bar(kBarOFull));
+                ++jp;
+                ++gp;
+                if (jp == wp.n_tiles) {
+                    jp = 0;
+                    more_p = next_item(wp, a);
+                }
             }
             if (!ok) { *abort_flag = 1; atomicMax(&g_attn5_error, 3u); }
         }
     } else {
         // ---------------- softmax: thread `r` owns query row r
         const int r = warp * 32 + lane;
-        const int pos = pos_first + min(r, rows - 1);             // rows beyond the tile's end repeat the last one
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-        const float sl2 = scale * kLog2e;
-        float m_used = -INFINITY, l_run = 0.0f;
+        const float sl2 = a.scale * kLog2e;
+        const int window = a.window;
         bool ok = true;
-        for (int j = 0; j < n_tiles; ++j) {
-            const int st = j & 1;
-            const uint32_t tmem_sj = tmem_s + (uint32_t)st * kBN + lane_addr;
-            ok = mbar_wait(bar(kBarSFull + st), (j >> 1) & 1, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            fence_after();
-            const int key0 = (kt0 + j) * kBN;
-            // every row of the block sees every key of the tile?
-            const bool all_visible = key0 + kBN - 1 <= pos_first && (window <= 0 || key0 > pos_last - window);
-            // the whole row of S into registers: four loads in flight, one wait
-            uint32_t v[kBN];
-#pragma unroll
-            for (int c = 0; c < kBN; c += 32) tmem_ld32_nowait(tmem_sj + c, *reinterpret_cast<uint32_t(*)[32]>(&v[c]));
-            tmem_wait_ld();
-#pragma unroll
-            for (int c = 0; c < kBN; c += 32) tmem_landed(*reinterpret_cast<uint32_t(*)[32]>(&v[c]));
-            if (!all_visible) {
-#pragma unroll
-                for (int i = 0; i < kBN; ++i) {
-                    const int key = key0 + i;
-                    if (!(key <= pos && (window <= 0 || key > pos - window))) v[i] = __float_as_uint(-INFINITY);
-                }
-            }
-            float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int i = 0; i < kBN; i += 4) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) tm[e] = fmaxf(tm[e], __uint_as_float(v[i + e]));
-            }
-            const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
-            // move the maximum only when it grew by more than the lazy threshold
-            float corr = 1.0f;
-            if ((tmax - m_used) * sl2 > kLazyRescale) {      // also the first visible key: m_used = -inf
-                corr = ex2((m_used - tmax) * sl2);            // 0 when m_used = -inf
-                m_used = tmax;
-                l_run *= corr;
-            }
-            const float neg_ms = (m_used == -INFINITY) ? 0.0f : -m_used * sl2;
-            // P over the first half of S's columns
-            float l0 = 0.0f, l1 = 0.0f;
-#pragma unroll
-            for (int c = 0; c < kBN; c += 32) {
-                uint32_t p[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2(fmaf(__uint_as_float(v[c + i]), sl2, neg_ms));
-                    const float p1 = ex2(fmaf(__uint_as_float(v[c + i + 1]), sl2, neg_ms));
-                    l0 += p0;
-                    l1 += p1;
-                    p[i >> 1] = pack_bf16x2(p0, p1);
-                }
-                tmem_st16(tmem_sj + (c >> 1), p);
-            }
-            l_run += l0 + l1;
-            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                // O is rescaled in place once O += P[j-1] V[j-1] has retired (O += P[j] V[j] waits for this warp)
-                ok = mbar_wait(bar(kBarOFull), (j - 1) & 1, abort_flag);
+        uint32_t g = 0;
+        Work w;
+        w.t = 0;
+        while (ok && next_item(w, a)) {
+            const int t = w.t - 1, ob = t & 1;
+            const int pos = w.pos_first + min(r, w.rows - 1);     // rows beyond the tile's end repeat the last one
+            const uint32_t tmem_ot = tmem_o + (uint32_t)ob * kD + lane_addr;
+            float m_used = -INFINITY, l_run = 0.0f;
+            for (int j = 0; j < w.n_tiles; ++j, ++g) {
+                const int sb = g & 1;
+                const uint32_t tmem_sj = tmem_s + (uint32_t)sb * kBN + lane_addr;
+                ok = mbar_wait(bar(kBarSFull + sb), (g >> 1) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 fence_after();
-#pragma unroll 1
-                for (int c = 0; c < kD; c += 32) {
-                    uint32_t o[32];
-                    tmem_ld32(tmem_o + lane_addr + c, o);
+                const int key0 = (w.kt0 + j) * kBN;
+                // every row of the block sees every key of the tile?
+                const bool all_visible = key0 + kBN - 1 <= w.pos_first && (window <= 0 || key0 > w.pos_last - window);
+                // the whole row of S into registers: four loads in flight, one wait
+                uint32_t v[kBN];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                    tmem_st32(tmem_o + lane_addr + c, o);
+                for (int c = 0; c < kBN; c += 32) tmem_ld32_nowait(tmem_sj + c, *reinterpret_cast<uint32_t(*)[32]>(&v[c]));
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < kBN; c += 32) tmem_landed(*reinterpret_cast<uint32_t(*)[32]>(&v[c]));
+                if (!all_visible) {
+#pragma unroll
+                    for (int i = 0; i < kBN; ++i) {
+                        const int key = key0 + i;
+                        if (!(key <= pos && (window <= 0 || key > pos - window))) v[i] = __float_as_uint(-INFINITY);
+                    }
                 }
+                float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < kBN; i += 4) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) tm[e] = fmaxf(tm[e], __uint_as_float(v[i + e]));
+                }
+                const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+                // move the maximum only when it grew by more than the lazy threshold
+                float corr = 1.0f;
+                if ((tmax - m_used) * sl2 > kLazyRescale) {      // also the first visible key: m_used = -inf
+                    corr = ex2((m_used - tmax) * sl2);            // 0 when m_used = -inf
+                    m_used = tmax;
+                    l_run *= corr;
+                }
+                const float neg_ms = (m_used == -INFINITY) ? 0.0f : -m_used * sl2;
+                // P over the first half of S's columns
+                float l0 = 0.0f, l1 = 0.0f;
+#pragma unroll
+                for (int c = 0; c < kBN; c += 32) {
+                    uint32_t p[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = ex2(fmaf(__uint_as_float(v[c + i]), sl2, neg_ms));
+                        const float p1 = ex2(fmaf(__uint_as_float(v[c + i + 1]), sl2, neg_ms));
+                        l0 += p0;
+                        l1 += p1;
+                        p[i >> 1] = pack_bf16x2(p0, p1);
+                    }
+                    tmem_st16(tmem_sj + (c >> 1), p);
+                }
+                l_run += l0 + l1;
+                if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                    // O is rescaled in place once O += P V of the tile before has retired (that of this tile waits
+                    // for this warp's P)
+                    ok = mbar_wait(bar(kBarOFull), (g - 1) & 1, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < kD; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_ot + c, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                        tmem_st32(tmem_ot + c, o);
+                    }
+                }
+                tmem_wait_st();
+                fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kBarPFull + sb));
             }
-            tmem_wait_st();
-            fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(kBarPFull + st));
-        }
-        if (ok) {
-            ok = mbar_wait(bar(kBarOFull), (n_tiles - 1) & 1, abort_flag);
+            if (!ok) break;
+            // the item's output: O of its last tile has retired
+            ok = mbar_wait(bar(kBarOFull), (g - 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok) {
+            if (!ok) break;
             fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            bf16* dst = out + ((size_t)(q0 + m0 + r) * Hq + head) * kD;
+            bf16* dst = a.out + ((size_t)(w.q_row0 + r) * a.Hq + w.head) * kD;
 #pragma unroll 1
             for (int c = 0; c < kD; c += 32) {
                 uint32_t o[32];
-                tmem_ld32(tmem_o + lane_addr + c, o);
-                if (r < rows) {
+                tmem_ld32(tmem_ot + c, o);
+                if (r < w.rows) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        uint32_t w[4];
+                        uint32_t x[4];
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            w[k] = pack_bf16x2(__uint_as_float(o[i * 8 + 2 * k]) * inv, __uint_as_float(o[i * 8 + 2 * k + 1]) * inv);
-                        reinterpret_cast<uint4*>(dst + c)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                            x[k] = pack_bf16x2(__uint_as_float(o[i * 8 + 2 * k]) * inv, __uint_as_float(o[i * 8 + 2 * k + 1]) * inv);
+                        reinterpret_cast<uint4*>(dst + c)[i] = make_uint4(x[0], x[1], x[2], x[3]);
                     }
                 }
             }
-        } else if (lane == 0) {
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kBarOEmpty + ob));       // this warp's lanes of the O buffer may be overwritten
+        }
+        if (!ok && lane == 0) {
             *abort_flag = 1;
             atomicMax(&g_attn5_error, 4u);
         }
@@ -401,6 +483,15 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return rc == CUDA_SUCCESS ? 0 : PB_ERR_BAD_SIZE;
+}
+
+int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) v = 0;
+        return v > 0 ? v : 148;
+    }();
+    return n;
 }
 
 int log2_exact(int v) {
@@ -438,7 +529,8 @@ PB_EXPORT int pb_paged_attention_prefill_tcgen05(int dtype, const void* q, const
                                                  cudaStream_t stream) {
     if (n_seqs <= 0 || n_q_tiles <= 0 || n_tokens <= 0) return 0;
     if (!pb_prefill_tcgen05_supported(dtype, Hq, Hkv, D, page_size)) return PB_ERR_BAD_SIZE;
-    if (n_q_tiles > 65535) return PB_ERR_TOO_LARGE;
+    const long long items = (long long)n_q_tiles * Hq;
+    if (items >= (1LL << 30)) return PB_ERR_TOO_LARGE;
     if ((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) != 0) return PB_ERR_BAD_SIZE;
     const long long pool_rows = (long long)n_pages * Hkv * page_size;
     if (pool_rows >= (1LL << 31)) return PB_ERR_TOO_LARGE;
@@ -456,9 +548,21 @@ PB_EXPORT int pb_paged_attention_prefill_tcgen05(int dtype, const void* q, const
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(Hq, n_q_tiles);
-    prefill_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, (bf16*)out, block_table, table_stride, cu_q, kv_len,
-                                                                  n_seqs, Hq, Hkv, log2_exact(page_size), rows_per_load, scale,
-                                                                  window);
+    Args a;
+    a.out = (bf16*)out;
+    a.block_table = block_table;
+    a.cu_q = cu_q;
+    a.kv_len = kv_len;
+    a.table_stride = table_stride;
+    a.n_seqs = n_seqs;
+    a.n_items = (int)items;
+    a.Hq = Hq;
+    a.Hkv = Hkv;
+    a.page_shift = log2_exact(page_size);
+    a.rows_per_load = rows_per_load;
+    a.window = window;
+    a.scale = scale;
+    const int grid = (int)(items < sm_count() ? items : sm_count());       // persistent: one block per SM
+    prefill_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, a);
     return launch_status();
 }
