@@ -126,7 +126,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 // Barrier slots; those of K and V exist once per stage, those of Q, S, P and O once per buffer.
-enum { kBarOFull = 0, kBarQFull, kBarQEmpty = kBarQFull + 2, kBarOEmpty = kBarQEmpty + 2, kBarSFull = kBarOEmpty + 2,
+enum { kBarOFull = 0, kBarODone, kBarQFull, kBarQEmpty = kBarQFull + 2, kBarOEmpty = kBarQEmpty + 2, kBarSFull = kBarOEmpty + 2,
        kBarPFull = kBarSFull + 2, kBarKFull = kBarPFull + 2, kBarKEmpty = kBarKFull + kStages,
        kBarVFull = kBarKEmpty + kStages, kBarVEmpty = kBarVFull + kStages, kNumBars = kBarVEmpty + kStages };
 
@@ -333,6 +333,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 ++jp;
                 ++gp;
                 if (jp == wp.n_tiles) {
+                    umma_commit(bar(kBarODone));               // the item's O is complete once everything issued so far has retired
                     jp = 0;
                     more_p = next_item(wp, a);
                 }
@@ -431,8 +432,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (lane == 0) mbar_arrive(bar(kBarPFull + sb));
             }
             if (!ok) break;
-            // the item's output: O of its last tile has retired
-            ok = mbar_wait(bar(kBarOFull), (g - 1) & 1, abort_flag);
+            // the item's output: O of its last tile has retired.  (A barrier of its own: a warp whose rows see nothing of
+            // the last tiles gets here while kBarOFull is still two phases behind, which a parity cannot tell from none.)
+            ok = mbar_wait(bar(kBarODone), t & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             fence_after();
