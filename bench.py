@@ -196,19 +196,25 @@ def time_e2e(engine, batch: int, context: int, steps: int, warmup: int):
     started = set()
     while len(started) < batch:                   # prompts in portions until every request has its first token
         started.update(sid for sid, _, _ in engine.step(1))
-    for _ in range(warmup):
-        engine.step(batch)
+    for i in range(warmup):
+        engine.step(batch, lookahead=i + 1 < warmup)
     torch.cuda.synchronize()
+    # Engine.step keeps one pass ahead of the tokens it returns: a call reads the ids of the pass that the call
+    # before it launched and launches the next one, whose input tokens are those ids, taken on the device.  Nothing
+    # is in flight when the clock starts, and the last call launches nothing more: exactly `steps` passes are launched
+    # and read inside the timed region, each with its host->device copy of index arrays and its device->host read.
     h2d0 = engine.runner.h2d_bytes
+    forwards0 = engine.forwards
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     wall0 = time.perf_counter()
     t0.record()
     got = 0
-    for _ in range(steps):
-        got += len(engine.step_once())
+    for i in range(steps):
+        got += len(engine.step(batch, lookahead=i + 1 < steps))
     t1.record()
     torch.cuda.synchronize()
     wall = time.perf_counter() - wall0
+    assert engine.forwards - forwards0 == steps, (engine.forwards - forwards0, steps)
     assert got == batch * steps, (got, batch, steps)
     h2d = (engine.runner.h2d_bytes - h2d0) / steps
     for sid in sids:

@@ -367,7 +367,23 @@ int block_for(int width) {
     return b;
 }
 
+// ids[dst[i]] = src_ids[src[i]]: token ids that an earlier step sampled go straight into this step's
+// ids without passing through the host.
+__global__ void move_ids_kernel(int* __restrict__ ids, const int* __restrict__ dst, const int* __restrict__ src,
+                                const int* __restrict__ src_ids, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) ids[dst[i]] = src_ids[src[i]];
+}
+
 }  // namespace
+
+// ids[dst[i]] = src_ids[src[i]] for i < n.  (The reference reads every sampled token back to the host and sends
+// it down again with the next step: pulsar-core/src/runtime/engine.cpp:703-729, 573-600.)
+PB_EXPORT int pb_move_ids(int* ids, const int* dst, const int* src, const int* src_ids, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    move_ids_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, dst, src, src_ids, n);
+    return launch_status();
+}
 
 PB_EXPORT int pb_embed(int dtype, const void* table, const int* ids, float* out, int n, int width, int vocab,
                        cudaStream_t stream) {

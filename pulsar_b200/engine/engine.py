@@ -8,7 +8,7 @@ nothing is active, a finished sequence is parked with its pages kept until ``rel
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
@@ -18,7 +18,7 @@ from ..config.engine_config import EngineConfig
 from ..sampling.sampler import GenerationParams, Sampler, make_generator
 from .loading import load_model, torch_dtype
 from .runner import ModelRunner, StepEntry
-from .scheduler import Scheduler, SchedulerError
+from .scheduler import UNREAD, Scheduled, Scheduler, SchedulerError
 
 
 @dataclass
@@ -29,6 +29,17 @@ class _Session:
     budget: int                   # new tokens allowed in the current turn
     state: str = "idle"           # "idle", "active", "parked"
     scheduled: bool = False       # known to the scheduler
+
+
+@dataclass
+class _Inflight:
+    """A forward pass whose sampled ids are on their way to the host."""
+    sampled: List[int]                     # sequences sampled in it, in the order of its rows
+    row_of: Dict[int, int]
+    host: torch.Tensor                     # pinned; filled when ``event`` has passed
+    event: torch.cuda.Event
+    generator_states: Dict[int, torch.Tensor]      # of stochastic sequences, before their draw
+    void: set = field(default_factory=set)         # sequences that had ended before this pass: its token is dropped
 
 
 class Engine:
@@ -81,6 +92,10 @@ class Engine:
         self._next_id = 0
         self.forwards = 0
         self._mailbox: Dict[int, list] = {}     # events of other sessions seen while one session streams
+        self._inflight: Optional[_Inflight] = None          # the pass whose tokens have not been read yet
+        self._unclaimed: List[Tuple[int, int, bool]] = []   # events booked outside ``step``
+        self._host_ids: List[Optional[torch.Tensor]] = [None, None, None]
+        self._host_next = 0
 
     # ------------------------------------------------------------------ sessions
     def _params(self, overrides: Optional[Dict[str, Any]]) -> GenerationParams:
@@ -116,6 +131,7 @@ class Engine:
         """Add tokens to the sequence and schedule it; it will emit up to ``max_tokens``
         new tokens (default: the budget set before, else unlimited until eos)."""
         s = self._session(seq_id)
+        self._drain()                   # a pass in flight may still owe this sequence a token
         if s.state == "active":
             raise RuntimeError(f"sequence {seq_id} is still generating")
         if max_tokens is not None:
@@ -156,41 +172,116 @@ class Engine:
 
     # ------------------------------------------------------------------ stepping
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None or bool(self._unclaimed)
 
-    def step_once(self) -> List[Tuple[int, int, bool]]:
-        """One forward pass.  Returns the events ``(seq_id, token, finished)`` of the
-        sequences whose logits were sampled in it."""
-        plan = self.scheduler.schedule()
-        if not plan:
-            return []
-        entries = [StepEntry(e.rid, e.tokens, [len(e.tokens) - 1] if e.sample else []) for e in plan]
-        logits = self.runner.step(entries)
+    def _launch(self, plan: List[Scheduled]) -> "_Inflight":
+        """Put one forward pass and its sampling on the device and ask for the sampled ids;
+        nothing here waits for the device.  Tokens that the pass before it sampled, and that the
+        host has not read yet, are taken from that pass's ids on the device."""
+        before = self._inflight
+        entries = []
+        for e in plan:
+            src = None
+            tokens = e.tokens
+            if tokens[-1] == UNREAD:
+                if before is None or e.rid not in before.row_of or len(tokens) != 1:
+                    raise RuntimeError(f"sequence {e.rid}: an unread token outside a single-token entry")
+                src, tokens = before.row_of[e.rid], [0]
+            entries.append(StepEntry(e.rid, tokens, [len(tokens) - 1] if e.sample else [], src))
+        logits = self.runner.step(entries, self.sampler.last_ids if before is not None else None)
         self.forwards += 1
         self.scheduler.on_step(plan)
         sampled = [e.rid for e in plan if e.sample]
-        tokens = self.sampler.sample(logits, [self._sessions[r].params for r in sampled],
-                                     [self._sessions[r].generator for r in sampled])
+        sessions = [self._sessions[r] for r in sampled]
+        states = {r: s.generator.get_state() for r, s in zip(sampled, sessions) if not s.params.greedy}
+        ids = self.sampler.sample_on_device(logits, [s.params for s in sessions], [s.generator for s in sessions])
+        slot = self._host_ids[self._host_next]
+        if slot is None or slot.numel() < len(sampled):
+            slot = self._host_ids[self._host_next] = torch.empty(max(64, len(sampled)), dtype=torch.int32, pin_memory=True)
+        self._host_next = (self._host_next + 1) % len(self._host_ids)
+        host = slot[:len(sampled)]
+        if sampled:
+            host.copy_(ids, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        for r in sampled:
+            self.scheduler.on_sampled(r)
+        return _Inflight(sampled, {r: i for i, r in enumerate(sampled)}, host, event, states)
+
+    def _collect(self, flight: "_Inflight") -> List[Tuple[int, int, bool]]:
+        """Wait for a pass's sampled ids and book them: events ``(seq_id, token, finished)``."""
+        flight.event.synchronize()
         events = []
-        for rid, tok in zip(sampled, tokens):
+        for rid, tok in zip(flight.sampled, flight.host.tolist()):
+            if rid not in self.scheduler.seqs:
+                continue                            # released while the pass was in flight
+            if rid in flight.void:
+                # the sequence had ended with the token before: this pass only cached that token
+                self.scheduler.drop_unread(rid)
+                if rid in flight.generator_states and rid in self._sessions:
+                    self._sessions[rid].generator.set_state(flight.generator_states[rid])
+                continue
             finished = self.scheduler.on_token(rid, tok, self.eos_id)
             if finished:
                 self.scheduler.park(rid)            # pages stay until release (engine.cpp:770-788)
                 self._sessions[rid].state = "parked"
+                nxt = self._inflight
+                if nxt is not None and nxt is not flight and rid in nxt.row_of:
+                    nxt.void.add(rid)
             events.append((rid, int(tok), finished))
         return events
 
-    def step(self, n: int = 1) -> List[Tuple[int, int, bool]]:
+    def _drain(self) -> None:
+        """Book the pass in flight, if any; its events wait for the next ``step``."""
+        if self._inflight is not None:
+            flight, self._inflight = self._inflight, None
+            self._unclaimed.extend(self._collect(flight))
+
+    def step_once(self) -> List[Tuple[int, int, bool]]:
+        """One forward pass.  Returns the events ``(seq_id, token, finished)`` of the
+        sequences whose logits were sampled in it."""
+        self._drain()
+        if self._unclaimed:
+            events, self._unclaimed = self._unclaimed, []
+            return events
+        plan = self.scheduler.schedule()
+        if not plan:
+            return []
+        return self._collect(self._launch(plan))
+
+    def step(self, n: int = 1, lookahead: bool = True) -> List[Tuple[int, int, bool]]:
         """Run forwards until ``n`` tokens were emitted or nothing is active; may overshoot
         by the number of active sequences minus one (engine.hpp:490-498).  A scheduler
-        that has work but can run nothing is an error (engine.cpp:809-814)."""
-        events: List[Tuple[int, int, bool]] = []
-        while len(events) < n and self.scheduler.has_work():
-            before = self.forwards
-            events.extend(self.step_once())
-            if self.forwards == before:
-                raise RuntimeError("the scheduler has work but nothing can run: the pool is held by parked "
-                                   "sequences or is too small; release a sequence")
+        that has work but can run nothing is an error (engine.cpp:809-814).
+
+        With ``lookahead`` the next pass is put on the device before the tokens of the last
+        one are read (its inputs are those tokens, taken on the device), so the device does
+        not idle while the host books tokens and decides the next step; one pass may then
+        still be in flight when the call returns, and the next call picks it up.  A sequence
+        that ends on a stop token has by then run one token too far; that token is discarded."""
+        events: List[Tuple[int, int, bool]] = self._unclaimed
+        self._unclaimed = []
+        while len(events) < n:
+            if self._inflight is None:
+                plan = self.scheduler.schedule()
+                if not plan:
+                    if self.scheduler.has_work():
+                        raise RuntimeError("the scheduler has work but nothing can run: the pool is held by parked "
+                                           "sequences or is too small; release a sequence")
+                    break
+                self._inflight = self._launch(plan)
+            flight = self._inflight
+            nxt = None
+            if lookahead:
+                plan = self.scheduler.schedule(allow_preempt=False)
+                if plan:
+                    nxt = self._launch(plan)
+            self._inflight = nxt
+            events.extend(self._collect(flight))
+        if not lookahead:
+            self._drain()
+            events.extend(self._unclaimed)
+            self._unclaimed = []
         return events
 
     # ------------------------------------------------------------------ the simple entry point
@@ -212,13 +303,10 @@ class Engine:
                 sid = self.create_session(prompts[i], ov)
                 self.feed(sid, [], max_new_tokens)
                 owner[sid] = i
-            before = self.forwards
-            for sid, tok, finished in self.step_once():      # one forward at a time: a finished
+            for sid, tok, finished in self.step(1):          # one forward at a time: a finished
                 if sid in owner:                              # sequence gives its pages back at once
                     results[owner[sid]].append(tok)
                     if finished:
                         self.release(sid)
                         del owner[sid]
-            if self.forwards == before and self.scheduler.has_work():
-                raise RuntimeError("the scheduler has work but nothing can run: the pool is too small for it")
         return results

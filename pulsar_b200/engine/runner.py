@@ -24,10 +24,13 @@ from ..parts.base import CacheView, HostBatch, StepContext
 @dataclass
 class StepEntry:
     """The next ``tokens`` of request ``rid``; ``want`` lists the indices among these
-    tokens whose logits are returned (in this order)."""
+    tokens whose logits are returned (in this order).  ``token_src`` (for an entry of one
+    token) says that the token is not known on the host yet: it is element ``token_src`` of
+    the device tensor of sampled ids that the step is given, and ``tokens`` holds a stand-in."""
     rid: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    token_src: Optional[int] = None
 
 
 class StepError(ValueError):
@@ -108,10 +111,11 @@ class ModelRunner:
         return buf
 
     # ------------------------------------------------------------------ the step
-    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+    def prepare(self, entries: Sequence[StepEntry], sampled_ids: Optional[torch.Tensor] = None) -> StepContext:
         """Grow the requests in the cache, build the step's index arrays and copy them
         to the device.  Raises OutOfPages before changing anything if the pages do not
-        suffice for the whole batch."""
+        suffice for the whole batch.  ``sampled_ids``: the device tensor that entries with
+        ``token_src`` take their token from."""
         cache = self.cache
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -126,6 +130,9 @@ class ModelRunner:
             if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
                 bad = [t for t in e.tokens if not (0 <= int(t) < self.vocab)][0]
                 raise StepError(f"request {e.rid!r}: token id {bad} outside the vocabulary [0, {self.vocab})")
+            if e.token_src is not None and (n_tok != 1 or sampled_ids is None or not (0 <= e.token_src < sampled_ids.numel())):
+                raise StepError(f"request {e.rid!r}: a token taken from the device needs an entry of one token and "
+                                f"a tensor of sampled ids that has element {e.token_src}")
             if len(e.want) and (min(e.want) < 0 or max(e.want) >= n_tok):
                 bad = [w for w in e.want if not (0 <= int(w) < n_tok)][0]
                 raise StepError(f"request {e.rid!r}: wanted index {bad} outside its {n_tok} tokens")
@@ -173,6 +180,9 @@ class ModelRunner:
         lengths = [n, n, n, s + 1, s, s, n_rows]
         for g in range(n_groups):
             lengths += [n, s * widths[g]]
+        moved = [(i, e.token_src) for i, e in enumerate(entries) if e.token_src is not None]
+        if moved:                 # last, so that the other arrays lie where they lie without them
+            lengths += [len(moved), len(moved)]
         offsets, total = [], 0
         for ln in lengths:
             offsets.append(total)
@@ -197,6 +207,11 @@ class ModelRunner:
             buf[o_cu + i + 1] = at
         buf[o_kv:o_kv + s] = kv_lens
         buf[o_slot:o_slot + s] = state_slots
+        if moved:
+            o_dst, o_src = offsets[-2], offsets[-1]
+            for k, (i, src) in enumerate(moved):
+                buf[o_dst + k] = buf[o_cu + i]          # the entry's one token sits at its cu_q
+                buf[o_src + k] = src
         ps = cache.page_size
         for g in range(n_groups):
             o_s, o_t = offsets[7 + 2 * g], offsets[8 + 2 * g]
@@ -242,13 +257,15 @@ class ModelRunner:
         for g in range(n_groups):
             ctx.group_slots.append(views[7 + 2 * g])
             ctx.group_tables.append(views[8 + 2 * g])
+        if moved:
+            ops.move_ids(ctx.token_ids, views[-2], views[-1], sampled_ids)
         return ctx
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], sampled_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run the given tokens as one batch from the cache that earlier steps left and
         return float32 logits ``[wanted, vocab]`` in the order of the entries and of their
         ``want`` lists.  The tensor is scratch memory: it is valid until the next step."""
-        ctx = self.prepare(entries)
+        ctx = self.prepare(entries, sampled_ids)
         with torch.cuda.device(self.device):
             logits = self._forward(ctx)
         self.steps_run += 1

@@ -18,6 +18,11 @@ Decisions that differ from the reference:
     (pulsar-core/src/runtime/kv/active_buffer.cpp:153-160);
   * a request that could never fit the pool alone is refused when it is submitted.
 
+A step may be decided while the tokens of the step before are still on the device: a
+sampled token that the host has not read yet stands in the request's token list as
+``UNREAD`` (``on_sampled``), is filled in by ``on_token`` when it arrives, and is taken
+back by ``drop_unread`` if the request turned out to have ended one token earlier.
+
 The scheduler is host code over the cache manager's accounting and runs without a GPU.
 """
 from __future__ import annotations
@@ -27,6 +32,9 @@ from dataclasses import dataclass, field
 from typing import Deque, Dict, Hashable, List, Optional
 
 from ..cache.manager import CacheManager
+
+
+UNREAD = -1        # stands in a token list for a sampled token that has not been read from the device yet
 
 
 class SchedulerError(RuntimeError):
@@ -43,6 +51,8 @@ class SequenceState:
     n_generated: int = 0
     admitted_at: int = -1           # admission counter value; larger = admitted later
     preemptions: int = 0
+    unread: int = 0                 # trailing tokens that are still UNREAD
+    spent: bool = False             # the turn's budget is used up: nothing more is scheduled for it
 
     @property
     def pending(self) -> int:
@@ -111,9 +121,12 @@ class Scheduler:
             raise SchedulerError(f"request {rid!r} is running; feed it when its turn is over")
         if self._pages(len(s.tokens) + len(tokens) + max(0, max_new_tokens)) > self._capacity_pages():
             raise SchedulerError(f"request {rid!r} would outgrow the pool")
+        if s.unread:
+            raise SchedulerError(f"request {rid!r} still has a sampled token that was not read")
         s.tokens.extend(tokens)
         s.max_new_tokens = int(max_new_tokens)
         s.n_generated = 0
+        s.spent = False
         if rid not in self.waiting:
             self.waiting.append(rid)
 
@@ -131,9 +144,11 @@ class Scheduler:
         self.running.remove(rid)
         self.waiting.appendleft(rid)
 
-    def schedule(self) -> List[Scheduled]:
+    def schedule(self, allow_preempt: bool = True) -> Optional[List[Scheduled]]:
         """Decide the next step.  Changes nothing in the cache except by preemption; the
-        step function takes the pages when it runs the entries."""
+        step function takes the pages when it runs the entries.  With ``allow_preempt``
+        false (a step is still in flight, so some tokens are UNREAD and nothing may be
+        recomputed from them) the answer is None where a request would have to be preempted."""
         budget = self.max_chunk_size
         out: List[Scheduled] = []
         planned: set = set()         # requests that already have an entry in this step
@@ -160,13 +175,16 @@ class Scheduler:
             return avail * self.cache.page_size + in_last
 
         # 1. decode tokens, oldest admission first; preempt the youngest when pages run out.
-        decoders = [r for r in self.running if self.seqs[r].pending == 1 and self.seqs[r].n_cached > 0]
+        decoders = [r for r in self.running
+                    if self.seqs[r].pending == 1 and self.seqs[r].n_cached > 0 and not self.seqs[r].spent]
         for rid in sorted(decoders, key=lambda r: self.seqs[r].admitted_at):
             if rid not in self.running:
                 continue                      # preempted below
             if budget <= 0:
                 break
             while not room_for(rid, 1):
+                if not allow_preempt:
+                    return None
                 victim = max(self.running, key=lambda r: self.seqs[r].admitted_at)
                 was_planned = [e for e in out if e.rid == victim]
                 for e in was_planned:          # its planned entry (and pages) leave the step
@@ -190,7 +208,7 @@ class Scheduler:
             s = self.seqs[rid]
             if budget <= 0:
                 break
-            if rid in planned or s.pending == 0:
+            if rid in planned or s.pending == 0 or s.spent:
                 continue
             if s.pending == 1 and s.n_cached > 0:
                 continue                      # a decoder that found no budget above
@@ -229,13 +247,37 @@ class Scheduler:
         for e in entries:
             self.seqs[e.rid].n_cached += len(e.tokens)
 
-    def on_token(self, rid: Hashable, token: int, eos_id: int) -> bool:
-        """A token was sampled for ``rid``.  Returns True when the request's turn is over
-        (stop token or budget, pulsar-core/src/runtime/engine.cpp:727-729)."""
+    def on_sampled(self, rid: Hashable) -> None:
+        """A token was sampled for ``rid`` on the device and is not read yet."""
         s = self.seqs[rid]
-        s.tokens.append(int(token))
+        s.tokens.append(UNREAD)
+        s.unread += 1
         s.n_generated += 1
-        return (eos_id >= 0 and int(token) == eos_id) or s.n_generated >= s.max_new_tokens
+        if s.n_generated >= s.max_new_tokens:
+            s.spent = True
+
+    def on_token(self, rid: Hashable, token: int, eos_id: int) -> bool:
+        """The oldest unread token of ``rid`` has arrived (or, if none was announced by
+        ``on_sampled``, a token was sampled and read at once).  Returns True when the
+        request's turn is over (stop token or budget,
+        pulsar-core/src/runtime/engine.cpp:727-729)."""
+        s = self.seqs[rid]
+        if s.unread == 0:
+            self.on_sampled(rid)
+        s.tokens[len(s.tokens) - s.unread] = int(token)
+        s.unread -= 1
+        spent_by_now = s.n_generated - s.unread >= s.max_new_tokens
+        return (eos_id >= 0 and int(token) == eos_id) or spent_by_now
+
+    def drop_unread(self, rid: Hashable) -> None:
+        """The newest unread token of ``rid`` is void: the request had ended with the token
+        before it.  (The step that sampled it has cached that last token, which is all it leaves.)"""
+        s = self.seqs[rid]
+        if s.unread <= 0 or s.tokens[-1] != UNREAD:
+            raise SchedulerError(f"request {rid!r} has no unread token to drop")
+        s.tokens.pop()
+        s.unread -= 1
+        s.n_generated -= 1
 
     def park(self, rid: Hashable) -> None:
         """The turn is over; the request leaves the running set and keeps its pages."""

@@ -36,6 +36,7 @@ _ERRORS = {-2: "unsupported dtype", -3: "unsupported size or argument", -4: "siz
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _SIGNATURES = {
     "pb_embed": [_I, _P, _P, _P, _I, _I, _I, _P],
+    "pb_move_ids": [_P, _P, _P, _P, _I, _P],
     "pb_add_rmsnorm": [_I, _P, _P, _P, _P, _P, _I, _I, _F, _I, _P],
     "pb_rope_table": [_P, _P, _P, _P, _I, _I, _P],
     "pb_qk_norm_rope_write": [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P],
@@ -121,6 +122,14 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
     assert ids.dtype == torch.int32 and out.dtype == torch.float32 and out.shape == (ids.numel(), table.shape[1])
     check(fn("pb_embed")(code(table.dtype), _p(table), _p(ids), _p(out), ids.numel(), table.shape[1], table.shape[0],
                          stream()), "embed")
+
+
+def move_ids(ids: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, src_ids: torch.Tensor) -> None:
+    """ids[dst[i]] = src_ids[src[i]] (all int32 on the device): sampled tokens of the step before become
+    this step's input without a trip through the host."""
+    _cuda(ids, dst, src, src_ids)
+    assert ids.dtype == dst.dtype == src.dtype == src_ids.dtype == torch.int32 and dst.numel() == src.numel()
+    check(fn("pb_move_ids")(_p(ids), _p(dst), _p(src), _p(src_ids), dst.numel(), stream()), "move_ids")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,

@@ -55,17 +55,20 @@ class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
         self._ids: Optional[torch.Tensor] = None
+        self.last_ids: Optional[torch.Tensor] = None      # what the last call returned
 
-    def sample(self, logits: torch.Tensor, params: Sequence[GenerationParams],
-               generators: Sequence[Optional[torch.Generator]]) -> List[int]:
-        """One token id per row of ``logits`` (float32 [R, V] on the device)."""
+    def sample_on_device(self, logits: torch.Tensor, params: Sequence[GenerationParams],
+                         generators: Sequence[Optional[torch.Generator]]) -> torch.Tensor:
+        """One token id per row of ``logits`` (float32 [R, V] on the device), left on the device:
+        an int32 tensor that stays valid until the next call."""
         rows = logits.shape[0]
-        if rows == 0:
-            return []
         assert len(params) == rows and len(generators) == rows
         if self._ids is None or self._ids.numel() < rows:
             self._ids = torch.empty(max(rows, 64), dtype=torch.int32, device=self.device)
         out = self._ids[:rows]
+        self.last_ids = out
+        if rows == 0:
+            return out
         if all(p.greedy for p in params):
             ops.sample(logits, out)
         else:
@@ -74,4 +77,11 @@ class Sampler:
                                   dtype=torch.float32).to(self.device, non_blocking=True)
             top_k = torch.tensor([p.top_k for p in params], dtype=torch.int32).to(self.device, non_blocking=True)
             ops.sample(logits, out, packed[0], top_k, packed[1], packed[2])
-        return out.tolist()
+        return out
+
+    def sample(self, logits: torch.Tensor, params: Sequence[GenerationParams],
+               generators: Sequence[Optional[torch.Generator]]) -> List[int]:
+        """One token id per row of ``logits``, read back to the host."""
+        if logits.shape[0] == 0:
+            return []
+        return self.sample_on_device(logits, params, generators).tolist()

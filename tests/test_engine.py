@@ -164,6 +164,75 @@ def test_sessions_turn_by_turn_on_kept_pages(folders):
         Pulsar(folders["B"], dict(pagesize=8))
 
 
+def _drive(eng, prompts, budgets, lookahead, overrides=None, second_turn=None):
+    """Feed the prompts and step until nothing is left; the events per sequence, in order."""
+    sids = [eng.create_session(p, overrides(i) if overrides else None) for i, p in enumerate(prompts)]
+    for sid, b in zip(sids, budgets):
+        eng.feed(sid, [], b)
+    seen = {sid: [] for sid in sids}
+
+    def run():
+        guard = 0
+        while eng.has_work():
+            events = eng.step(1) if lookahead else eng.step_once()
+            for sid, tok, fin in events:
+                seen[sid].append((tok, fin))
+            guard += 1
+            assert guard < 10000
+    run()
+    if second_turn:
+        for sid, extra in zip(sids, second_turn):
+            eng.feed(sid, extra, 5)
+        run()
+    eng.cache.check_consistency()
+    for sid in sids:
+        eng.release(sid)
+    assert eng.cache.live_requests() == [] and all(f == eng.config.num_pages for f in eng.cache.n_free_pages())
+    return [seen[sid] for sid in sids]
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("D", "bfloat16")])
+def test_stepping_one_pass_ahead_gives_the_same_tokens(folders, name, dtype):
+    """Engine.step launches the next pass before it reads the last one's tokens (they are fed on the
+    device).  Same events as one pass at a time: prompts in portions beside decoding sequences, budgets that
+    end at different steps, a stop token that ends sequences one pass after they were scheduled again, and a
+    second turn behind the stop token."""
+    raw, seed, page = TINY[name]
+    rng = random.Random(21)
+    prompts = [helpers.random_tokens(rng, n, raw["vocab_size"]) for n in (5, 30, 17, 9)]
+    budgets = [12, 7, 20, 15]
+    free = _drive(_engine(folders[name], dtype, page, max_chunk_size=12), prompts, budgets, lookahead=False)
+    assert [len(ev) for ev in free] == budgets
+    # a stop token that some sequence emits in the middle of its turn
+    eos = free[2][6][0]
+    extra = [[3, 1], [4], [5, 9, 2], [8]]
+    runs = []
+    for lookahead in (False, True):
+        eng = _engine(folders[name], dtype, page, max_chunk_size=12, eos_id=eos)
+        runs.append(_drive(eng, prompts, budgets, lookahead, second_turn=extra))
+        if lookahead:
+            assert eng._inflight is None and not eng._unclaimed
+    assert runs[0] == runs[1]
+    assert any(ev[-1] == (eos, True) for ev in runs[0][2:3] + runs[0]) and len(runs[0][2]) < budgets[2] + 5
+
+
+def test_stepping_one_pass_ahead_keeps_the_random_streams(folders):
+    """A sequence that stops on a stop token has drawn one number too many when the next pass was already
+    in flight; its generator is set back, so a seeded sequence continues in its next turn as it would have."""
+    raw, seed, page = TINY["B"]
+    rng = random.Random(22)
+    prompts = [helpers.random_tokens(rng, n, raw["vocab_size"]) for n in (6, 14, 10)]
+    budgets = [16, 16, 16]
+    ov = lambda i: dict(temperature=0.9, top_k=12, top_p=0.9, seed=100 + i)
+    free = _drive(_engine(folders["B"], "float32", page), prompts, budgets, lookahead=False, overrides=ov)
+    eos = free[1][4][0]
+    extra = [[1], [2, 3], [4]]
+    runs = [_drive(_engine(folders["B"], "float32", page, eos_id=eos), prompts, budgets, la, overrides=ov, second_turn=extra)
+            for la in (False, True)]
+    assert runs[0] == runs[1]
+    assert runs[0][1][4] == (eos, True)
+
+
 def test_engine_refuses_a_cpu_device(folders):
     from pulsar_b200.engine.engine import Engine
     with pytest.raises(RuntimeError, match="no CPU path"):

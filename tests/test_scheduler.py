@@ -5,7 +5,7 @@ on finish) and adds what this engine decides differently (whole-step budget, pre
 import pytest
 
 from pulsar_b200.cache import CacheManager, CacheNeed
-from pulsar_b200.engine.scheduler import Scheduler, SchedulerError
+from pulsar_b200.engine.scheduler import UNREAD, Scheduler, SchedulerError
 
 
 def make(pages=16, page=4, max_running=4, budget=16, max_requests=8):
@@ -173,3 +173,81 @@ def test_refusals():
         s.add_request("a", [1], 3)
     with pytest.raises(SchedulerError):
         Scheduler(cache, 0, 8)
+
+
+def take(cache, plan):
+    for e in plan:
+        if not cache.has(e.rid):
+            cache.open(e.rid)
+        cache.append(e.rid, len(e.tokens))
+
+
+def test_next_step_is_decided_before_the_last_tokens_are_read():
+    """A sampled token that the host has not read stands in the token list as UNREAD; the next
+    step feeds it (the engine takes it on the device); on_token fills it in later."""
+    cache, s = make()
+    s.add_request("a", list(range(6)), 3)
+    plan = s.schedule()
+    take(cache, plan)
+    s.on_step(plan)
+    s.on_sampled("a")                                     # step 1 sampled, not read
+    nxt = s.schedule(allow_preempt=False)
+    assert [(e.rid, e.tokens, e.sample) for e in nxt] == [("a", [UNREAD], True)]
+    take(cache, nxt)
+    s.on_step(nxt)
+    s.on_sampled("a")                                     # step 2 sampled: two unread now
+    assert s.seqs["a"].tokens[-2:] == [UNREAD, UNREAD]
+    assert s.on_token("a", 41, eos_id=-1) is False        # step 1's token arrives: the older one is filled
+    assert s.seqs["a"].tokens[-2:] == [41, UNREAD]
+    third = s.schedule(allow_preempt=False)
+    take(cache, third)
+    s.on_step(third)
+    s.on_sampled("a")                                     # the third and last token of the budget
+    assert s.schedule(allow_preempt=False) == []          # budget spent: nothing more is planned for it
+    assert s.on_token("a", 42, -1) is False and s.on_token("a", 43, -1) is True
+    assert s.seqs["a"].tokens[-3:] == [41, 42, 43] and s.seqs["a"].unread == 0
+    cache.check_consistency()
+
+
+def test_a_stop_token_voids_the_token_sampled_after_it():
+    cache, s = make()
+    s.add_request("a", list(range(5)), 10)
+    for _ in range(2):                                    # two steps ahead of the host
+        plan = s.schedule(allow_preempt=False)
+        take(cache, plan)
+        s.on_step(plan)
+        s.on_sampled("a")
+    assert s.on_token("a", 9, eos_id=9) is True           # the first token was the stop token
+    s.park("a")
+    s.drop_unread("a")                                    # what was sampled after it never happened
+    st = s.seqs["a"]
+    assert st.tokens == list(range(5)) + [9] and st.unread == 0 and st.n_generated == 1
+    assert st.n_cached == len(st.tokens) == cache.length("a")       # the step that ran too far cached the stop token
+    with pytest.raises(SchedulerError, match="no unread"):
+        s.drop_unread("a")
+    s.extend_request("a", [4, 4], 2)                      # a further turn continues behind the stop token
+    plan = s.schedule()
+    assert [(e.rid, e.tokens, e.sample) for e in plan] == [("a", [4, 4], True)]
+
+
+def test_no_preemption_while_tokens_are_unread():
+    cache, s = make(pages=4, page=4, max_running=2)       # 16 tokens of cache
+    s.add_request("a", list(range(7)), 8)
+    s.add_request("b", list(range(7)), 8)
+    plan = s.schedule()
+    take(cache, plan)
+    s.on_step(plan)
+    s.on_sampled("a")
+    s.on_sampled("b")
+    nxt = s.schedule(allow_preempt=False)                 # position 7 of each: still inside their second pages
+    assert len(nxt) == 2
+    take(cache, nxt)
+    s.on_step(nxt)
+    s.on_sampled("a")
+    s.on_sampled("b")
+    assert s.schedule(allow_preempt=False) is None        # position 8 needs a third page each: one must be preempted
+    for rid in ("a", "b"):
+        s.on_token(rid, 1, -1)
+        s.on_token(rid, 1, -1)
+    plan = s.schedule()                                   # everything read: now the youngest is preempted
+    assert [e.rid for e in plan] == ["a"] and s.n_preemptions == 1
