@@ -21,9 +21,10 @@ import os
 
 F32, BF16 = 0, 1
 # Which product serves bfloat16 projections of more than 16 rows:
-#   "auto"     the gate/up product with its SwiGLU gating fused runs on this library's tcgen05 / TMA
-#              kernel (faster than the library product plus a gating kernel); the plain projections
-#              take the library product (cuBLAS through torch.mm, as the reference does);
+#   "auto"     with more than 128 rows the gate/up product with its SwiGLU gating fused runs on this
+#              library's tcgen05 / TMA kernel (faster than the library product plus a gating kernel);
+#              the plain projections, and gate/up of 17 to 128 rows, take the library product
+#              (cuBLAS through torch.mm, as the reference does);
 #   "tcgen05"  every projection on the tcgen05 kernel;
 #   "library"  every projection on the library product, gating in a kernel of its own.
 # Up to 16 rows always take the weight-streaming kernel.
@@ -298,12 +299,16 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out [M, I] = silu(a Wg^T) * (a Wu^T) with ``w_gate_up`` = gate rows then up rows.  Few
-    bfloat16 rows: one kernel that never writes the [M, 2I] intermediate; otherwise the
-    product followed by the gating kernel."""
+    """out [M, I] = silu(a Wg^T) * (a Wu^T) with ``w_gate_up`` = gate rows then up rows.  In
+    bfloat16, up to 16 rows (the weight-streaming kernel) and more than 128 rows (the tcgen05 kernel)
+    take one kernel that never writes the [M, 2I] intermediate; otherwise the product followed by the
+    gating kernel."""
     if gemm_skinny(a, w_gate_up, out, swiglu=True):
         return
-    if GEMM_BACKEND in ("auto", "tcgen05") and gemm_tcgen05(a, w_gate_up, out, swiglu=True):
+    # Between 17 and 128 rows the product is still bound by streaming the weights, which the library's small
+    # tiles do faster (4.5 against 3.2 TB/s at the 8B sizes) than the tcgen05 kernel's 128 x 256 tiles.
+    fused = GEMM_BACKEND == "tcgen05" or (GEMM_BACKEND == "auto" and a.shape[0] > 128)
+    if fused and gemm_tcgen05(a, w_gate_up, out, swiglu=True):
         return
     gate_up = ctx.scratch("mlp.gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
     linear(a, w_gate_up, gate_up)
