@@ -10,8 +10,8 @@ group with a window gives pages back as soon as every future query has passed th
 Beside the pages every request holds one slot index into the fixed-state arenas of
 the entries that declare such state (none do for Qwen3 dense, the slot exists anyway).
 
-The accounting (``PageAllocator``, ``CacheManager`` with ``device=None``) is pure host
-code and is tested without a GPU.
+The accounting lives in the host runtime (C++, csrc/host/cache.cpp) and is tested without a GPU
+(``PageAllocator``, ``CacheManager`` with ``device=None``).
 
 Physical layout of a group's pool: ``[entries, 2 (k, v), pages, kv_heads, page_size,
 head_dim]``, so that one (page, kv head) tile of keys is contiguous
@@ -19,10 +19,13 @@ head_dim]``, so that one (page, kv head) tile of keys is contiguous
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
+
+from .. import host
 
 
 class OutOfPages(RuntimeError):
@@ -58,51 +61,67 @@ class CacheNeed:
 
 class PageAllocator:
     """LIFO free list over ``n`` ids; a fresh allocator yields 0, 1, 2, ... and a
-    released id is the next one handed out (active_buffer.cpp:71-75, 219-221)."""
+    released id is the next one handed out (active_buffer.cpp:71-75, 219-221).  The list
+    lives in the host runtime (csrc/host/cache.h: FreeList)."""
 
     def __init__(self, n: int):
         self.n = int(n)
-        self._free: List[int] = list(range(self.n - 1, -1, -1))
-        self._held = [False] * self.n
+        self._lib = host.lib()
+        self._h = self._lib.ph_freelist_new(self.n)
+        if not self._h:
+            raise CacheError(f"a free list needs a size >= 0, found {n}")
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.ph_freelist_delete(h)
 
     @property
     def n_free(self) -> int:
-        return len(self._free)
+        return self._lib.ph_freelist_n_free(self._h)
 
     def take(self) -> int:
-        if not self._free:
+        i = self._lib.ph_freelist_take(self._h)
+        if i < 0:
             raise OutOfPages("no free page")
-        i = self._free.pop()
-        self._held[i] = True
         return i
 
     def give(self, i: int) -> None:
-        if not (0 <= i < self.n) or not self._held[i]:
+        if self._lib.ph_freelist_give(self._h, int(i)) != 0:
             raise CacheError(f"page {i} is not held (freed twice or never taken)")
-        self._held[i] = False
-        self._free.append(i)
 
     def held(self) -> List[int]:
-        return [i for i, h in enumerate(self._held) if h]
+        return [i for i in range(self.n) if self._lib.ph_freelist_held(self._h, i)]
+
+
+class _GroupPages:
+    """The free list of one group inside the native cache, as far as callers look at it."""
+
+    def __init__(self, manager: "CacheManager", group: int):
+        self._m, self._g = manager, group
+        self.n = manager._lib.ph_n_pages(manager._h, group)
+
+    @property
+    def n_free(self) -> int:
+        return self._m._lib.ph_n_free_pages(self._m._h, self._g)
+
+    def held(self) -> List[int]:
+        return [i for i in range(self.n) if self._m._lib.ph_page_held(self._m._h, self._g, i)]
 
 
 @dataclass
 class _Group:
     need: CacheNeed                   # kind paged_kv; window shared by the group
     entries: List[int]                # cache entries that live in this group
-    allocator: PageAllocator
+    allocator: Optional[_GroupPages]
     pool: Optional[torch.Tensor] = None   # [entries, 2, pages, Hkv, page, D]
 
 
-@dataclass
-class _Request:
-    length: int = 0
-    state_slot: int = -1
-    tables: List[List[int]] = field(default_factory=list)     # per group: logical page -> page id or -1
-    released: List[int] = field(default_factory=list)         # per group: logical pages [0, released) given back
-
-
 class CacheManager:
+    """The tensors of the cache (pools, state arenas) and the request names live here; pages, block
+    tables, lengths and slots are kept by the host runtime (csrc/host/cache.cpp), which this class
+    calls.  Requests are named by any hashable value; the runtime knows them by a number."""
+
     def __init__(self, needs: Sequence[CacheNeed], page_size: int, num_pages, max_requests: int,
                  dtype: torch.dtype = torch.float32, device=None):
         """``needs[i]`` is the need of cache entry i.  ``num_pages`` is an int (every
@@ -131,105 +150,123 @@ class CacheManager:
         counts = [int(num_pages)] * len(self.groups) if isinstance(num_pages, int) else [int(n) for n in num_pages]
         if len(counts) != len(self.groups) or any(c <= 0 for c in counts):
             raise CacheError(f"num_pages must give a positive count for each of the {len(self.groups)} groups")
-        for grp, c in zip(self.groups, counts):
-            grp.allocator = PageAllocator(c)
+        self.max_requests = int(max_requests)
+        self._lib = host.lib()
+        windows = [int(grp.need.window) if grp.need.window is not None else -1 for grp in self.groups]
+        self._h = self._lib.ph_cache_new(len(self.groups), host.ints(windows), host.ints(counts), self.page_size,
+                                         self.max_requests)
+        if not self._h:
+            raise CacheError("the host runtime refused the cache's sizes")
+        self._n_groups = len(self.groups)
+        self._scratch = (ctypes.c_int * max(1, self._n_groups))()
+        for g, (grp, c) in enumerate(zip(self.groups, counts)):
+            grp.allocator = _GroupPages(self, g)
             if device is not None:
                 grp.pool = torch.zeros((len(grp.entries), 2, c, grp.need.n_kv_heads, self.page_size, grp.need.head_dim),
                                        dtype=dtype, device=device)
-        self._windowed = any(grp.need.window is not None for grp in self.groups)
-        self.max_requests = int(max_requests)
-        self._slots = PageAllocator(self.max_requests)
         self.state: Dict[int, torch.Tensor] = {}
         for e, need in enumerate(self.needs):
             if need.kind == "state" and device is not None:
                 self.state[e] = torch.zeros((self.max_requests, *need.state_shape),
                                             dtype=need.state_dtype or dtype, device=device)
-        self._requests: Dict[Hashable, _Request] = {}
+        self._ids: Dict[Hashable, int] = {}         # request name -> the runtime's number for it
+        self._next_id = 0
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.ph_cache_delete(h)
 
     # ------------------------------------------------------------------ requests
+    def native_id(self, rid: Hashable) -> int:
+        """The runtime's number for an open request."""
+        try:
+            return self._ids[rid]
+        except KeyError:
+            raise CacheError(f"unknown request {rid!r}") from None
+
+    def _raise(self, code: int, rid: Hashable, what: str = ""):
+        if code == host.UNKNOWN_REQUEST:
+            raise CacheError(f"unknown request {rid!r}")
+        if code == host.ALREADY_OPEN:
+            raise CacheError(f"request {rid!r} is already open")
+        if code == host.OUT_OF_PAGES:
+            raise OutOfPages(f"request {rid!r}: {what or 'no free page'}; {self.n_free_pages()} pages are free")
+        if code == host.OUT_OF_SLOTS:
+            raise OutOfPages(f"no free state slot (max_requests = {self.max_requests})")
+        if code == host.RELEASED_PAGE:
+            raise CacheError(f"request {rid!r}: {what or 'a position'} lies in a released page")
+        if code == host.NOT_HELD:
+            raise CacheError(f"request {rid!r}: a page or slot is not held (freed twice or never taken)")
+        raise CacheError(f"request {rid!r}: the host runtime answered {code} {what}")
+
     def open(self, rid: Hashable) -> int:
         """Register a request and give it a state slot.  Holds no pages yet."""
-        if rid in self._requests:
+        if rid in self._ids:
             raise CacheError(f"request {rid!r} is already open")
-        try:
-            slot = self._slots.take()
-        except OutOfPages:
-            raise OutOfPages(f"no free state slot (max_requests = {self.max_requests})") from None
-        self._requests[rid] = _Request(0, slot, [[] for _ in self.groups], [0 for _ in self.groups])
+        nid = self._next_id
+        slot = self._lib.ph_open(self._h, nid)
+        if slot < 0:
+            self._raise(slot, rid)
+        self._next_id += 1
+        self._ids[rid] = nid
         for e, t in self.state.items():      # fresh state starts at zero
             t[slot].zero_()
         return slot
 
-    def has(self, rid: Hashable) -> bool:
-        return rid in self._requests
+    def adopt(self, rid: Hashable, native_id: int) -> None:
+        """The runtime opened request ``native_id`` itself (the step packer does): remember its name."""
+        self._ids[rid] = native_id
+        self._next_id = max(self._next_id, native_id + 1)
+        slot = self._lib.ph_state_slot(self._h, native_id)
+        for e, t in self.state.items():
+            t[slot].zero_()
 
-    def _req(self, rid: Hashable) -> _Request:
-        try:
-            return self._requests[rid]
-        except KeyError:
-            raise CacheError(f"unknown request {rid!r}") from None
+    def reserve_id(self) -> int:
+        """A number for a request that the step packer is about to open."""
+        nid = self._next_id
+        self._next_id += 1
+        return nid
+
+    def has(self, rid: Hashable) -> bool:
+        return rid in self._ids
 
     def length(self, rid: Hashable) -> int:
-        return self._req(rid).length
+        return self._lib.ph_length(self._h, self.native_id(rid))
 
     def n_logical_pages(self, rid: Hashable) -> int:
         """Logical pages the request's tables cover (the fewest over the groups)."""
-        r = self._req(rid)
-        return min(len(t) for t in r.tables) if r.tables else 0
+        return self._lib.ph_n_logical_pages(self._h, self.native_id(rid))
 
     def state_slot(self, rid: Hashable) -> int:
-        return self._req(rid).state_slot
+        return self._lib.ph_state_slot(self._h, self.native_id(rid))
 
     def live_requests(self) -> List[Hashable]:
-        return list(self._requests)
+        return list(self._ids)
 
     # ------------------------------------------------------------------ pages
-    def _first_needed_page(self, grp: _Group, length: int) -> int:
-        """Logical pages below this hold only keys that no query at position >= length sees."""
-        if grp.need.window is None:
-            return 0
-        first_key = length - grp.need.window + 1        # oldest key the query at `length` sees
-        return max(0, first_key) // self.page_size
-
     def pages_to_append(self, rid: Hashable, n_new: int) -> List[int]:
         """New pages each group must take so that the request can grow by ``n_new``
         tokens, after giving back what its windows have passed."""
-        r = self._req(rid)
-        out = []
-        for g, grp in enumerate(self.groups):
-            have = len(r.tables[g])
-            need = -(-(r.length + n_new) // self.page_size)
-            out.append(max(0, need - have))
-        return out
+        self._lib.ph_pages_to_append(self._h, self.native_id(rid), int(n_new), self._scratch)
+        return list(self._scratch[:self._n_groups])
 
     def reclaimable(self, rid: Hashable) -> List[int]:
-        r = self._req(rid)
-        return [max(0, min(self._first_needed_page(grp, r.length), len(r.tables[g])) - r.released[g])
-                for g, grp in enumerate(self.groups)]
+        self._lib.ph_reclaimable(self._h, self.native_id(rid), self._scratch)
+        return list(self._scratch[:self._n_groups])
 
     def can_append(self, rid: Hashable, n_new: int) -> bool:
-        need = self.pages_to_append(rid, n_new)
-        back = self.reclaimable(rid)
-        return all(n <= grp.allocator.n_free + b for n, b, grp in zip(need, back, self.groups))
+        return self._lib.ph_can_append(self._h, self.native_id(rid), int(n_new)) == 1
 
     def can_admit(self, n_tokens: int) -> bool:
         """Could a request that holds nothing yet take ``n_tokens`` tokens (and a slot)?"""
-        pages = -(-n_tokens // self.page_size)
-        return self._slots.n_free > 0 and all(pages <= grp.allocator.n_free for grp in self.groups)
+        return self._lib.ph_can_admit(self._h, int(n_tokens)) == 1
 
     def release_passed(self, rid: Hashable) -> int:
         """Give back the pages of windowed groups that every future query has passed."""
-        if not self._windowed:
-            return 0
-        r = self._req(rid)
-        n = 0
-        for g, grp in enumerate(self.groups):
-            upto = min(self._first_needed_page(grp, r.length), len(r.tables[g]))
-            for lp in range(r.released[g], upto):
-                grp.allocator.give(r.tables[g][lp])
-                r.tables[g][lp] = -1
-                n += 1
-            r.released[g] = max(r.released[g], upto)
+        n = self._lib.ph_release_passed(self._h, self.native_id(rid))
+        if n < 0:
+            self._raise(n, rid)
         return n
 
     def append(self, rid: Hashable, n_new: int) -> int:
@@ -237,58 +274,37 @@ class CacheManager:
         Either every group gets its pages or nothing changes (OutOfPages)."""
         if n_new <= 0:
             raise CacheError("append needs n_new > 0")
-        r = self._req(rid)
-        if not self._windowed:
-            # no group gives pages back early: one pass, check every group before taking anything
-            need = -(-(r.length + n_new) // self.page_size)
-            for g, grp in enumerate(self.groups):
-                if need - len(r.tables[g]) > grp.allocator.n_free:
-                    raise OutOfPages(f"request {rid!r}: {self.pages_to_append(rid, n_new)} new pages needed, "
-                                     f"{[x.allocator.n_free for x in self.groups]} free")
-            for g, grp in enumerate(self.groups):
-                table = r.tables[g]
-                for _ in range(need - len(table)):
-                    table.append(grp.allocator.take())
-            start = r.length
-            r.length += n_new
-            return start
-        if not self.can_append(rid, n_new):
-            raise OutOfPages(f"request {rid!r}: {self.pages_to_append(rid, n_new)} new pages needed, "
-                             f"{[g.allocator.n_free for g in self.groups]} free")
-        self.release_passed(rid)
-        for g, need in enumerate(self.pages_to_append(rid, n_new)):
-            for _ in range(need):
-                r.tables[g].append(self.groups[g].allocator.take())
-        start = r.length
-        r.length += n_new
+        start = self._lib.ph_append(self._h, self.native_id(rid), int(n_new))
+        if start < 0:
+            self._raise(start, rid, f"{n_new} more tokens do not fit")
         return start
 
     def close(self, rid: Hashable) -> None:
         """Give back everything the request holds."""
-        r = self._req(rid)
-        for g, grp in enumerate(self.groups):
-            for page in r.tables[g]:
-                if page >= 0:
-                    grp.allocator.give(page)
-        self._slots.give(r.state_slot)
-        del self._requests[rid]
+        rc = self._lib.ph_close(self._h, self.native_id(rid))
+        del self._ids[rid]
+        if rc < 0:
+            self._raise(rc, rid)
 
     # ------------------------------------------------------------------ views for a step
     def table(self, rid: Hashable, group: int) -> List[int]:
-        return self._req(rid).tables[group]
+        nid = self.native_id(rid)
+        cap = 64
+        while True:
+            out = (ctypes.c_int * cap)()
+            n = self._lib.ph_table(self._h, nid, int(group), out, cap)
+            if n <= cap:
+                return list(out[:n])
+            cap = n
 
     def slots(self, rid: Hashable, group: int, start: int, n: int) -> List[int]:
         """slot = page * page_size + offset for positions [start, start + n)
         (active_buffer.cpp:255-279)."""
-        table = self._req(rid).tables[group]
-        ps = self.page_size
-        out = []
-        for p in range(start, start + n):
-            page = table[p // ps]
-            if page < 0:
-                raise CacheError(f"request {rid!r}: position {p} lies in a released page")
-            out.append(page * ps + p % ps)
-        return out
+        out = (ctypes.c_int * max(1, n))()
+        rc = self._lib.ph_slots(self._h, self.native_id(rid), int(group), int(start), int(n), out)
+        if rc < 0:
+            self._raise(rc, rid, f"a position in [{start}, {start + n})")
+        return list(out[:n])
 
     def kv_pools(self, entry: int) -> Tuple[torch.Tensor, torch.Tensor]:
         g = self.group_of_entry[entry]
@@ -296,26 +312,16 @@ class CacheManager:
         return pool[0], pool[1]
 
     def n_free_pages(self) -> List[int]:
-        return [g.allocator.n_free for g in self.groups]
+        return [self._lib.ph_n_free_pages(self._h, g) for g in range(self._n_groups)]
 
     def n_free_slots(self) -> int:
-        return self._slots.n_free
+        return self._lib.ph_n_free_slots(self._h)
 
     def check_consistency(self) -> None:
-        """Every page is free or held by exactly one request; used by tests."""
-        for g, grp in enumerate(self.groups):
-            seen: Dict[int, Hashable] = {}
-            for rid, r in self._requests.items():
-                for page in r.tables[g]:
-                    if page < 0:
-                        continue
-                    if page in seen:
-                        raise CacheError(f"group {g}: page {page} held by {seen[page]!r} and {rid!r}")
-                    seen[page] = rid
-            if sorted(seen) != grp.allocator.held():
-                raise CacheError(f"group {g}: held pages {grp.allocator.held()} != pages in tables {sorted(seen)}")
-            if len(seen) + grp.allocator.n_free != grp.allocator.n:
-                raise CacheError(f"group {g}: a page was lost")
-        slots = sorted(r.state_slot for r in self._requests.values())
-        if slots != self._slots.held():
+        """Every page is free or held by exactly one request, every slot likewise; used by tests."""
+        if self._lib.ph_check(self._h) != 0:
+            raise CacheError("the cache's accounting is inconsistent: a page or slot is lost, held twice or freed twice")
+        live = sorted(self._lib.ph_state_slot(self._h, nid) for nid in self._ids.values())
+        held = [s for s in range(self.max_requests) if self._lib.ph_slot_held(self._h, s)]
+        if live != held:
             raise CacheError("state slots out of step with the live requests")

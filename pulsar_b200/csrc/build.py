@@ -150,5 +150,65 @@ def library() -> ctypes.CDLL:
     return _lib
 
 
+# ------------------------------------------------------------------ the host runtime (plain C++, no CUDA)
+HOST_DIR = os.path.join(HERE, "host")
+HOST_LIB_NAME = "libpulsar_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+_host_lib: Optional[ctypes.CDLL] = None
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("PULSAR_CXX"), os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"),
+                 shutil.which("clang++")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return cand
+    raise BuildError("no C++ compiler found (set PULSAR_CXX or put g++ on PATH): the host runtime cannot be built")
+
+
+def build_host(verbose: bool = True, force: bool = False) -> str:
+    """Compile the sources of ``host/`` into one shared library (cache accounting, step packer, scheduler:
+    see the ``PH_EXPORT`` functions) and return its path."""
+    out_dir = _build_dir()
+    lib_path = os.path.join(out_dir, HOST_LIB_NAME)
+    stamp_path = os.path.join(out_dir, "host_stamp.txt")
+    names = sorted(f for f in os.listdir(HOST_DIR) if f.endswith((".cpp", ".h")))
+    h = hashlib.sha256(" ".join(HOST_FLAGS).encode())
+    for name in names:
+        h.update(name.encode())
+        with open(os.path.join(HOST_DIR, name), "rb") as f:
+            h.update(f.read())
+    digest = h.hexdigest()[:16]
+    if not force and os.path.isfile(lib_path) and os.path.isfile(stamp_path):
+        with open(stamp_path) as f:
+            if f.read().strip() == digest:
+                return lib_path
+    cxx = find_cxx()
+    if verbose:
+        _say(f"compiling the host runtime ({len([n for n in names if n.endswith('.cpp')])} C++ sources) into {out_dir}")
+    t0 = time.time()
+    tmp_lib = lib_path + f".tmp{os.getpid()}"
+    cmd = [cxx, *HOST_FLAGS, "-I", HOST_DIR, "-o", tmp_lib, *[os.path.join(HOST_DIR, n) for n in names if n.endswith(".cpp")]]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"{cxx} failed:\n" + r.stdout)
+    os.replace(tmp_lib, lib_path)
+    with open(stamp_path, "w") as f:
+        f.write(digest)
+    if verbose:
+        _say(f"built {HOST_LIB_NAME} in {time.time() - t0:.0f}s")
+    return lib_path
+
+
+def host_library() -> ctypes.CDLL:
+    """The loaded host runtime; builds it on first use."""
+    global _host_lib
+    if _host_lib is None:
+        with _lock:
+            if _host_lib is None:
+                _host_lib = ctypes.CDLL(build_host())
+    return _host_lib
+
+
 if __name__ == "__main__":
+    print(build_host(force="--force" in sys.argv))
     print(build(force="--force" in sys.argv, extra_flags=["-Xptxas", "-v"] if "-v" in sys.argv else None))

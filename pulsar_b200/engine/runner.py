@@ -13,10 +13,11 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
-import numpy as np
+import ctypes
+
 import torch
 
-from .. import ops
+from .. import host, ops
 from ..cache.manager import CacheManager, OutOfPages
 from ..parts.base import CacheView, HostBatch, StepContext
 
@@ -136,101 +137,56 @@ class ModelRunner:
             if len(e.want) and (min(e.want) < 0 or max(e.want) >= n_tok):
                 bad = [w for w in e.want if not (0 <= int(w) < n_tok)][0]
                 raise StepError(f"request {e.rid!r}: wanted index {bad} outside its {n_tok} tokens")
-        # Page check for the whole batch before any change.
-        fresh = [e for e in entries if not cache.has(e.rid)]
-        if len(fresh) > cache.n_free_slots():
-            raise OutOfPages(f"{len(fresh)} new requests but {cache.n_free_slots()} free state slots")
-        n_groups = len(cache.groups)
-        need = [0] * n_groups
-        for e in entries:
-            if cache.has(e.rid):
-                cache.release_passed(e.rid)      # pages a window has passed serve this very step
-                want_pages = cache.pages_to_append(e.rid, len(e.tokens))
-            else:
-                want_pages = [-(-len(e.tokens) // cache.page_size)] * n_groups
-            for g in range(n_groups):
-                need[g] += want_pages[g]
-        free = cache.n_free_pages()
-        if any(need[g] > free[g] for g in range(n_groups)):
-            raise OutOfPages(f"step needs {need} new pages per group, {free} are free")
-
-        q_lens, kv_lens, starts, state_slots = [], [], [], []
-        for e in entries:
-            if not cache.has(e.rid):
-                cache.open(e.rid)
-            starts.append(cache.append(e.rid, len(e.tokens)))
-            q_lens.append(len(e.tokens))
-            kv_lens.append(starts[-1] + len(e.tokens))
-            state_slots.append(cache.state_slot(e.rid))
-        host = HostBatch(q_lens, kv_lens, state_slots)
-        n, s = sum(q_lens), len(entries)
-        ctx = StepContext(self, n, s, host)
-
-        # Lengths of the step's index arrays, each padded to 16 bytes, in one pinned buffer:
+        # The host runtime checks the whole step's pages and slots before anything changes, grows the
+        # requests, and writes the step's index arrays into one pinned buffer:
         # token_ids, positions, seq_of_token [N]; cu_q [S+1]; kv_len, state_slots [S]; logit_rows [R];
-        # per group slots [N] and the block table [S, width].
-        widths = []
-        for g in range(n_groups):
-            w = max(1, max(len(cache.table(e.rid, g)) for e in entries))
-            if ctx.all_decode:      # few distinct widths, so that captured steps are reused as contexts grow
-                w = -(-w // self.TABLE_BUCKET) * self.TABLE_BUCKET
-            widths.append(w)
+        # per group slots [N] and the block table [S, width]; move_dst, move_src if tokens come from the device.
+        s = len(entries)
+        n_groups = len(cache.groups)
+        fresh = [e.rid for e in entries if not cache.has(e.rid)]
+        fresh_ids = {rid: cache.reserve_id() for rid in fresh}
+        rids = host.longs([fresh_ids[e.rid] if e.rid in fresh_ids else cache.native_id(e.rid) for e in entries])
+        q_lens = [len(e.tokens) for e in entries]
+        n = sum(q_lens)
+        flat_tokens = [int(t) for e in entries for t in e.tokens]
+        flat_wants = [int(w) for e in entries for w in e.want]
+        n_tok, want_n = host.ints(q_lens), host.ints([len(e.want) for e in entries])
+        tokens, wants = host.ints(flat_tokens), host.ints(flat_wants or [0])
+        token_src = host.ints([-1 if e.token_src is None else int(e.token_src) for e in entries])
+        starts, slots = (ctypes.c_int * s)(), (ctypes.c_int * s)()
+        widths_c, bad = (ctypes.c_int * max(1, n_groups))(), ctypes.c_int(-1)
+        lib, handle = cache._lib, cache._h
+        total = lib.ph_step_plan(handle, s, rids, n_tok, tokens, want_n, wants, token_src,
+                                 0 if sampled_ids is None else int(sampled_ids.numel()), self.vocab, self.TABLE_BUCKET,
+                                 starts, slots, widths_c, ctypes.byref(bad))
+        if total < 0:
+            if total == host.OUT_OF_SLOTS:
+                raise OutOfPages(f"{len(fresh)} new requests but {cache.n_free_slots()} free state slots")
+            if total == host.OUT_OF_PAGES:
+                raise OutOfPages(f"the step's {n} tokens need more pages than the {cache.n_free_pages()} free ones")
+            who = entries[bad.value].rid if 0 <= bad.value < s else None
+            if total == host.RELEASED_PAGE:
+                raise StepError(f"request {who!r}: a position of the step lies in a released page")
+            raise StepError(f"the host runtime refused the step (code {total}, entry of request {who!r})")
+        for rid, nid in fresh_ids.items():
+            cache.adopt(rid, nid)
+        starts, state_slots = list(starts), list(slots)
+        kv_lens = [st + q for st, q in zip(starts, q_lens)]
+        host_batch = HostBatch(q_lens, kv_lens, state_slots)
+        ctx = StepContext(self, n, s, host_batch)
+        widths = list(widths_c[:n_groups])
         ctx.table_widths = tuple(widths)
-        n_rows = sum(len(e.want) for e in entries)
-        lengths = [n, n, n, s + 1, s, s, n_rows]
-        for g in range(n_groups):
-            lengths += [n, s * widths[g]]
-        moved = [(i, e.token_src) for i, e in enumerate(entries) if e.token_src is not None]
-        if moved:                 # last, so that the other arrays lie where they lie without them
-            lengths += [len(moved), len(moved)]
-        offsets, total = [], 0
-        for ln in lengths:
-            offsets.append(total)
-            total += _align(max(ln, 1))
+        moved = any(e.token_src is not None for e in entries)
+        n_arrays = 7 + 2 * n_groups + (2 if moved else 0)
+        offsets_c, lengths_c = (ctypes.c_int * n_arrays)(), (ctypes.c_int * n_arrays)()
         stage = self._stage(total)
-        buf = stage.numpy()
-        o_tok, o_pos, o_seq, o_cu, o_kv, o_slot, o_rows = offsets[:7]
-        at, row_at = 0, 0
-        buf[o_cu] = 0
-        for i, e in enumerate(entries):
-            q = q_lens[i]
-            buf[o_tok + at:o_tok + at + q] = e.tokens
-            if q == 1:
-                buf[o_pos + at] = starts[i]
-            else:
-                buf[o_pos + at:o_pos + at + q] = np.arange(starts[i], starts[i] + q, dtype=np.int32)
-            buf[o_seq + at:o_seq + at + q] = i
-            for w in e.want:
-                buf[o_rows + row_at] = at + int(w)
-                row_at += 1
-            at += q
-            buf[o_cu + i + 1] = at
-        buf[o_kv:o_kv + s] = kv_lens
-        buf[o_slot:o_slot + s] = state_slots
-        if moved:
-            o_dst, o_src = offsets[-2], offsets[-1]
-            for k, (i, src) in enumerate(moved):
-                buf[o_dst + k] = buf[o_cu + i]          # the entry's one token sits at its cu_q
-                buf[o_src + k] = src
-        ps = cache.page_size
-        for g in range(n_groups):
-            o_s, o_t = offsets[7 + 2 * g], offsets[8 + 2 * g]
-            w = widths[g]
-            buf[o_t:o_t + s * w] = -1
-            at = 0
-            for i, e in enumerate(entries):
-                row = cache.table(e.rid, g)
-                q = q_lens[i]
-                if q == 1:
-                    p = starts[i]
-                    page = row[p // ps]
-                    if page < 0:
-                        raise StepError(f"request {e.rid!r}: position {p} lies in a released page")
-                    buf[o_s + at] = page * ps + p % ps
-                else:
-                    buf[o_s + at:o_s + at + q] = cache.slots(e.rid, g, starts[i], q)
-                buf[o_t + i * w:o_t + i * w + len(row)] = row
-                at += q
+        rc = lib.ph_step_pack(handle, s, rids, n_tok, tokens, want_n, wants, token_src, (ctypes.c_int * s)(*starts),
+                              (ctypes.c_int * s)(*state_slots), widths_c, stage.data_ptr(), stage.numel(), offsets_c, lengths_c)
+        if rc == host.RELEASED_PAGE:
+            raise StepError("a position of the step lies in a released page")
+        if rc != total:
+            raise StepError(f"the host runtime packed {rc} words where {total} were planned")
+        offsets, lengths = list(offsets_c), list(lengths_c)
         if self._index_buf is None or self._index_buf.numel() < total:
             self._index_buf = torch.empty(max(total, 4096) * 2, dtype=torch.int32, device=self.device)
             self.scratch_epoch += 1
