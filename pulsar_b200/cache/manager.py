@@ -170,6 +170,8 @@ class CacheManager:
                 self.state[e] = torch.zeros((self.max_requests, *need.state_shape),
                                             dtype=need.state_dtype or dtype, device=device)
         self._ids: Dict[Hashable, int] = {}         # request name -> the runtime's number for it
+        self._names: Dict[int, Hashable] = {}
+        self._pinned: set = set()                   # names that keep their number while they hold nothing
         self._next_id = 0
 
     def __del__(self):
@@ -178,12 +180,37 @@ class CacheManager:
             self._lib.ph_cache_delete(h)
 
     # ------------------------------------------------------------------ requests
-    def native_id(self, rid: Hashable) -> int:
-        """The runtime's number for an open request."""
-        try:
-            return self._ids[rid]
-        except KeyError:
-            raise CacheError(f"unknown request {rid!r}") from None
+    def native_id(self, rid: Hashable, create: bool = False) -> int:
+        """The runtime's number for a request name.  Names are numbered at their first mention
+        (``create``), which may be before the request is opened: the scheduler knows waiting
+        requests by the same numbers."""
+        nid = self._ids.get(rid)
+        if nid is None:
+            if not create:
+                raise CacheError(f"unknown request {rid!r}")
+            nid = self._ids[rid] = self._next_id
+            self._names[nid] = rid
+            self._next_id += 1
+        return nid
+
+    def name_of(self, native_id: int) -> Hashable:
+        return self._names[native_id]
+
+    def pin(self, rid: Hashable) -> int:
+        """Keep the name's number although the request holds nothing (it waits in the scheduler)."""
+        nid = self.native_id(rid, create=True)
+        self._pinned.add(rid)
+        return nid
+
+    def unpin(self, rid: Hashable) -> None:
+        self._pinned.discard(rid)
+        self._forget_if_idle(rid)
+
+    def _forget_if_idle(self, rid: Hashable) -> None:
+        nid = self._ids.get(rid)
+        if nid is not None and rid not in self._pinned and not self._lib.ph_has(self._h, nid):
+            del self._ids[rid]
+            del self._names[nid]
 
     def _raise(self, code: int, rid: Hashable, what: str = ""):
         if code == host.UNKNOWN_REQUEST:
@@ -202,61 +229,59 @@ class CacheManager:
 
     def open(self, rid: Hashable) -> int:
         """Register a request and give it a state slot.  Holds no pages yet."""
-        if rid in self._ids:
+        if self.has(rid):
             raise CacheError(f"request {rid!r} is already open")
-        nid = self._next_id
-        slot = self._lib.ph_open(self._h, nid)
+        slot = self._lib.ph_open(self._h, self.native_id(rid, create=True))
         if slot < 0:
+            self._forget_if_idle(rid)
             self._raise(slot, rid)
-        self._next_id += 1
-        self._ids[rid] = nid
-        for e, t in self.state.items():      # fresh state starts at zero
-            t[slot].zero_()
+        self._fresh_state(slot)
         return slot
 
-    def adopt(self, rid: Hashable, native_id: int) -> None:
-        """The runtime opened request ``native_id`` itself (the step packer does): remember its name."""
-        self._ids[rid] = native_id
-        self._next_id = max(self._next_id, native_id + 1)
-        slot = self._lib.ph_state_slot(self._h, native_id)
+    def opened_by_runtime(self, rid: Hashable) -> None:
+        """The step packer opened the request: its state starts at zero."""
+        self._fresh_state(self._lib.ph_state_slot(self._h, self.native_id(rid)))
+
+    def _fresh_state(self, slot: int) -> None:
         for e, t in self.state.items():
             t[slot].zero_()
 
-    def reserve_id(self) -> int:
-        """A number for a request that the step packer is about to open."""
-        nid = self._next_id
-        self._next_id += 1
+    def has(self, rid: Hashable) -> bool:
+        nid = self._ids.get(rid)
+        return nid is not None and self._lib.ph_has(self._h, nid) == 1
+
+    def _open_id(self, rid: Hashable) -> int:
+        nid = self._ids.get(rid)
+        if nid is None or not self._lib.ph_has(self._h, nid):
+            raise CacheError(f"unknown request {rid!r}")
         return nid
 
-    def has(self, rid: Hashable) -> bool:
-        return rid in self._ids
-
     def length(self, rid: Hashable) -> int:
-        return self._lib.ph_length(self._h, self.native_id(rid))
+        return self._lib.ph_length(self._h, self._open_id(rid))
 
     def n_logical_pages(self, rid: Hashable) -> int:
         """Logical pages the request's tables cover (the fewest over the groups)."""
-        return self._lib.ph_n_logical_pages(self._h, self.native_id(rid))
+        return self._lib.ph_n_logical_pages(self._h, self._open_id(rid))
 
     def state_slot(self, rid: Hashable) -> int:
-        return self._lib.ph_state_slot(self._h, self.native_id(rid))
+        return self._lib.ph_state_slot(self._h, self._open_id(rid))
 
     def live_requests(self) -> List[Hashable]:
-        return list(self._ids)
+        return [rid for rid, nid in self._ids.items() if self._lib.ph_has(self._h, nid)]
 
     # ------------------------------------------------------------------ pages
     def pages_to_append(self, rid: Hashable, n_new: int) -> List[int]:
         """New pages each group must take so that the request can grow by ``n_new``
         tokens, after giving back what its windows have passed."""
-        self._lib.ph_pages_to_append(self._h, self.native_id(rid), int(n_new), self._scratch)
+        self._lib.ph_pages_to_append(self._h, self._open_id(rid), int(n_new), self._scratch)
         return list(self._scratch[:self._n_groups])
 
     def reclaimable(self, rid: Hashable) -> List[int]:
-        self._lib.ph_reclaimable(self._h, self.native_id(rid), self._scratch)
+        self._lib.ph_reclaimable(self._h, self._open_id(rid), self._scratch)
         return list(self._scratch[:self._n_groups])
 
     def can_append(self, rid: Hashable, n_new: int) -> bool:
-        return self._lib.ph_can_append(self._h, self.native_id(rid), int(n_new)) == 1
+        return self._lib.ph_can_append(self._h, self._open_id(rid), int(n_new)) == 1
 
     def can_admit(self, n_tokens: int) -> bool:
         """Could a request that holds nothing yet take ``n_tokens`` tokens (and a slot)?"""
@@ -264,7 +289,7 @@ class CacheManager:
 
     def release_passed(self, rid: Hashable) -> int:
         """Give back the pages of windowed groups that every future query has passed."""
-        n = self._lib.ph_release_passed(self._h, self.native_id(rid))
+        n = self._lib.ph_release_passed(self._h, self._open_id(rid))
         if n < 0:
             self._raise(n, rid)
         return n
@@ -274,21 +299,21 @@ class CacheManager:
         Either every group gets its pages or nothing changes (OutOfPages)."""
         if n_new <= 0:
             raise CacheError("append needs n_new > 0")
-        start = self._lib.ph_append(self._h, self.native_id(rid), int(n_new))
+        start = self._lib.ph_append(self._h, self._open_id(rid), int(n_new))
         if start < 0:
             self._raise(start, rid, f"{n_new} more tokens do not fit")
         return start
 
     def close(self, rid: Hashable) -> None:
         """Give back everything the request holds."""
-        rc = self._lib.ph_close(self._h, self.native_id(rid))
-        del self._ids[rid]
+        rc = self._lib.ph_close(self._h, self._open_id(rid))
+        self._forget_if_idle(rid)
         if rc < 0:
             self._raise(rc, rid)
 
     # ------------------------------------------------------------------ views for a step
     def table(self, rid: Hashable, group: int) -> List[int]:
-        nid = self.native_id(rid)
+        nid = self._open_id(rid)
         cap = 64
         while True:
             out = (ctypes.c_int * cap)()
@@ -301,7 +326,7 @@ class CacheManager:
         """slot = page * page_size + offset for positions [start, start + n)
         (active_buffer.cpp:255-279)."""
         out = (ctypes.c_int * max(1, n))()
-        rc = self._lib.ph_slots(self._h, self.native_id(rid), int(group), int(start), int(n), out)
+        rc = self._lib.ph_slots(self._h, self._open_id(rid), int(group), int(start), int(n), out)
         if rc < 0:
             self._raise(rc, rid, f"a position in [{start}, {start + n})")
         return list(out[:n])
@@ -321,7 +346,7 @@ class CacheManager:
         """Every page is free or held by exactly one request, every slot likewise; used by tests."""
         if self._lib.ph_check(self._h) != 0:
             raise CacheError("the cache's accounting is inconsistent: a page or slot is lost, held twice or freed twice")
-        live = sorted(self._lib.ph_state_slot(self._h, nid) for nid in self._ids.values())
+        live = sorted(self._lib.ph_state_slot(self._h, nid) for nid in self._ids.values() if self._lib.ph_has(self._h, nid))
         held = [s for s in range(self.max_requests) if self._lib.ph_slot_held(self._h, s)]
         if live != held:
             raise CacheError("state slots out of step with the live requests")

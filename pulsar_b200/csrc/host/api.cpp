@@ -265,3 +265,98 @@ PH_EXPORT int ph_step_pack(void* h, int n_entries, const int64_t* rids, const in
     }
     return total;
 }
+
+// ------------------------------------------------------------------ the scheduler
+#include "scheduler.h"
+
+PH_EXPORT void* ph_sched_new(void* cache, int max_running, int max_chunk_size) {
+    if (!cache || max_running <= 0 || max_chunk_size <= 0) return nullptr;
+    return new Scheduler(static_cast<Cache*>(cache), max_running, max_chunk_size);
+}
+PH_EXPORT void ph_sched_delete(void* h) { delete static_cast<Scheduler*>(h); }
+PH_EXPORT int ph_sched_add(void* h, int64_t rid, const int* tokens, int n, int max_new_tokens) {
+    return static_cast<Scheduler*>(h)->add_request(rid, tokens, n, max_new_tokens);
+}
+PH_EXPORT int ph_sched_extend(void* h, int64_t rid, const int* tokens, int n, int max_new_tokens) {
+    return static_cast<Scheduler*>(h)->extend_request(rid, tokens, n, max_new_tokens);
+}
+PH_EXPORT int ph_sched_has_work(void* h) { return static_cast<Scheduler*>(h)->has_work() ? 1 : 0; }
+// Decides a step and keeps it; returns the number of its entries, or kNeedsPreemption.
+PH_EXPORT int ph_sched_schedule(void* h, int allow_preempt) {
+    Scheduler* s = static_cast<Scheduler*>(h);
+    const int rc = s->schedule(allow_preempt != 0, &s->plan_buffer());
+    return rc < 0 ? rc : (int)s->last_plan().size();
+}
+// The step decided last: per entry the request, the index of its first token, the count and whether its last
+// logits are wanted; returns the total number of tokens.
+PH_EXPORT int ph_sched_plan(void* h, int64_t* rids, int* first, int* count, int* sample) {
+    const Scheduler* s = static_cast<Scheduler*>(h);
+    int total = 0, i = 0;
+    for (const PlanEntry& e : s->last_plan()) {
+        rids[i] = e.rid;
+        first[i] = e.first;
+        count[i] = e.count;
+        sample[i] = e.sample ? 1 : 0;
+        total += e.count;
+        ++i;
+    }
+    return total;
+}
+// The tokens of the step decided last, entry after entry.
+PH_EXPORT int ph_sched_plan_tokens(void* h, int* out) {
+    const Scheduler* s = static_cast<Scheduler*>(h);
+    int at = 0;
+    for (const PlanEntry& e : s->last_plan()) {
+        const Sequence* q = s->find(e.rid);
+        if (!q) return kUnknownRequest;
+        std::memcpy(out + at, q->tokens.data() + e.first, sizeof(int) * e.count);
+        at += e.count;
+    }
+    return at;
+}
+// The entries of the step decided last ran: their tokens are cached now.
+PH_EXPORT void ph_sched_on_step(void* h) {
+    Scheduler* s = static_cast<Scheduler*>(h);
+    s->on_step(s->last_plan());
+}
+PH_EXPORT int ph_sched_on_sampled(void* h, int64_t rid) { return static_cast<Scheduler*>(h)->on_sampled(rid); }
+PH_EXPORT int ph_sched_on_token(void* h, int64_t rid, int token, int eos_id) {
+    return static_cast<Scheduler*>(h)->on_token(rid, token, eos_id);
+}
+PH_EXPORT int ph_sched_drop_unread(void* h, int64_t rid) { return static_cast<Scheduler*>(h)->drop_unread(rid); }
+PH_EXPORT void ph_sched_park(void* h, int64_t rid) { static_cast<Scheduler*>(h)->park(rid); }
+PH_EXPORT void ph_sched_finish(void* h, int64_t rid) { static_cast<Scheduler*>(h)->finish(rid); }
+PH_EXPORT int ph_sched_knows(void* h, int64_t rid) { return static_cast<Scheduler*>(h)->find(rid) ? 1 : 0; }
+// info: n_tokens, max_new_tokens, n_cached, n_generated, admitted_at, preemptions, unread, spent.
+PH_EXPORT int ph_sched_info(void* h, int64_t rid, int64_t* info) {
+    const Sequence* q = static_cast<Scheduler*>(h)->find(rid);
+    if (!q) return kUnknownRequest;
+    info[0] = (int64_t)q->tokens.size();
+    info[1] = q->max_new_tokens;
+    info[2] = q->n_cached;
+    info[3] = q->n_generated;
+    info[4] = q->admitted_at;
+    info[5] = q->preemptions;
+    info[6] = q->unread;
+    info[7] = q->spent ? 1 : 0;
+    return 0;
+}
+PH_EXPORT int ph_sched_tokens(void* h, int64_t rid, int* out, int cap) {
+    const Sequence* q = static_cast<Scheduler*>(h)->find(rid);
+    if (!q) return kUnknownRequest;
+    std::memcpy(out, q->tokens.data(), sizeof(int) * std::min((int)q->tokens.size(), cap));
+    return (int)q->tokens.size();
+}
+PH_EXPORT int ph_sched_n_preemptions(void* h) { return static_cast<Scheduler*>(h)->n_preemptions(); }
+PH_EXPORT int ph_sched_max_running(void* h) { return static_cast<Scheduler*>(h)->max_running(); }
+// which: 0 = waiting (in order), 1 = running (in order); returns the count, fills min(count, cap).
+PH_EXPORT int ph_sched_list(void* h, int which, int64_t* out, int cap) {
+    const Scheduler* s = static_cast<Scheduler*>(h);
+    int n = 0;
+    if (which == 0) {
+        for (int64_t r : s->waiting()) { if (n < cap) out[n] = r; ++n; }
+    } else {
+        for (int64_t r : s->running()) { if (n < cap) out[n] = r; ++n; }
+    }
+    return n;
+}

@@ -144,8 +144,7 @@ class ModelRunner:
         s = len(entries)
         n_groups = len(cache.groups)
         fresh = [e.rid for e in entries if not cache.has(e.rid)]
-        fresh_ids = {rid: cache.reserve_id() for rid in fresh}
-        rids = host.longs([fresh_ids[e.rid] if e.rid in fresh_ids else cache.native_id(e.rid) for e in entries])
+        rids = host.longs([cache.native_id(e.rid, create=True) for e in entries])
         q_lens = [len(e.tokens) for e in entries]
         n = sum(q_lens)
         flat_tokens = [int(t) for e in entries for t in e.tokens]
@@ -160,6 +159,8 @@ class ModelRunner:
                                  0 if sampled_ids is None else int(sampled_ids.numel()), self.vocab, self.TABLE_BUCKET,
                                  starts, slots, widths_c, ctypes.byref(bad))
         if total < 0:
+            for rid in fresh:
+                cache._forget_if_idle(rid)
             if total == host.OUT_OF_SLOTS:
                 raise OutOfPages(f"{len(fresh)} new requests but {cache.n_free_slots()} free state slots")
             if total == host.OUT_OF_PAGES:
@@ -168,8 +169,8 @@ class ModelRunner:
             if total == host.RELEASED_PAGE:
                 raise StepError(f"request {who!r}: a position of the step lies in a released page")
             raise StepError(f"the host runtime refused the step (code {total}, entry of request {who!r})")
-        for rid, nid in fresh_ids.items():
-            cache.adopt(rid, nid)
+        for rid in fresh:
+            cache.opened_by_runtime(rid)
         starts, state_slots = list(starts), list(slots)
         kv_lens = [st + q for st, q in zip(starts, q_lens)]
         host_batch = HostBatch(q_lens, kv_lens, state_slots)

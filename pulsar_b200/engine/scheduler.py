@@ -23,18 +23,46 @@ sampled token that the host has not read yet stands in the request's token list 
 ``UNREAD`` (``on_sampled``), is filled in by ``on_token`` when it arrives, and is taken
 back by ``drop_unread`` if the request turned out to have ended one token earlier.
 
-The scheduler is host code over the cache manager's accounting and runs without a GPU.
+The decisions are taken by the host runtime (C++, csrc/host/scheduler.cpp) over the cache's accounting;
+this class names the requests, moves token lists across and turns status codes into exceptions.  It runs
+without a GPU.
 """
 from __future__ import annotations
 
-from collections import deque
-from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional
+import ctypes
+from collections.abc import Mapping
+from dataclasses import dataclass
+from typing import Hashable, Iterator, List, Optional
 
+from .. import host
 from ..cache.manager import CacheManager
 
-
 UNREAD = -1        # stands in a token list for a sampled token that has not been read from the device yet
+
+_NEVER_FITS, _STILL_RUNNING, _HAS_UNREAD, _NO_UNREAD, _NEEDS_PREEMPTION = -20, -21, -22, -23, -24
+
+_SIGNATURES = {
+    "ph_sched_new": (ctypes.c_void_p, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]),
+    "ph_sched_delete": (None, [ctypes.c_void_p]),
+    "ph_sched_add": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, host._IP, ctypes.c_int, ctypes.c_int]),
+    "ph_sched_extend": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, host._IP, ctypes.c_int, ctypes.c_int]),
+    "ph_sched_has_work": (ctypes.c_int, [ctypes.c_void_p]),
+    "ph_sched_schedule": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int]),
+    "ph_sched_plan": (ctypes.c_int, [ctypes.c_void_p, host._LP, host._IP, host._IP, host._IP]),
+    "ph_sched_plan_tokens": (ctypes.c_int, [ctypes.c_void_p, host._IP]),
+    "ph_sched_on_step": (None, [ctypes.c_void_p]),
+    "ph_sched_on_sampled": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64]),
+    "ph_sched_on_token": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int]),
+    "ph_sched_drop_unread": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64]),
+    "ph_sched_park": (None, [ctypes.c_void_p, ctypes.c_int64]),
+    "ph_sched_finish": (None, [ctypes.c_void_p, ctypes.c_int64]),
+    "ph_sched_knows": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64]),
+    "ph_sched_info": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, host._LP]),
+    "ph_sched_tokens": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, host._IP, ctypes.c_int]),
+    "ph_sched_n_preemptions": (ctypes.c_int, [ctypes.c_void_p]),
+    "ph_sched_max_running": (ctypes.c_int, [ctypes.c_void_p]),
+    "ph_sched_list": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, host._LP, ctypes.c_int]),
+}
 
 
 class SchedulerError(RuntimeError):
@@ -43,7 +71,7 @@ class SchedulerError(RuntimeError):
 
 @dataclass
 class SequenceState:
-    """Scheduling state of one request: all its tokens so far and how many are cached."""
+    """A snapshot of one request's scheduling state: all its tokens so far and how many are cached."""
     rid: Hashable
     tokens: List[int]
     max_new_tokens: int
@@ -68,18 +96,56 @@ class Scheduled:
     sample: bool
 
 
+class _Sequences(Mapping):
+    """``scheduler.seqs``: the requests the scheduler knows, by name; a lookup takes a snapshot."""
+
+    def __init__(self, owner: "Scheduler"):
+        self._o = owner
+
+    def __contains__(self, rid) -> bool:
+        return rid in self._o._known
+
+    def __iter__(self) -> Iterator[Hashable]:
+        return iter(list(self._o._known))
+
+    def __len__(self) -> int:
+        return len(self._o._known)
+
+    def __getitem__(self, rid) -> SequenceState:
+        o = self._o
+        if rid not in o._known:
+            raise KeyError(rid)
+        nid = o.cache.native_id(rid)
+        info = (ctypes.c_int64 * 8)()
+        o._lib.ph_sched_info(o._h, nid, info)
+        n = int(info[0])
+        buf = (ctypes.c_int * max(1, n))()
+        o._lib.ph_sched_tokens(o._h, nid, buf, n)
+        return SequenceState(rid, list(buf[:n]), int(info[1]), int(info[2]), int(info[3]), int(info[4]), int(info[5]),
+                             int(info[6]), bool(info[7]))
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, max_running: int, max_chunk_size: int):
         if max_running <= 0 or max_chunk_size <= 0:
             raise SchedulerError("max_running and max_chunk_size must be > 0")
         self.cache = cache
-        self.max_running = min(int(max_running), cache.max_requests)
+        self._lib = host.lib()
+        for name, (res, args) in _SIGNATURES.items():
+            f = getattr(self._lib, name)
+            f.restype, f.argtypes = res, args
+        self._h = self._lib.ph_sched_new(cache._h, int(max_running), int(max_chunk_size))
+        if not self._h:
+            raise SchedulerError("the host runtime refused the scheduler's sizes")
+        self.max_running = self._lib.ph_sched_max_running(self._h)
         self.max_chunk_size = int(max_chunk_size)
-        self.waiting: Deque[Hashable] = deque()
-        self.running: List[Hashable] = []
-        self.seqs: Dict[Hashable, SequenceState] = {}
-        self._admissions = 0
-        self.n_preemptions = 0
+        self._known: set = set()
+        self.seqs = _Sequences(self)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.ph_sched_delete(h)
 
     # ------------------------------------------------------------------ bookkeeping
     def _pages(self, n_tokens: int) -> int:
@@ -88,208 +154,125 @@ class Scheduler:
     def _capacity_pages(self) -> int:
         return min(g.allocator.n for g in self.cache.groups) if self.cache.groups else 1 << 30
 
-    def _free_pages(self) -> int:
-        return min(self.cache.n_free_pages()) if self.cache.groups else 1 << 30
+    def _names(self, which: int) -> List[Hashable]:
+        cap = 64
+        while True:
+            out = (ctypes.c_int64 * cap)()
+            n = self._lib.ph_sched_list(self._h, which, out, cap)
+            if n <= cap:
+                return [self.cache.name_of(int(v)) for v in out[:n]]
+            cap = n
 
-    def _held_back(self) -> int:
-        """Pages that running prompts still need to reach their last known token plus one."""
-        total = 0
-        for rid in self.running:
-            s = self.seqs[rid]
-            have = self._pages(s.n_cached)
-            total += max(0, self._pages(len(s.tokens) + 1) - have)
-        return total
+    @property
+    def waiting(self) -> List[Hashable]:
+        return self._names(0)
+
+    @property
+    def running(self) -> List[Hashable]:
+        return self._names(1)
+
+    @property
+    def n_preemptions(self) -> int:
+        return self._lib.ph_sched_n_preemptions(self._h)
 
     def add_request(self, rid: Hashable, tokens: List[int], max_new_tokens: int) -> None:
-        if rid in self.seqs:
+        if rid in self._known:
             raise SchedulerError(f"request {rid!r} is already known")
         if len(tokens) == 0:
             raise SchedulerError("a request needs at least one prompt token")
-        if self._pages(len(tokens) + max(0, max_new_tokens)) > self._capacity_pages():
-            raise SchedulerError(f"request {rid!r}: {len(tokens)} prompt tokens + {max_new_tokens} new tokens can never "
-                                 f"fit the pool of {self._capacity_pages()} pages of {self.cache.page_size}")
-        self.seqs[rid] = SequenceState(rid, list(tokens), int(max_new_tokens))
-        self.waiting.append(rid)
+        nid = self.cache.pin(rid)
+        rc = self._lib.ph_sched_add(self._h, nid, host.ints([int(t) for t in tokens]), len(tokens), int(max_new_tokens))
+        if rc < 0:
+            self.cache.unpin(rid)
+            if rc == _NEVER_FITS:
+                raise SchedulerError(f"request {rid!r}: {len(tokens)} prompt tokens + {max_new_tokens} new tokens can never "
+                                     f"fit the pool of {self._capacity_pages()} pages of {self.cache.page_size}")
+            raise SchedulerError(f"request {rid!r}: the host runtime answered {rc}")
+        self._known.add(rid)
 
     def extend_request(self, rid: Hashable, tokens: List[int], max_new_tokens: int) -> None:
         """More tokens for a known request that is not running (a further turn): it keeps
         its pages and waits for admission again."""
-        s = self.seqs.get(rid)
-        if s is None:
+        if rid not in self._known:
             raise SchedulerError(f"unknown request {rid!r}")
-        if rid in self.running:
+        rc = self._lib.ph_sched_extend(self._h, self.cache.native_id(rid), host.ints([int(t) for t in tokens] or [0]),
+                                       len(tokens), int(max_new_tokens))
+        if rc == _STILL_RUNNING:
             raise SchedulerError(f"request {rid!r} is running; feed it when its turn is over")
-        if self._pages(len(s.tokens) + len(tokens) + max(0, max_new_tokens)) > self._capacity_pages():
+        if rc == _NEVER_FITS:
             raise SchedulerError(f"request {rid!r} would outgrow the pool")
-        if s.unread:
+        if rc == _HAS_UNREAD:
             raise SchedulerError(f"request {rid!r} still has a sampled token that was not read")
-        s.tokens.extend(tokens)
-        s.max_new_tokens = int(max_new_tokens)
-        s.n_generated = 0
-        s.spent = False
-        if rid not in self.waiting:
-            self.waiting.append(rid)
+        if rc < 0:
+            raise SchedulerError(f"request {rid!r}: the host runtime answered {rc}")
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return self._lib.ph_sched_has_work(self._h) == 1
 
     # ------------------------------------------------------------------ one step
-    def _preempt(self, rid: Hashable) -> None:
-        s = self.seqs[rid]
-        if self.cache.has(rid):
-            self.cache.close(rid)
-        s.n_cached = 0
-        s.preemptions += 1
-        self.n_preemptions += 1
-        self.running.remove(rid)
-        self.waiting.appendleft(rid)
-
     def schedule(self, allow_preempt: bool = True) -> Optional[List[Scheduled]]:
         """Decide the next step.  Changes nothing in the cache except by preemption; the
         step function takes the pages when it runs the entries.  With ``allow_preempt``
         false (a step is still in flight, so some tokens are UNREAD and nothing may be
         recomputed from them) the answer is None where a request would have to be preempted."""
-        budget = self.max_chunk_size
-        out: List[Scheduled] = []
-        planned: set = set()         # requests that already have an entry in this step
-        planned_pages = 0            # pages this step's entries will take
-        ps = self.cache.page_size
-
-        def pages_for(rid, n_new) -> int:
-            if self.cache.has(rid) and self.cache.groups:
-                # pages to reach the new length, beyond the logical pages the request already has
-                return max(0, -(-(self.cache.length(rid) + n_new) // ps) - self.cache.n_logical_pages(rid))
-            return self._pages(n_new)
-
-        def room_for(rid, n_new) -> bool:
-            return pages_for(rid, n_new) <= self._free_pages() - planned_pages
-
-        def take(rid, n_new) -> None:
-            nonlocal planned_pages
-            planned_pages += pages_for(rid, n_new)
-
-        def fits(rid) -> int:
-            """Most new tokens of ``rid`` that the free pages allow in this step."""
-            avail = max(0, self._free_pages() - planned_pages)
-            in_last = (-self.cache.length(rid)) % self.cache.page_size if self.cache.has(rid) else 0
-            return avail * self.cache.page_size + in_last
-
-        # 1. decode tokens, oldest admission first; preempt the youngest when pages run out.
-        decoders = [r for r in self.running
-                    if self.seqs[r].pending == 1 and self.seqs[r].n_cached > 0 and not self.seqs[r].spent]
-        for rid in sorted(decoders, key=lambda r: self.seqs[r].admitted_at):
-            if rid not in self.running:
-                continue                      # preempted below
-            if budget <= 0:
-                break
-            while not room_for(rid, 1):
-                if not allow_preempt:
-                    return None
-                victim = max(self.running, key=lambda r: self.seqs[r].admitted_at)
-                was_planned = [e for e in out if e.rid == victim]
-                for e in was_planned:          # its planned entry (and pages) leave the step
-                    out.remove(e)
-                    planned.discard(victim)
-                    budget += len(e.tokens)
-                    planned_pages -= pages_for(victim, len(e.tokens))
-                self._preempt(victim)
-                if victim == rid:
-                    break
-            if rid not in self.running:
-                continue
-            s = self.seqs[rid]
-            out.append(Scheduled(rid, [s.tokens[-1]], True))
-            planned.add(rid)
-            take(rid, 1)
-            budget -= 1
-
-        # 2. prompts in progress, in running order.
-        for rid in list(self.running):
-            s = self.seqs[rid]
-            if budget <= 0:
-                break
-            if rid in planned or s.pending == 0 or s.spent:
-                continue
-            if s.pending == 1 and s.n_cached > 0:
-                continue                      # a decoder that found no budget above
-            n = min(s.pending, budget, fits(rid))     # pages are held back for it, so it rarely shrinks
-            if n <= 0:
-                continue
-            out.append(Scheduled(rid, s.tokens[s.n_cached:s.n_cached + n], n == s.pending))
-            planned.add(rid)
-            take(rid, n)
-            budget -= n
-
-        # 3. admission, first-in first-out.
-        while self.waiting and len(self.running) < self.max_running and budget > 0:
-            rid = self.waiting[0]
-            s = self.seqs[rid]
-            have = self._pages(s.n_cached) if self.cache.has(rid) else 0
-            need_all = self._pages(len(s.tokens) + 1) - have
-            # what running requests still need (this step's pages included) stays theirs
-            if need_all > self._free_pages() - self._held_back():
-                break                          # head of the queue waits; nobody overtakes it
-            if not self.cache.has(rid) and self.cache.n_free_slots() - sum(1 for e in out if not self.cache.has(e.rid)) <= 0:
-                break
-            planned.add(rid)
-            self.waiting.popleft()
-            self.running.append(rid)
-            s.admitted_at = self._admissions
-            self._admissions += 1
-            n = min(s.pending, budget)
-            out.append(Scheduled(rid, s.tokens[s.n_cached:s.n_cached + n], n == s.pending))
-            take(rid, n)
-            budget -= n
+        n = self._lib.ph_sched_schedule(self._h, 1 if allow_preempt else 0)
+        if n == _NEEDS_PREEMPTION:
+            return None
+        if n < 0:
+            raise SchedulerError(f"the host runtime answered {n}")
+        if n == 0:
+            return []
+        rids, first = (ctypes.c_int64 * n)(), (ctypes.c_int * n)()
+        count, sample = (ctypes.c_int * n)(), (ctypes.c_int * n)()
+        total = self._lib.ph_sched_plan(self._h, rids, first, count, sample)
+        tokens = (ctypes.c_int * max(1, total))()
+        self._lib.ph_sched_plan_tokens(self._h, tokens)
+        out, at = [], 0
+        for i in range(n):
+            c = count[i]
+            out.append(Scheduled(self.cache.name_of(int(rids[i])), list(tokens[at:at + c]), bool(sample[i])))
+            at += c
+        self._last = out
         return out
 
     def on_step(self, entries: List[Scheduled]) -> None:
-        """The entries ran: their tokens are cached now."""
-        for e in entries:
-            self.seqs[e.rid].n_cached += len(e.tokens)
+        """The entries of the step decided last ran: their tokens are cached now."""
+        last = getattr(self, "_last", None)
+        if entries is not last and [(e.rid, len(e.tokens)) for e in entries] != [(e.rid, len(e.tokens)) for e in last or []]:
+            raise SchedulerError("on_step takes the step that schedule() decided last")
+        self._lib.ph_sched_on_step(self._h)
 
     def on_sampled(self, rid: Hashable) -> None:
         """A token was sampled for ``rid`` on the device and is not read yet."""
-        s = self.seqs[rid]
-        s.tokens.append(UNREAD)
-        s.unread += 1
-        s.n_generated += 1
-        if s.n_generated >= s.max_new_tokens:
-            s.spent = True
+        self._lib.ph_sched_on_sampled(self._h, self.cache.native_id(rid))
 
     def on_token(self, rid: Hashable, token: int, eos_id: int) -> bool:
         """The oldest unread token of ``rid`` has arrived (or, if none was announced by
         ``on_sampled``, a token was sampled and read at once).  Returns True when the
         request's turn is over (stop token or budget,
         pulsar-core/src/runtime/engine.cpp:727-729)."""
-        s = self.seqs[rid]
-        if s.unread == 0:
-            self.on_sampled(rid)
-        s.tokens[len(s.tokens) - s.unread] = int(token)
-        s.unread -= 1
-        spent_by_now = s.n_generated - s.unread >= s.max_new_tokens
-        return (eos_id >= 0 and int(token) == eos_id) or spent_by_now
+        rc = self._lib.ph_sched_on_token(self._h, self.cache.native_id(rid), int(token), int(eos_id))
+        if rc < 0:
+            raise SchedulerError(f"unknown request {rid!r}")
+        return rc == 1
 
     def drop_unread(self, rid: Hashable) -> None:
         """The newest unread token of ``rid`` is void: the request had ended with the token
         before it.  (The step that sampled it has cached that last token, which is all it leaves.)"""
-        s = self.seqs[rid]
-        if s.unread <= 0 or s.tokens[-1] != UNREAD:
+        rc = self._lib.ph_sched_drop_unread(self._h, self.cache.native_id(rid))
+        if rc < 0:
             raise SchedulerError(f"request {rid!r} has no unread token to drop")
-        s.tokens.pop()
-        s.unread -= 1
-        s.n_generated -= 1
 
     def park(self, rid: Hashable) -> None:
         """The turn is over; the request leaves the running set and keeps its pages."""
-        if rid in self.running:
-            self.running.remove(rid)
+        if rid in self._known:
+            self._lib.ph_sched_park(self._h, self.cache.native_id(rid))
 
     def finish(self, rid: Hashable) -> None:
         """Forget the request and give back what it holds."""
-        if rid in self.running:
-            self.running.remove(rid)
-        if rid in self.waiting:
-            self.waiting.remove(rid)
-        if self.cache.has(rid):
+        if rid in self._known:
+            self._lib.ph_sched_finish(self._h, self.cache.native_id(rid))
+            self._known.discard(rid)
+            self.cache.unpin(rid)
+        elif self.cache.has(rid):
             self.cache.close(rid)
-        self.seqs.pop(rid, None)
