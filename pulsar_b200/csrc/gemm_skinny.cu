@@ -142,9 +142,10 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT*
     }
 }
 
-// kUnroll: k-blocks whose weight loads a thread keeps in flight.  Few blocks on the machine (the
-// per-layer projections): 8, which costs 128 registers; thousands of blocks (gate/up, lm_head): 4, so
-// that more blocks are resident per SM.
+// kUnroll: k-blocks whose weight loads a thread keeps in flight.  8 costs 128 registers, so that two blocks
+// share an SM; 4 lets three share it.  A product whose blocks all fit two per SM takes 8; one with more blocks
+// takes 4, so that it does not need a second, nearly empty round of blocks (the QKV product of the 8B sizes:
+// 384 blocks on 148 SMs) and, with thousands of blocks (gate/up, lm_head), more of them are resident.
 template <int NT, int kUnroll>
 int launch_u(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
     const bf16* xp = (const bf16*)x;
@@ -159,10 +160,19 @@ int launch_u(int mode, int out_dtype, const void* x, const void* w, void* out, i
     return launch_pdl(gemm_skinny_kernel<NT, kPlain, float, kUnroll>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
 }
 
+int sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) v = 0;
+        return v > 0 ? v : 148;
+    }();
+    return n;
+}
+
 template <int NT>
 int launch(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
     const int tiles = (mode == kSwiGLU) ? N / 2 / 8 : N / kRows;
-    if (tiles >= 1024) return launch_u<NT, 4>(mode, out_dtype, x, w, out, M, N, K, stream);
+    if (tiles > 2 * sm_count()) return launch_u<NT, 4>(mode, out_dtype, x, w, out, M, N, K, stream);
     return launch_u<NT, 8>(mode, out_dtype, x, w, out, M, N, K, stream);
 }
 
