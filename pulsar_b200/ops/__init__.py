@@ -60,7 +60,8 @@ _SIGNATURES = {
     "pb_gemm_tcgen05_supported": [_I, _I, _I, _I],
     "pb_gemm_tcgen05_error": [],
     "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
-    "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _P, _P],
+    "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P],
+    "pb_sample_workspace": [_I],
     "pb_argmax": [_P, _I, _I, _P, _P, _P],
 }
 _fns = {}
@@ -214,12 +215,14 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 _argmax_keys = {}
+_sample_work = {}
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
            top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
-           uniform: Optional[torch.Tensor] = None) -> None:
-    """out[r] = argmax (temperature <= 0 or None) or a draw from the filtered softmax."""
+           uniform: Optional[torch.Tensor] = None, any_greedy: bool = True) -> None:
+    """out[r] = argmax (temperature <= 0 or None) or a draw from the filtered softmax.
+    ``any_greedy=False`` promises that every row has a temperature > 0."""
     _cuda(logits, out, temperature, top_k, top_p, uniform)
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == rows
@@ -227,14 +230,21 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
     assert top_k is None or (top_k.dtype == torch.int32 and top_k.numel() == rows)
     assert top_p is None or (top_p.dtype == torch.float32 and top_p.numel() == rows)
     assert uniform is None or (uniform.dtype == torch.float32 and uniform.numel() == rows)
+    keys = _argmax_keys.get(logits.device)
+    if keys is None or keys.numel() < rows:
+        keys = _argmax_keys[logits.device] = torch.empty(max(rows, 256), dtype=torch.int64, device=logits.device)
     if temperature is None:                       # all rows greedy: many blocks per row
-        keys = _argmax_keys.get(logits.device)
-        if keys is None or keys.numel() < rows:
-            keys = _argmax_keys[logits.device] = torch.empty(max(rows, 256), dtype=torch.int64, device=logits.device)
         check(fn("pb_argmax")(_p(logits), rows, vocab, _p(keys), _p(out), stream()), "argmax", kernels=2)
         return
-    check(fn("pb_sample")(_p(logits), rows, vocab, _p(temperature), _p(top_k), _p(top_p), _p(uniform), _p(out),
-                          stream()), "sample")
+    if uniform is None:
+        raise KernelError("sample: rows with a temperature need uniform numbers")
+    need = int(fn("pb_sample_workspace")(rows)) * 1024
+    work = _sample_work.get(logits.device)
+    if work is None or work.numel() < need:
+        work = _sample_work[logits.device] = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=logits.device)
+    filtered = top_k is not None or top_p is not None
+    check(fn("pb_sample")(_p(logits), rows, vocab, _p(temperature), _p(top_k), _p(top_p), _p(uniform), 1 if any_greedy else 0,
+                          _p(work), _p(keys), _p(out), stream()), "sample", kernels=(2 if any_greedy else 0) + (5 if filtered else 2))
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> bool:

@@ -76,7 +76,7 @@ class Sampler:
             packed = torch.tensor([[p.temperature for p in params], [p.top_p for p in params], uniform],
                                   dtype=torch.float32).to(self.device, non_blocking=True)
             top_k = torch.tensor([p.top_k for p in params], dtype=torch.int32).to(self.device, non_blocking=True)
-            ops.sample(logits, out, packed[0], top_k, packed[1], packed[2])
+            ops.sample(logits, out, packed[0], top_k, packed[1], packed[2], any_greedy=any(p.greedy for p in params))
         return out
 
     def sample(self, logits: torch.Tensor, params: Sequence[GenerationParams],
