@@ -325,11 +325,12 @@ def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tenso
     silu_mul(gate_up, out)
 
 
-def decode_splits(n_seqs: int, n_kv_heads: int) -> int:
+def decode_splits(n_seqs: int, n_kv_heads: int, table_tokens: int = 4096) -> int:
     """Splits of the keys per (sequence, kv head): as many as fit one wave of two blocks on
-    each of the 148 SMs, at most 16.  A function of the batch alone, so that a captured step
-    stays valid while its sequences grow."""
-    return max(1, min(16, 296 // max(1, n_seqs * n_kv_heads)))
+    each of the 148 SMs, at most 32 and at most one per 256 tokens that the block table can name.
+    A function of the batch and of the block table's width alone (the width of a step of single
+    tokens grows in buckets), so that a captured step stays valid while its sequences grow."""
+    return max(1, min(32, 296 // max(1, n_seqs * n_kv_heads), max(1, table_tokens // 256)))
 
 
 _TICKETS = 1 << 16
@@ -455,7 +456,7 @@ def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, wind
     applies (bfloat16, head size 128, pages of 8 or more), else the mma.sync kernel (bfloat16, head
     size 64 or 128), else the generic kernel.  ``PULSAR_ATTENTION=mma`` leaves the tcgen05 kernel out."""
     if ctx.all_decode:
-        n_splits = decode_splits(ctx.n_seqs, cache.k_pool.shape[1])
+        n_splits = decode_splits(ctx.n_seqs, cache.k_pool.shape[1], cache.block_table.shape[1] * cache.k_pool.shape[2])
         partial = ctx.scratch("attn.partial", (ctx.n_seqs * q.shape[1] * n_splits * (q.shape[2] + 2),), torch.float32)
         paged_attention_decode(q, cache.k_pool, cache.v_pool, out, partial, cache.block_table, ctx.kv_len, scale,
                                window, n_splits)
