@@ -462,13 +462,28 @@ def attention(ctx, q: torch.Tensor, cache, out: torch.Tensor, scale: float, wind
                                window, n_splits)
         return
     hkv, page_size = cache.k_pool.shape[1], cache.k_pool.shape[2]
-    if ATTENTION_BACKEND != "mma" and prefill_tcgen05_supported(q.dtype, q.shape[1], hkv, q.shape[2], page_size):
-        paged_attention_prefill_tcgen05(q, cache.k_pool, cache.v_pool, out, cache.block_table, ctx.cu_q, ctx.kv_len,
-                                        prefill_tcgen05_tiles(ctx.host.q_lens), scale, window)
-        return
-    if prefill_tc_supported(q.dtype, q.shape[1], hkv, q.shape[2], page_size):
-        paged_attention_prefill_tc(q, cache.k_pool, cache.v_pool, out, cache.block_table, ctx.cu_q, ctx.kv_len,
-                                   prefill_tc_tiles(ctx.host.q_lens), scale, window)
+    use_tcgen05 = ATTENTION_BACKEND != "mma" and prefill_tcgen05_supported(q.dtype, q.shape[1], hkv, q.shape[2], page_size)
+    if use_tcgen05 or prefill_tc_supported(q.dtype, q.shape[1], hkv, q.shape[2], page_size):
+        # The scheduler puts the decoded tokens of a mixed step first: those sequences take the decode kernel
+        # (a tile of 64 or 128 query rows for one token would waste the tensor cores on every key tile), the
+        # portions behind them the prefill kernel, over the same arrays.
+        q_lens = ctx.host.q_lens
+        n_dec = 0
+        while n_dec < len(q_lens) and q_lens[n_dec] == 1:
+            n_dec += 1
+        table, cu_q, kv_len = cache.block_table, ctx.cu_q, ctx.kv_len
+        if n_dec > 0:
+            n_splits = decode_splits(n_dec, hkv, table.shape[1] * page_size)
+            partial = ctx.scratch("attn.partial", (n_dec * q.shape[1] * n_splits * (q.shape[2] + 2),), torch.float32)
+            paged_attention_decode(q[:n_dec], cache.k_pool, cache.v_pool, out[:n_dec], partial, table[:n_dec], kv_len[:n_dec],
+                                   scale, window, n_splits)
+            table, cu_q, kv_len, q_lens = table[n_dec:], cu_q[n_dec:], kv_len[n_dec:], q_lens[n_dec:]
+        if use_tcgen05:
+            paged_attention_prefill_tcgen05(q, cache.k_pool, cache.v_pool, out, table, cu_q, kv_len,
+                                            prefill_tcgen05_tiles(q_lens), scale, window)
+        else:
+            paged_attention_prefill_tc(q, cache.k_pool, cache.v_pool, out, table, cu_q, kv_len, prefill_tc_tiles(q_lens),
+                                       scale, window)
         return
     paged_attention_generic(q, cache.k_pool, cache.v_pool, out, cache.block_table, ctx.cu_q, ctx.kv_len,
                             ctx.seq_of_token, scale, window)

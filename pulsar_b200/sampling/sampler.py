@@ -7,10 +7,11 @@ otherwise softmax(logits / temperature), top_k > 0 keeps the k most probable, to
 (0, 1) keeps a token while the mass before it is <= top_p, both give the intersection;
 seed >= 0 makes a request reproducible, seed < 0 draws a fresh seed.
 
-The reference samples one row at a time with a device-to-host read each.  Here one
-kernel handles all rows of the step and the chosen ids come back in one copy; the
-uniform number of each stochastic row comes from that request's own host generator, so a
-request's tokens do not depend on what else is in the batch.
+The reference samples one row at a time with a device-to-host read each.  Here a few
+kernels handle all rows of the step (many blocks per row) and the chosen ids stay on the
+device for the next step or come back in one copy; the uniform number of each stochastic
+row comes from that request's own host generator, so a request's tokens do not depend on
+what else is in the batch.
 """
 from __future__ import annotations
 

@@ -445,6 +445,48 @@ def test_attention_prefill_tcgen05_growing_scores():
     close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, None), TOL[dtype])
 
 
+@pytest.mark.parametrize("d,page", [(128, 16), (64, 8)])
+def test_attention_dispatch_splits_a_mixed_step(d, page):
+    """ops.attention on a step whose first sequences bring one token each (the scheduler's order): those take the
+    decode kernel, the portions behind them the prefill kernel; single tokens further back stay with the portions."""
+    from pulsar_b200 import ops
+
+    class Host:
+        pass
+
+    class Ctx:
+        def __init__(self, case, lens_q):
+            self.host = Host()
+            self.host.q_lens = list(lens_q)
+            self.cu_q, self.kv_len, self.seq_of_token = dev(case["cu"]), dev(case["kv"]), dev(case["seq_of"])
+            self.n_seqs, self.all_decode = len(lens_q), max(lens_q) == 1
+            self._scratch = {}
+
+        def scratch(self, tag, shape, dtype=None):
+            key = (tag, tuple(shape), dtype)
+            if key not in self._scratch:
+                self._scratch[key] = torch.full(tuple(shape), float("nan"), dtype=dtype, device="cuda")
+            return self._scratch[key]
+
+    class View:
+        pass
+
+    dtype, hq, hkv = torch.bfloat16, 8, 2
+    g = torch.Generator().manual_seed(17)
+    lens_q = [1, 1, 1, 150, 1, 33, 2]
+    lens_kv = [300, 17, 1, 150, 77, 260, 140]
+    case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype, spike=(0, 3, hq - 1))
+    view = View()
+    view.k_pool, view.v_pool, view.block_table = dev(case["kp"]), dev(case["vp"]), dev(case["table"])
+    scale = 1.0 / math.sqrt(d)
+    for window in (None, 90):
+        out = torch.full((sum(lens_q), hq, d), float("nan"), dtype=dtype, device="cuda")
+        before = ops.LAUNCHES
+        ops.attention(Ctx(case, lens_q), dev(case["q"]), view, out, scale, window)
+        assert ops.LAUNCHES - before in (2, 3)                # decode (+ combine when the keys are split), one prefill kernel
+        close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window), TOL[dtype])
+
+
 def test_attention_prefill_tcgen05_applicability():
     from pulsar_b200 import ops
     assert not ops.prefill_tcgen05_supported(torch.float32, 32, 8, 128, 16)
