@@ -54,6 +54,7 @@ class Qwen3Config:
     attention_bias: bool
     initializer_range: float
     architecture: str = "Qwen3ForCausalLM"
+    layer_types: Optional[tuple] = None        # per layer "full_attention" | "sliding_attention", where config.json lists them
 
     @classmethod
     def from_dict(cls, raw: Dict[str, Any]) -> "Qwen3Config":
@@ -83,6 +84,7 @@ class Qwen3Config:
             hidden_act=str(raw.get("hidden_act", "silu")),
             attention_bias=bool(raw.get("attention_bias", False)),
             initializer_range=float(raw.get("initializer_range", 0.02)),
+            layer_types=None if raw.get("layer_types") is None else tuple(str(t) for t in raw["layer_types"]),
         )
         if raw.get("rope_scaling") not in (None, {}):
             raise ConfigError("config.json: rope_scaling is not implemented by this engine; found "
@@ -110,16 +112,33 @@ class Qwen3Config:
             raise ConfigError("config.json: rms_norm_eps and rope_theta must be positive")
         if self.use_sliding_window and (self.sliding_window is None or self.sliding_window <= 0):
             raise ConfigError("config.json: use_sliding_window=true needs a positive sliding_window")
+        if self.layer_types is not None:
+            if len(self.layer_types) != self.num_hidden_layers:
+                raise ConfigError(f"config.json: layer_types names {len(self.layer_types)} layers, num_hidden_layers is "
+                                  f"{self.num_hidden_layers}")
+            for i, kind in enumerate(self.layer_types):
+                if kind not in ("full_attention", "sliding_attention"):
+                    raise ConfigError(f"config.json: layer_types[{i}] = '{kind}' is not implemented "
+                                      "(known: full_attention, sliding_attention)")
+                if kind == "sliding_attention" and (self.sliding_window is None or self.sliding_window <= 0):
+                    raise ConfigError(f"config.json: layer_types[{i}] slides but sliding_window is not a positive number")
 
     def to_dict(self) -> Dict[str, Any]:
         out = {f.name: getattr(self, f.name) for f in fields(self) if f.name != "architecture"}
         out["architectures"] = [self.architecture]
         out["model_type"] = "qwen3"
         out["rope_scaling"] = None
+        if self.layer_types is None:
+            del out["layer_types"]
+        else:
+            out["layer_types"] = list(self.layer_types)
         return out
 
     def layer_window(self, layer: int) -> Optional[int]:
-        """Layers with index >= max_window_layers slide when use_sliding_window is set."""
+        """Where config.json lists ``layer_types`` they decide; else layers with index >=
+        max_window_layers slide when use_sliding_window is set."""
+        if self.layer_types is not None:
+            return self.sliding_window if self.layer_types[layer] == "sliding_attention" else None
         if not self.use_sliding_window or self.sliding_window is None:
             return None
         return self.sliding_window if layer >= self.max_window_layers else None

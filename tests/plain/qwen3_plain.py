@@ -87,9 +87,11 @@ def swiglu_mlp(h: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down
 
 
 def layer_window(cfg: dict, layer: int) -> int | None:
-    """Window of a layer by the architecture's own keys: layers with index >=
-    max_window_layers slide when use_sliding_window is set (keys the reference ignores,
-    pulsar/src/pulsar/checkpoint.py:36-51 reads none of them)."""
+    """Window of a layer by the architecture's own keys: a ``layer_types`` list decides where it is
+    given; else layers with index >= max_window_layers slide when use_sliding_window is set (keys the
+    reference ignores, pulsar/src/pulsar/checkpoint.py:36-51 reads none of them)."""
+    if cfg.get("layer_types") is not None:
+        return int(cfg["sliding_window"]) if cfg["layer_types"][layer] == "sliding_attention" else None
     if not cfg.get("use_sliding_window", False) or cfg.get("sliding_window") is None:
         return None
     return int(cfg["sliding_window"]) if layer >= int(cfg.get("max_window_layers", 0)) else None

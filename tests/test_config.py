@@ -77,6 +77,20 @@ def test_window_per_layer_and_model_spec():
     assert config_from_dict(TINY_A).model_spec().blocks[1].mixer.window is None
 
 
+def test_layer_types_decide_where_they_are_listed():
+    kinds = ["sliding_attention", "full_attention", "full_attention", "sliding_attention"]
+    cfg = config_from_dict(dict(TINY_C, layer_types=kinds))                  # TINY_C alone: layers 2 and 3 slide
+    assert [cfg.layer_window(i) for i in range(4)] == [12, None, None, 12]
+    assert [b.mixer.window for b in cfg.model_spec().blocks] == [12, None, None, 12]
+    assert config_from_dict(cfg.to_dict()) == cfg
+    with pytest.raises(ConfigError, match="names 3 layers"):
+        config_from_dict(dict(TINY_C, layer_types=kinds[:3]))
+    with pytest.raises(ConfigError, match="chunked_attention"):
+        config_from_dict(dict(TINY_C, layer_types=kinds[:3] + ["chunked_attention"]))
+    with pytest.raises(ConfigError, match="sliding_window"):
+        config_from_dict(dict(TINY_A, layer_types=["full_attention", "sliding_attention"]))
+
+
 def test_to_dict_round_trip():
     for raw in (TINY_A, TINY_B, TINY_C):
         cfg = config_from_dict(raw)

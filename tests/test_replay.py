@@ -148,6 +148,20 @@ def test_long_portions_head_size_128(folders, dtype):
     assert ops.prefill_tcgen05_error() == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_types_choose_the_sliding_layers(tmp_path, dtype):
+    """config.json may list which layers slide: here the lower two of four, the opposite of what
+    max_window_layers alone would give."""
+    raw = dict(TINY["C"][0], layer_types=["sliding_attention", "sliding_attention", "full_attention", "full_attention"])
+    folder = helpers.make_folder(tmp_path, raw, 12)
+    rng = random.Random(61)
+    toks = helpers.random_tokens(rng, 60, raw["vocab_size"])
+    ref = _reference(folder, dtype, {"a": toks})
+    got = _replay(folder, dtype, helpers.trace_portions(toks, [17, 2, 9, 21]), _round64(len(toks)), 4)
+    assert len(got) == len(toks)
+    _compare(got, ref, dtype)
+
+
 def test_trace_run_program(folders, tmp_path):
     """The program itself: stdin records, done lines, .f32 files."""
     raw, seed, page = TINY["A"]
