@@ -65,6 +65,15 @@ class Qwen3Config:
         eos = raw.get("eos_token_id", -1)
         if isinstance(eos, (list, tuple)):      # scripts/migrate.py:28-34 resolves a list to its first id
             eos = eos[0] if eos else -1
+        # Newer config.json files carry the rotary settings as one dictionary, ``rope_parameters``
+        # ({"rope_theta": ..., "rope_type": "default"}), in place of ``rope_theta`` / ``rope_scaling``.
+        params = raw.get("rope_parameters")
+        if isinstance(params, dict):
+            kind = params.get("rope_type", params.get("type", "default"))
+            if kind not in (None, "default"):
+                raise ConfigError(f"config.json: rope_parameters of type '{kind}' (rope_scaling) is not implemented by this engine")
+            if "rope_theta" not in raw and "rope_theta" in params:
+                raw = dict(raw, rope_theta=params["rope_theta"])
         cfg = cls(
             vocab_size=_require(raw, "vocab_size", int),
             hidden_size=hidden,

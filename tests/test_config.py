@@ -91,6 +91,16 @@ def test_layer_types_decide_where_they_are_listed():
         config_from_dict(dict(TINY_A, layer_types=["full_attention", "sliding_attention"]))
 
 
+def test_rotary_settings_as_one_dictionary():
+    raw = {k: v for k, v in TINY_B.items() if k != "rope_theta"}
+    cfg = config_from_dict(dict(raw, rope_parameters={"rope_theta": 250000.0, "rope_type": "default"}))
+    assert cfg.rope_theta == 250000.0 and cfg.model_spec().blocks[0].mixer.position.theta == 250000.0
+    with pytest.raises(ConfigError, match="rope_scaling"):
+        config_from_dict(dict(raw, rope_parameters={"rope_theta": 1e6, "rope_type": "yarn", "factor": 4.0}))
+    with pytest.raises(ConfigError, match="rope_theta"):
+        config_from_dict(dict(raw, rope_parameters={"rope_type": "default"}))
+
+
 def test_to_dict_round_trip():
     for raw in (TINY_A, TINY_B, TINY_C):
         cfg = config_from_dict(raw)
