@@ -182,7 +182,10 @@ int Scheduler::schedule(bool allow_preempt, std::vector<PlanEntry>* out_ptr) {
 }
 
 void Scheduler::on_step(const std::vector<PlanEntry>& plan) {
-    for (const PlanEntry& e : plan) seqs_.at(e.rid).n_cached += e.count;
+    for (const PlanEntry& e : plan) {
+        auto it = seqs_.find(e.rid);
+        if (it != seqs_.end()) it->second.n_cached += e.count;      // a request that was finished meanwhile is gone
+    }
 }
 
 // A token was sampled for the request on the device and is not read yet.
