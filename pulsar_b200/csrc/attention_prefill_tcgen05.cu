@@ -13,8 +13,9 @@
 //               MN-major operand straight from the page layout (keys along K);
 //   warps 5-7   TMA producers: an item's query tile, then per tile of 128 keys the pages that the
 //               block table names, each as two boxes of [page x 64] into 128-byte-swizzled
-//               tiles, two stages each for K and V.  A warp issues the copies of its lanes one
-//               after the other, so a tile's boxes are dealt out over the three warps.
+//               tiles, two stages each for K and V.  Two warps bring K, one brings V (a K tile is
+//               never queued behind the wait for a V buffer); a warp issues the copies of its
+//               lanes one after the other, so K's boxes are dealt out over lanes of both warps.
 // The roles run ahead of one another across items: the producers load the next item's Q, K and V
 // while the current one is computed (two Q buffers), and O has two buffers, so that the next item's
 // products start while the softmax warps still write the last item's output.
@@ -48,7 +49,7 @@ constexpr int kD = 128;              // head size
 constexpr int kBM = 128;             // query rows per block (MMA M, tensor-memory lanes)
 constexpr int kBN = 128;             // keys per tile
 constexpr int kThreads = 256;             // 4 softmax warps, the MMA warp, 3 producer warps
-constexpr int kProducers = 3;
+constexpr int kKProducers = 2;           // warps that bring K; one more brings V
 constexpr int kHalfBytes = 128 * 64 * 2;       // one [128 x 64] swizzled half tile: 16 KB
 constexpr int kTileBytes = 2 * kHalfBytes;     // 32 KB
 constexpr int kStages = 2;                     // K and V tiles in flight
@@ -202,8 +203,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i) {
             const bool from_softmax = (i >= kBarPFull && i < kBarPFull + 2) || (i >= kBarOEmpty && i < kBarOEmpty + 2);
-            const bool from_producers = (i >= kBarKFull && i < kBarKEmpty) || (i >= kBarVFull && i < kBarVEmpty);
-            mbar_init(bar(i), from_softmax ? 4 : from_producers ? kProducers : 1);
+            const bool from_k_producers = i >= kBarKFull && i < kBarKEmpty;
+            mbar_init(bar(i), from_softmax ? 4 : from_k_producers ? kKProducers : 1);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -220,20 +221,25 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kBN;      // S[0] | S[1] | O[0] | O[1]
 
     if (warp >= 5) {
-        // ---------------- TMA producers: a tile's boxes are dealt out over the lanes of three warps (a warp issues
-        // the copies of its lanes one after the other, so few lanes per warp keep a tile's issue time short)
-        const int pw = warp - 5;
+        // ---------------- TMA producers.  Warps 5 and 6 bring K (and warp 5 the query tiles), warp 7 brings V, so
+        // that a K tile, which the next S product waits for, is never queued behind the wait for a V buffer.  A warp
+        // issues the copies of its lanes one after the other, so a tile's boxes are dealt out over lanes of two warps.
+        const bool for_v = warp == 7;
+        const int pw = warp - 5;                               // K: 0 or 1
         const int loads = kBN / a.rows_per_load;               // pages (or parts of a page) per tile
         const uint32_t load_bytes = (uint32_t)a.rows_per_load * 128u;
-        const int box = pw + kProducers * lane;                // box -> (page slot, half)
+        const int box = for_v ? lane : pw + kKProducers * lane;      // box -> (page slot, half)
         const int slot = box >> 1, half = box & 1;
+        unsigned char* tiles = for_v ? v_s : k_s;
+        const CUtensorMap* map = for_v ? &map_v : &map_k;
+        const int bar_full = for_v ? kBarVFull : kBarKFull, bar_empty = for_v ? kBarVEmpty : kBarKEmpty;
         bool ok = true;
         uint32_t g = 0;                                        // key tiles so far, over all items
         Work w;
         w.t = 0;
         while (ok && next_item(w, a)) {
             const int t = w.t - 1, qb = t & 1;
-            if (pw == 0) {
+            if (warp == 5) {
                 if (lane == 0) {
                     ok = mbar_wait(bar(kBarQEmpty + qb), ((t >> 1) & 1) ^ 1, abort_flag);      // the item before last has used it
                     if (ok) {
@@ -258,22 +264,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 const uint32_t n_want = __popc(__ballot_sync(0xffffffffu, want));
                 const uint32_t dst_off = (uint32_t)st * kTileBytes + (uint32_t)half * kHalfBytes + (uint32_t)(slot * a.rows_per_load) * 128u;
-                // K: when the S product that read the stage last has retired
+                // the stage is free when the product that read it last has retired
                 if (lane == 0) {
-                    ok = mbar_wait(bar(kBarKEmpty + st), free_parity, abort_flag);
-                    if (ok) mbar_expect_tx(bar(kBarKFull + st), n_want * load_bytes);
+                    ok = mbar_wait(bar(bar_empty + st), free_parity, abort_flag);
+                    if (ok) mbar_expect_tx(bar(bar_full + st), n_want * load_bytes);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
-                if (want) tma_load_2d(smem_addr(k_s) + dst_off, &map_k, bar(kBarKFull + st), half * 64, row);
-                // V: when the P V product that read the stage last has retired
-                if (lane == 0) {
-                    ok = mbar_wait(bar(kBarVEmpty + st), free_parity, abort_flag);
-                    if (ok) mbar_expect_tx(bar(kBarVFull + st), n_want * load_bytes);
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-                if (want) tma_load_2d(smem_addr(v_s) + dst_off, &map_v, bar(kBarVFull + st), half * 64, row);
+                if (want) tma_load_2d(smem_addr(tiles) + dst_off, map, bar(bar_full + st), half * 64, row);
             }
         }
         if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_attn5_error, 2u); }
@@ -283,7 +281,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // S of tile g+1 overwrites the columns that held S and P of tile g-1: O += P V of tile g-1 was issued
         // before it, and the MMAs of one thread run in the order of their issue.
         if (lane == 0) {
-            const uint32_t q_addr = smem_addr(q_s), k_addr = smem_addr(k_s), v_addr = smem_addr(v_s);
+            const uint64_t q_desc = desc_k_major(smem_addr(q_s)), k_desc = desc_k_major(smem_addr(k_s));
+            const uint64_t v_desc = desc_mn_major(smem_addr(v_s));
             Work ws, wp;                                       // the items of the S cursor and of the P V cursor
             ws.t = wp.t = 0;
             int js = 0, jp = 0;                                // tile within the item
@@ -296,11 +295,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (js == 0 && !mbar_wait(bar(kBarQFull + qb), (t >> 1) & 1, abort_flag)) return false;
                 if (!mbar_wait(bar(kBarKFull + st), (gs / kStages) & 1, abort_flag)) return false;
                 fence_after();
+                // descriptors differ from tile to tile only in their address field (16-byte units): a 64-bit add each
+                const uint64_t qd = q_desc + (uint64_t)((uint32_t)qb * (kTileBytes >> 4));
+                const uint64_t kd = k_desc + (uint64_t)((uint32_t)st * (kTileBytes >> 4));
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint32_t off = (uint32_t)(ks >> 2) * kHalfBytes + (uint32_t)(ks & 3) * 32u;
-                    umma_ss(tmem_s + (uint32_t)sb * kBN, desc_k_major(q_addr + (uint32_t)qb * kTileBytes + off),
-                            desc_k_major(k_addr + (uint32_t)st * kTileBytes + off), kIdescS, ks > 0 ? 1u : 0u);
+                    constexpr uint32_t kHalf16 = kHalfBytes >> 4;
+                    const uint32_t off = (uint32_t)(ks >> 2) * kHalf16 + (uint32_t)(ks & 3) * 2u;      // 32 bytes per k-step
+                    umma_ss(tmem_s + (uint32_t)sb * kBN, qd + off, kd + off, kIdescS, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(kBarKEmpty + st));
                 umma_commit(bar(kBarSFull + sb));
@@ -323,11 +325,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!mbar_wait(bar(kBarVFull + st), (gp / kStages) & 1, abort_flag)) { ok = false; break; }
                 if (!mbar_wait(bar(kBarPFull + sb), (gp >> 1) & 1, abort_flag)) { ok = false; break; }
                 fence_after();
+                const uint64_t vd = v_desc + (uint64_t)((uint32_t)st * (kTileBytes >> 4));
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk)
-                    umma_ts(tmem_o + (uint32_t)ob * kD, tmem_s + (uint32_t)sb * kBN + (uint32_t)kk * 8u,
-                            desc_mn_major(v_addr + (uint32_t)st * kTileBytes + (uint32_t)kk * 2048u), kIdescPV,
-                            (jp > 0 || kk > 0) ? 1u : 0u);
+                    umma_ts(tmem_o + (uint32_t)ob * kD, tmem_s + (uint32_t)sb * kBN + (uint32_t)kk * 8u, vd + (uint64_t)(kk * (2048 >> 4)),
+                            kIdescPV, (jp > 0 || kk > 0) ? 1u : 0u);
                 umma_commit(bar(kBarVEmpty + st));
                 umma_commit(bar(kBarOFull));
                 ++jp;
