@@ -233,6 +233,47 @@ def test_stepping_one_pass_ahead_keeps_the_random_streams(folders):
     assert runs[0][1][4] == (eos, True)
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_arrivals_one_pass_ahead_and_one_pass_at_a_time(folders, seed):
+    """Requests of random lengths and budgets arrive while others run, a stop token ends some early, and the pool is
+    so small that requests are preempted and recomputed: the engine that steps one pass ahead emits what the one
+    that steps one pass at a time emits, token for token."""
+    raw, model_seed, page = TINY["A"]
+    rng = random.Random(100 + seed)
+    arrivals = []
+    for i in range(10):
+        arrivals.append((rng.randint(0, 25), helpers.random_tokens(rng, rng.randint(1, 45), raw["vocab_size"]), rng.randint(1, 24)))
+    arrivals.sort(key=lambda a: a[0])
+    eos = rng.randrange(raw["vocab_size"])
+
+    def drive(lookahead):
+        eng = _engine(folders["A"], "float32", page, num_pages=10, max_sessions=4, max_running=3, max_chunk_size=13, eos_id=eos)
+        seen, owner, todo, tick = {}, {}, list(arrivals), 0
+        while todo or owner:
+            while todo and todo[0][0] <= tick and len(owner) < 4:
+                _, prompt, budget = todo.pop(0)
+                sid = eng.create_session(prompt)
+                eng.feed(sid, [], budget)
+                owner[sid] = len(seen)
+                seen[owner[sid]] = []
+            events = (eng.step(1) if lookahead else eng.step_once()) if eng.has_work() else []
+            for sid, tok, fin in events:
+                seen[owner[sid]].append((tok, fin))
+                if fin:
+                    eng.release(sid)
+                    del owner[sid]
+            tick += 1
+            assert tick < 5000
+        eng.cache.check_consistency()
+        assert eng.cache.live_requests() == [] and all(f == 10 for f in eng.cache.n_free_pages())
+        return seen, eng.scheduler.n_preemptions
+
+    a, pre_a = drive(False)
+    b, pre_b = drive(True)
+    assert a == b
+    assert all(ev and ev[-1][1] for ev in a.values())
+
+
 def test_engine_refuses_a_cpu_device(folders):
     from pulsar_b200.engine.engine import Engine
     with pytest.raises(RuntimeError, match="no CPU path"):
