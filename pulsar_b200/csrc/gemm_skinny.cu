@@ -4,8 +4,8 @@
 //
 // The weights take the role of the MMA's 16-row operand and the tokens that of its 8-wide
 // one (mma.m16n8k16, float32 accumulators).  Nothing is staged in shared memory: a thread
-// loads 16 contiguous bytes of a weight row straight into the registers of the A fragment
-// and 16 bytes of a token's activations into the B fragment; because a dot product does
+// loads 32 contiguous bytes of a weight row (16 where K is no multiple of 64) straight into the
+// registers of A fragments and as many bytes of a token's activations into B fragments; because a dot product does
 // not care about the order of its terms, the k-index that a fragment slot stands for is
 // permuted the same way on both sides, which makes the vector loads legal.  A block owns
 // 16 weight rows; its 8 warps split K, keep 8 vector loads each in flight, and their
@@ -19,6 +19,8 @@
 // once for down, plus two elementwise kernels for the gating
 // (pulsar-core/src/model/qwen3.cpp:82-84, 114, 117-119).
 #include "mma_common.cuh"
+
+#include <cstdlib>
 
 namespace {
 
@@ -142,14 +144,150 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT*
     }
 }
 
+// The same product with 32-byte loads (ld.global.v8): a thread fetches 16 contiguous elements of a weight row,
+// so a warp's request covers whole 128-byte lines of eight rows, and feeds four MMAs from one load.  K must be a
+// multiple of 64.  kUnroll counts these double-width loads.
+struct Wide { uint4 lo, hi; };
+
+__device__ __forceinline__ Wide load_stream32(const void* p) {
+    Wide v;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
+    Wide v;
+    if (ok) {
+        v.lo = __ldg(reinterpret_cast<const uint4*>(p));
+        v.hi = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+    } else {
+        v.lo = v.hi = make_uint4(0, 0, 0, 0);
+    }
+    return v;
+}
+
+template <int NT, int MODE, typename OutT, int kUnroll>
+__global__ void __launch_bounds__(kWarps * 32)
+gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
+                        int inter) {
+    constexpr int kWideK = 64;                        // k per load: 4 threads x 16 contiguous elements
+    __shared__ float red[kWarps][kRows][8 * NT + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    int row_a, row_b;
+    if (MODE == kSwiGLU) { row_a = blockIdx.x * 8 + g; row_b = inter + blockIdx.x * 8 + g; }
+    else { row_a = blockIdx.x * kRows + g; row_b = row_a + 8; }
+    const bf16* wa_p = w + (size_t)row_a * K + 16 * t;
+    const bf16* wb_p = w + (size_t)row_b * K + 16 * t;
+    const bf16* x_p[NT];
+    bool x_ok[NT];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        x_ok[n] = n * 8 + g < M;
+        x_p[n] = x + (size_t)(x_ok[n] ? n * 8 + g : 0) * K + 16 * t;
+    }
+    float c[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) { c[n][0] = c[n][1] = c[n][2] = c[n][3] = 0.0f; }
+
+    const int blocks = K / kWideK;
+    const int kb_begin = (int)((long long)blocks * warp / kWarps), kb_end = (int)((long long)blocks * (warp + 1) / kWarps);
+    int kb = kb_begin;
+    Wide wa[kUnroll], wb[kUnroll];
+    const bool first = kb + kUnroll <= kb_end;
+    if (first) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            wa[u] = load_stream32(wa_p + (size_t)(kb + u) * kWideK);
+            wb[u] = load_stream32(wb_p + (size_t)(kb + u) * kWideK);
+        }
+    }
+    pdl_wait();
+    auto multiply = [&](const Wide& a, const Wide& b, size_t kb_at) {
+        const uint32_t a1[4] = {a.lo.x, b.lo.x, a.lo.y, b.lo.y};
+        const uint32_t a2[4] = {a.lo.z, b.lo.z, a.lo.w, b.lo.w};
+        const uint32_t a3[4] = {a.hi.x, b.hi.x, a.hi.y, b.hi.y};
+        const uint32_t a4[4] = {a.hi.z, b.hi.z, a.hi.w, b.hi.w};
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            const Wide xv = load_x32(x_p[n] + kb_at * kWideK, x_ok[n]);
+            mma_bf16(c[n], a1, xv.lo.x, xv.lo.y);
+            mma_bf16(c[n], a2, xv.lo.z, xv.lo.w);
+            mma_bf16(c[n], a3, xv.hi.x, xv.hi.y);
+            mma_bf16(c[n], a4, xv.hi.z, xv.hi.w);
+        }
+    };
+    for (bool loaded = first; kb + kUnroll <= kb_end; kb += kUnroll, loaded = false) {
+        if (!loaded) {
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                wa[u] = load_stream32(wa_p + (size_t)(kb + u) * kWideK);
+                wb[u] = load_stream32(wb_p + (size_t)(kb + u) * kWideK);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) multiply(wa[u], wb[u], (size_t)(kb + u));
+    }
+    for (; kb < kb_end; ++kb) {
+        const Wide a = load_stream32(wa_p + (size_t)kb * kWideK), b = load_stream32(wb_p + (size_t)kb * kWideK);
+        multiply(a, b, (size_t)kb);
+    }
+    pdl_trigger();
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        red[warp][g][n * 8 + 2 * t] = c[n][0];
+        red[warp][g][n * 8 + 2 * t + 1] = c[n][1];
+        red[warp][g + 8][n * 8 + 2 * t] = c[n][2];
+        red[warp][g + 8][n * 8 + 2 * t + 1] = c[n][3];
+    }
+    __syncthreads();
+    if (MODE == kSwiGLU) {
+        for (int i = tid; i < 8 * M; i += kWarps * 32) {
+            const int token = i / 8, r = i % 8;
+            float gate = 0.0f, up = 0.0f;
+#pragma unroll
+            for (int wi = 0; wi < kWarps; ++wi) { gate += red[wi][r][token]; up += red[wi][r + 8][token]; }
+            out[(size_t)token * inter + blockIdx.x * 8 + r] = from_float<OutT>(gate / (1.0f + expf(-gate)) * up);
+        }
+    } else {
+        for (int i = tid; i < kRows * M; i += kWarps * 32) {
+            const int token = i / kRows, r = i % kRows;
+            float acc = 0.0f;
+#pragma unroll
+            for (int wi = 0; wi < kWarps; ++wi) acc += red[wi][r][token];
+            out[(size_t)token * N + blockIdx.x * kRows + r] = from_float<OutT>(acc);
+        }
+    }
+}
+
 // kUnroll: k-blocks whose weight loads a thread keeps in flight.  8 costs 128 registers, so that two blocks
 // share an SM; 4 lets three share it.  A product whose blocks all fit two per SM takes 8; one with more blocks
 // takes 4, so that it does not need a second, nearly empty round of blocks (the QKV product of the 8B sizes:
 // 384 blocks on 148 SMs) and, with thousands of blocks (gate/up, lm_head), more of them are resident.
+bool wide_enabled() {       // PULSAR_SKINNY_WIDE=0 keeps the 16-byte loads
+    static const bool on = [] {
+        const char* v = getenv("PULSAR_SKINNY_WIDE");
+        return !(v && v[0] == '0' && v[1] == 0);
+    }();
+    return on;
+}
+
 template <int NT, int kUnroll>
 int launch_u(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)w;
+    if (K % 64 == 0 && (((uintptr_t)x | (uintptr_t)w) & 31) == 0 && wide_enabled()) {
+        constexpr int kU = kUnroll / 2;                 // the same bytes in flight
+        if (mode == kSwiGLU) {
+            const int inter = N / 2;
+            if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
+            return launch_pdl(gemm_skinny_wide_kernel<NT, kSwiGLU, bf16, kU>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
+        }
+        if (out_dtype == PB_BF16)
+            return launch_pdl(gemm_skinny_wide_kernel<NT, kPlain, bf16, kU>, N / kRows, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, 0);
+        return launch_pdl(gemm_skinny_wide_kernel<NT, kPlain, float, kU>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
+    }
     if (mode == kSwiGLU) {
         const int inter = N / 2;
         if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
