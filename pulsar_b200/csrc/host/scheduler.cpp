@@ -92,6 +92,36 @@ int Scheduler::pages_for(int64_t rid, int n_new) const {
 // unread and nothing may be recomputed from them) the answer is kNeedsPreemption where a request would
 // have to be preempted.
 int Scheduler::schedule(bool allow_preempt, std::vector<PlanEntry>* out_ptr) {
+    // When nothing at all can run although there is work, pages are held by requests that the three steps of
+    // plan_once cannot touch: requests that wait for a further turn on kept pages, or a prompt in progress beside
+    // them.  Then the holder furthest back in the queue gives its pages up (it is recomputed later); if no waiting
+    // request holds any, the running request admitted last is preempted; and the step is decided again.
+    for (;;) {
+        const int rc = plan_once(allow_preempt, out_ptr);
+        if (rc < 0 || !out_ptr->empty() || !allow_preempt || !has_work()) return rc;
+        int64_t victim = -1;
+        for (auto it = waiting_.rbegin(); it != waiting_.rend(); ++it)
+            if (cache_->has(*it)) { victim = *it; break; }
+        if (victim >= 0) {
+            if (waiting_.size() == 1 && running_.empty()) return rc;        // it waits alone: its own pages do not block it
+            Sequence& v = seqs_.at(victim);
+            cache_->close(victim);
+            v.n_cached = 0;
+            ++v.preemptions;
+            ++n_preemptions_;
+            continue;
+        }
+        if (running_.size() + waiting_.size() < 2) return rc;             // one request alone that cannot run: the engine reports it
+        if (running_.empty()) return rc;
+        int64_t youngest = running_.front();
+        for (int64_t r : running_)
+            if (seqs_.at(r).admitted_at > seqs_.at(youngest).admitted_at) youngest = r;
+        if (!cache_->has(youngest)) return rc;
+        preempt(youngest);
+    }
+}
+
+int Scheduler::plan_once(bool allow_preempt, std::vector<PlanEntry>* out_ptr) {
     std::vector<PlanEntry>& out = *out_ptr;
     out.clear();
     int budget = max_chunk_size_;

@@ -13,6 +13,9 @@
 //   * when a decoding request cannot get its next page the request admitted last is preempted: its
 //     pages go back, it returns to the head of the queue and is recomputed from its tokens later
 //     (the reference throws "out of pages": pulsar-core/src/runtime/kv/active_buffer.cpp:153-160);
+//   * when nothing at all can run because pages are held by requests that wait for a further turn on kept
+//     pages (or by a prompt in progress beside them), the holder furthest back in the queue gives its pages up
+//     and is recomputed; if no waiting request holds any, the running request admitted last is preempted;
 //   * a request that could never fit the pool alone is refused when it is submitted.
 // A step may be decided while the tokens of the step before are still on the device: such a token
 // stands in the request's token list as kUnread until on_token fills it in.
@@ -83,6 +86,7 @@ private:
     int held_back() const;
     int pages_for(int64_t rid, int n_new) const;
     void preempt(int64_t rid);
+    int plan_once(bool allow_preempt, std::vector<PlanEntry>* out);
     bool is_running(int64_t rid) const;
 
     Cache* cache_;

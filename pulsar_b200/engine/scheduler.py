@@ -16,6 +16,9 @@ Decisions that differ from the reference:
     preempted: its pages go back, it returns to the head of the queue and is recomputed
     from its tokens later.  The reference throws "out of pages" here
     (pulsar-core/src/runtime/kv/active_buffer.cpp:153-160);
+  * when nothing at all can run because pages are held by requests that wait for a further turn on
+    kept pages, the holder furthest back in the queue gives its pages up and is recomputed (if no
+    waiting request holds any, the running request admitted last is preempted);
   * a request that could never fit the pool alone is refused when it is submitted.
 
 A step may be decided while the tokens of the step before are still on the device: a

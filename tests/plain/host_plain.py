@@ -406,6 +406,31 @@ class Scheduler:
         self.waiting.appendleft(rid)
 
     def schedule(self, allow_preempt: bool = True) -> Optional[List[Scheduled]]:
+        """When nothing at all can run although there is work, the holder of pages furthest back in the queue
+        gives them up; if no waiting request holds any, the running request admitted last is preempted; then
+        the step is decided again."""
+        while True:
+            out = self._plan_once(allow_preempt)
+            if out is None or out or not allow_preempt or not self.has_work():
+                return out
+            holders = [r for r in reversed(self.waiting) if self.cache.has(r)]
+            if holders:
+                if len(self.waiting) == 1 and not self.running:
+                    return out
+                victim = holders[0]
+                self.cache.close(victim)
+                self.seqs[victim].n_cached = 0
+                self.seqs[victim].preemptions += 1
+                self.n_preemptions += 1
+                continue
+            if len(self.running) + len(self.waiting) < 2 or not self.running:
+                return out
+            youngest = max(self.running, key=lambda r: self.seqs[r].admitted_at)
+            if not self.cache.has(youngest):
+                return out
+            self._preempt(youngest)
+
+    def _plan_once(self, allow_preempt: bool = True) -> Optional[List[Scheduled]]:
         """Decide the next step.  Changes nothing in the cache except by preemption; the
         step function takes the pages when it runs the entries.  With ``allow_preempt``
         false (a step is still in flight, so some tokens are UNREAD and nothing may be

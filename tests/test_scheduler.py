@@ -251,3 +251,27 @@ def test_no_preemption_while_tokens_are_unread():
         s.on_token(rid, 1, -1)
     plan = s.schedule()                                   # everything read: now the youngest is preempted
     assert [e.rid for e in plan] == ["a"] and s.n_preemptions == 1
+
+
+def test_waiting_requests_that_hold_pages_give_them_up_when_nothing_can_run():
+    """Two requests finished a turn and kept their pages; both come back for a further turn that no longer fits
+    beside the other's pages.  Nothing runs, so nothing above could preempt: the one further back in the queue
+    gives its pages up and is recomputed after the first."""
+    cache, s = make(pages=6, page=4, max_running=2, budget=64)      # 24 tokens of cache
+    for rid in ("a", "b"):
+        s.add_request(rid, list(range(9)), 1)                       # 9 + 1 tokens: 3 pages each
+    plan = s.schedule()                                             # both prompts in one step
+    take(cache, plan)
+    s.on_step(plan)
+    for rid in ("a", "b"):
+        assert s.on_token(rid, 1, -1) is True                       # the one token of the turn
+        s.park(rid)                                                 # pages are kept for a further turn
+    assert not s.running and cache.n_free_pages() == [0]
+    s.extend_request("a", [5] * 6, 2)                               # 10 + 6 + 2 tokens: needs 5 pages, holds 3, none free
+    s.extend_request("b", [6] * 6, 2)
+    plan = s.schedule()
+    assert [e.rid for e in plan] == ["a"] and s.n_preemptions == 1 and not cache.has("b")
+    assert s.seqs["b"].n_cached == 0 and s.waiting == ["b"]
+    take(cache, plan)
+    s.on_step(plan)
+    cache.check_consistency()
