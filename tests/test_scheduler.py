@@ -275,3 +275,42 @@ def test_waiting_requests_that_hold_pages_give_them_up_when_nothing_can_run():
     take(cache, plan)
     s.on_step(plan)
     cache.check_consistency()
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_arrivals_and_further_turns_never_stall(seed):
+    """Requests of random lengths keep arriving on a small pool with a windowed group; finished ones are released or
+    come back for a further turn on their kept pages.  Whenever there is work a step can be decided (somebody gives
+    pages up if need be), every request ends, and the accounting stays consistent."""
+    import random
+    from pulsar_b200.cache import CacheManager, CacheNeed
+    rng = random.Random(seed)
+    cache = CacheManager([CacheNeed.paged_kv(2, 16), CacheNeed.paged_kv(2, 16, 150)], 8, 160, 12)
+    s = Scheduler(cache, 8, 96)
+    live, next_id, done = {}, 0, 0
+    for _ in range(6000):
+        while len(live) < 12 and rng.random() < 0.5:
+            s.add_request(next_id, [1] * rng.randint(1, 300), rng.randint(1, 80))
+            live[next_id] = 0
+            next_id += 1
+        if not s.has_work():
+            continue
+        plan = s.schedule()
+        assert plan, (s.waiting, s.running, cache.n_free_pages())
+        take(cache, plan)
+        s.on_step(plan)
+        for e in plan:
+            if e.sample and s.on_token(e.rid, rng.choice([9, 1, 2, 3, 4, 5, 6, 7]), 9):
+                s.park(e.rid)
+                if rng.random() < 0.3 and live[e.rid] < 2:
+                    live[e.rid] += 1
+                    s.extend_request(e.rid, [2] * rng.randint(1, 20), rng.randint(1, 30))
+                else:
+                    s.finish(e.rid)
+                    del live[e.rid]
+                    done += 1
+        cache.check_consistency()
+    assert done > 100
+    for rid in list(live):
+        s.finish(rid)
+    assert cache.n_free_pages() == [160, 160] and cache.live_requests() == []
