@@ -190,17 +190,17 @@ __global__ void decode_combine_kernel(const float* __restrict__ partial, T* __re
     const int stride = D + 2;
     const float* base = partial + row * n_splits * stride;
     if (threadIdx.x < 32) {
-        float m_all = -INFINITY;
-        for (int i = threadIdx.x; i < n_splits; i += 32) m_all = fmaxf(m_all, base[i * stride + D]);
-        m_all = warp_max(m_all);
-        float l_part = 0.0f;
-        for (int i = threadIdx.x; i < n_splits; i += 32) {
-            const float m = base[i * stride + D];
-            const float w = (m > -INFINITY) ? expf(m - m_all) : 0.0f;
-            w_s[i] = w;
-            l_part += base[i * stride + D + 1] * w;
-        }
+        // a lane's splits (i and i + 32): maximum and sum fetched together, so that the loads are in flight at once
+        const int i0 = threadIdx.x, i1 = threadIdx.x + 32;
+        const bool ok0 = i0 < n_splits, ok1 = i1 < n_splits;
+        const float m0 = ok0 ? base[i0 * stride + D] : -INFINITY, l0 = ok0 ? base[i0 * stride + D + 1] : 0.0f;
+        const float m1 = ok1 ? base[i1 * stride + D] : -INFINITY, l1 = ok1 ? base[i1 * stride + D + 1] : 0.0f;
+        const float m_all = warp_max(fmaxf(m0, m1));
+        const float w0 = (m0 > -INFINITY) ? expf(m0 - m_all) : 0.0f, w1 = (m1 > -INFINITY) ? expf(m1 - m_all) : 0.0f;
+        w_s[i0] = w0;                                    // beyond n_splits: 0
+        w_s[i1] = w1;
         // lanes hold disjoint splits; add them in lane order for a fixed result
+        float l_part = l0 * w0 + l1 * w1;
         for (int o = 16; o > 0; o >>= 1) l_part += __shfl_xor_sync(0xffffffffu, l_part, o);
         if (threadIdx.x == 0) l_s = l_part;
     }
@@ -208,7 +208,13 @@ __global__ void decode_combine_kernel(const float* __restrict__ partial, T* __re
     const float inv = 1.0f / l_s;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float o = 0.0f;
-        for (int i = 0; i < n_splits; ++i) o = fmaf(base[i * stride + d], w_s[i], o);
+        for (int i = 0; i < n_splits; i += 8) {          // eight loads in flight, added in split order
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (i + j < n_splits) ? base[(i + j) * stride + d] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o = fmaf(v[j], w_s[i + j], o);
+        }
         out[row * D + d] = from_float<T>(o * inv);
     }
 }
