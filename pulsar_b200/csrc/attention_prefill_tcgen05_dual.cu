@@ -47,9 +47,46 @@ static_assert(kRegsLaunch * kThreads <= 65536 && kRegsSoftmax % 8 == 0 && kRegsO
 __device__ unsigned int g_dual_error = 0;      // 0 = fine; else 1 + the role that gave up
 
 // Barrier slots; those of K and V exist once per stage, the others once per head.
-enum { kBarQFull = 0, kBarQEmpty = 2, kBarSFull = 4, kBarPFull = 6, kBarOFull = 8, kBarODone = 10, kBarOEmpty = 12,
-       kBarKFull = 14, kBarKEmpty = kBarKFull + kStages, kBarVFull = kBarKEmpty + kStages, kBarVEmpty = kBarVFull + kStages,
+enum { kBarQFull = 0, kBarQEmpty = 2, kBarSFull = 4, kBarPFull = 6, kBarPRest = 8, kBarOFull = 10, kBarODone = 12, kBarOEmpty = 14,
+       kBarKFull = 16, kBarKEmpty = kBarKFull + kStages, kBarVFull = kBarKEmpty + kStages, kBarVEmpty = kBarVFull + kStages,
        kBarTurn = kBarVEmpty + kStages, kNumBars = kBarTurn + 2 };
+
+// Half a row of P (64 keys) from the row of S in registers: 2^(s * sl2 + neg_ms) as bfloat16 pairs into 32 columns, the
+// sums of the even and odd columns added to l0 and l1.
+template <int kHalf>
+__device__ __forceinline__ void store_p_half(const uint32_t (&v)[kBN], float sl2, float neg_ms, uint32_t tmem_sx, float& l0, float& l1) {
+#pragma unroll
+    for (int c = kHalf * (kBN / 2); c < (kHalf + 1) * (kBN / 2); c += 32) {
+        uint32_t p[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2(fmaf(__uint_as_float(v[c + i]), sl2, neg_ms));
+            const float p1 = ex2(fmaf(__uint_as_float(v[c + i + 1]), sl2, neg_ms));
+            l0 += p0;
+            l1 += p1;
+            p[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(tmem_sx + (c >> 1), p);
+    }
+}
+
+__device__ __forceinline__ float row_max(const uint32_t (&v)[kBN]) {
+    float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < kBN; i += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) tm[e] = fmaxf(tm[e], __uint_as_float(v[i + e]));
+    }
+    return fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+}
+
+// The warp's stores to tensor memory are complete; one lane tells the issuing warp.
+__device__ __forceinline__ void hand_over(uint32_t bar, int lane) {
+    tmem_wait_st();
+    fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+}
 
 struct Args {
     bf16* out;
@@ -121,7 +158,7 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int i = tid; i < kStages * kTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i) {
-            const bool from_softmax = (i >= kBarPFull && i < kBarPFull + 2) || (i >= kBarOEmpty && i < kBarOEmpty + 2);
+            const bool from_softmax = (i >= kBarPFull && i < kBarPRest + 2) || (i >= kBarOEmpty && i < kBarOEmpty + 2);
             const bool from_both_issuers = (i >= kBarKEmpty && i < kBarKEmpty + kStages) || (i >= kBarVEmpty && i < kBarVEmpty + kStages);
             mbar_init(bar(i), from_softmax ? 4 : from_both_issuers ? 2 : 1);
         }
@@ -278,10 +315,19 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 fence_after();
                 const uint64_t vd = v_desc + (uint64_t)((uint32_t)st * (kTileBytes >> 4));
                 const bool item_done = jp + 1 == wp.n_tiles;
+                // the first half of P's columns (64 keys) is there: their products run while the softmax warps finish the rest
                 if (elect_one()) {
 #pragma unroll
-                    for (int kk = 0; kk < kBN / 16; ++kk)
+                    for (int kk = 0; kk < kBN / 32; ++kk)
                         umma_ts(tmem_ox, tmem_sx + (uint32_t)kk * 8u, vd + (uint64_t)(kk * (2048 >> 4)), kIdescPV, (jp > 0 || kk > 0) ? 1u : 0u);
+                }
+                __syncwarp();
+                if (!mbar_wait(bar(kBarPRest + x), gp & 1, abort_flag)) { ok = false; break; }
+                fence_after();
+                if (elect_one()) {
+#pragma unroll
+                    for (int kk = kBN / 32; kk < kBN / 16; ++kk)
+                        umma_ts(tmem_ox, tmem_sx + (uint32_t)kk * 8u, vd + (uint64_t)(kk * (2048 >> 4)), kIdescPV, 1u);
                     umma_commit(bar(kBarOFull + x));
                     umma_commit(bar(kBarVEmpty + st));
                     if (item_done) umma_commit(bar(kBarODone + x));       // the item's O of this head is complete
@@ -338,13 +384,7 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         if (!(key <= pos && (window <= 0 || key > pos - window))) v[i] = __float_as_uint(-INFINITY);
                     }
                 }
-                float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int i = 0; i < kBN; i += 4) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) tm[e] = fmaxf(tm[e], __uint_as_float(v[i + e]));
-                }
-                const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3]));
+                const float tmax = row_max(v);
                 // move the maximum only when it grew by more than the lazy threshold
                 float corr = 1.0f;
                 if ((tmax - m_used) * sl2 > kLazyRescale) {      // also the first visible key: m_used = -inf
@@ -352,26 +392,9 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     m_used = tmax;
                     l_run *= corr;
                 }
-                const float neg_ms = (m_used == -INFINITY) ? 0.0f : -m_used * sl2;
-                // P over the first half of S's columns
-                float l0 = 0.0f, l1 = 0.0f;
-#pragma unroll
-                for (int c = 0; c < kBN; c += 32) {
-                    uint32_t p[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float p0 = ex2(fmaf(__uint_as_float(v[c + i]), sl2, neg_ms));
-                        const float p1 = ex2(fmaf(__uint_as_float(v[c + i + 1]), sl2, neg_ms));
-                        l0 += p0;
-                        l1 += p1;
-                        p[i >> 1] = pack_bf16x2(p0, p1);
-                    }
-                    tmem_st16(tmem_sx + (c >> 1), p);
-                }
-                l_run += l0 + l1;
                 if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                    // O is rescaled in place once O += P V of the tile before has retired (that of this tile waits
-                    // for this warp's P)
+                    // O is rescaled in place, before any product of this tile adds to it: O += P V of the tile before
+                    // has retired (this tile's S was issued after it)
                     ok = mbar_wait(bar(kBarOFull + x), (g - 1) & 1, abort_flag);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
@@ -385,10 +408,14 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         tmem_st32(tmem_ox + c, o);
                     }
                 }
-                tmem_wait_st();
-                fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(kBarPFull + x));
+                // P lies over the first half of S's columns and is handed over in two halves of 64 keys
+                const float neg_ms = (m_used == -INFINITY) ? 0.0f : -m_used * sl2;
+                float l0 = 0.0f, l1 = 0.0f;
+                store_p_half<0>(v, sl2, neg_ms, tmem_sx, l0, l1);
+                hand_over(bar(kBarPFull + x), lane);
+                store_p_half<1>(v, sl2, neg_ms, tmem_sx, l0, l1);
+                hand_over(bar(kBarPRest + x), lane);
+                l_run += l0 + l1;
             }
             if (!ok) break;
             // the item's output: O of its last tile has retired.  (A barrier of its own: a warp whose rows see nothing of
