@@ -195,28 +195,38 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer: rank 0 only, for both blocks
-        if (lane == 0 && rank == 0) {
+        // ---------------- MMA issuer: rank 0 only, for both blocks.  The whole warp walks the loop and waits on the
+        // barriers, one elected lane issues: with uniform control flow the descriptors live in uniform registers and
+        // the issuing stream is short (an MMA is accepted only when the one before it has started, so every cycle
+        // that the issuing lane needs beyond an MMA's own time is a cycle without products).
+        if (rank == 0) {
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);         // (a broadcast: uniform for the compiler)
+            const uint64_t desc0 = umma_desc(smem_addr(smem));
             uint32_t it = 0;
             int j = 0;
-            for (int tile = pair; tile < total_tiles; tile += n_pairs, ++j) {
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++j) {
                 const int acc = j & 1;
-                bool ok = mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, abort_flag);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + acc * kBN;
+                ok = mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, abort_flag);
+                const uint32_t tmem_d = tmem_u + acc * kBN;
                 for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                     const int s = it % kPairStages;
                     if (!mbar_wait(full0 + 8 * s, (it / kPairStages) & 1, abort_flag)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_addr(smem + s * kPairStageBytes), b_addr = a_addr + kABytes;
+                    // descriptors differ from stage to stage only in their address field (16-byte units)
+                    const uint64_t a_desc = desc0 + (uint64_t)((uint32_t)s * (kPairStageBytes >> 4));
+                    const uint64_t b_desc = a_desc + (uint64_t)(kABytes >> 4);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k)
-                        umma_bf16_pair(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
-                    umma_commit_pair(empty0 + 8 * s);
+                        for (int k = 0; k < kBK / 16; ++k)
+                            umma_bf16_pair(tmem_d, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), (kt > 0 || k > 0) ? 1u : 0u);
+                        umma_commit_pair(empty0 + 8 * s);
+                        if (kt == k_tiles - 1) umma_commit_pair(acc_full0 + 8 * acc);
+                    }
+                    __syncwarp();
                 }
-                if (!ok) { *abort_flag = 1; atomicMax(&g_tc5_error, 3u); break; }
-                umma_commit_pair(acc_full0 + 8 * acc);
             }
+            if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_tc5_error, 3u); }
         }
     } else {
         // ---------------- epilogue of this block's 128 tokens
