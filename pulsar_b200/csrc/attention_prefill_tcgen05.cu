@@ -208,8 +208,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // ---------------- MMA issuer.  Two cursors walk the block's key tiles: S is issued one tile ahead of
         // O += P V (also across items), so that the next S is complete when the softmax warps finish a tile.
         // S of tile g+1 overwrites the columns that held S and P of tile g-1: O += P V of tile g-1 was issued
-        // before it, and the MMAs of one thread run in the order of their issue.
-        if (lane == 0) {
+        // before it, and the MMAs of one thread run in the order of their issue.  The whole warp walks the loop
+        // and waits on the barriers, one elected lane issues: with uniform control flow the descriptors live in
+        // uniform registers, and the issuing stream is short enough to keep up with the tensor core (which takes
+        // an MMA only when the one before it has started) although a softmax warp shares the scheduler.
+        {
+            const uint32_t tmem_s = __shfl_sync(0xffffffffu, tmem_base, 0), tmem_o = tmem_s + 2 * kBN;
             const uint64_t q_desc = desc_k_major(smem_addr(q_s)), k_desc = desc_k_major(smem_addr(k_s));
             const uint64_t v_desc = desc_mn_major(smem_addr(v_s));
             Work ws, wp;                                       // the items of the S cursor and of the P V cursor
@@ -227,18 +231,22 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 // descriptors differ from tile to tile only in their address field (16-byte units): a 64-bit add each
                 const uint64_t qd = q_desc + (uint64_t)((uint32_t)qb * (kTileBytes >> 4));
                 const uint64_t kd = k_desc + (uint64_t)((uint32_t)st * (kTileBytes >> 4));
-#pragma unroll
-                for (int ks = 0; ks < kD / 16; ++ks) {
-                    constexpr uint32_t kHalf16 = kHalfBytes >> 4;
-                    const uint32_t off = (uint32_t)(ks >> 2) * kHalf16 + (uint32_t)(ks & 3) * 2u;      // 32 bytes per k-step
-                    umma_ss(tmem_s + (uint32_t)sb * kBN, qd + off, kd + off, kIdescS, ks > 0 ? 1u : 0u);
-                }
-                umma_commit(bar(kBarKEmpty + st));
-                umma_commit(bar(kBarSFull + sb));
                 ++js;
                 ++gs;
-                if (js == ws.n_tiles) {                        // the item's last S: its Q buffer is free once it has retired
-                    umma_commit(bar(kBarQEmpty + qb));
+                const bool last = js == ws.n_tiles;
+                if (elect_one()) {
+#pragma unroll
+                    for (int ks = 0; ks < kD / 16; ++ks) {
+                        constexpr uint32_t kHalf16 = kHalfBytes >> 4;
+                        const uint32_t off = (uint32_t)(ks >> 2) * kHalf16 + (uint32_t)(ks & 3) * 2u;      // 32 bytes per k-step
+                        umma_ss(tmem_s + (uint32_t)sb * kBN, qd + off, kd + off, kIdescS, ks > 0 ? 1u : 0u);
+                    }
+                    umma_commit(bar(kBarKEmpty + st));
+                    umma_commit(bar(kBarSFull + sb));
+                    if (last) umma_commit(bar(kBarQEmpty + qb));     // the item's last S: its Q buffer is free once it has retired
+                }
+                __syncwarp();
+                if (last) {
                     js = 0;
                     more_s = next_item(ws, a);
                 }
@@ -255,21 +263,25 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!mbar_wait(bar(kBarPFull + sb), (gp >> 1) & 1, abort_flag)) { ok = false; break; }
                 fence_after();
                 const uint64_t vd = v_desc + (uint64_t)((uint32_t)st * (kTileBytes >> 4));
+                const bool item_done = jp + 1 == wp.n_tiles;
+                if (elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk)
-                    umma_ts(tmem_o + (uint32_t)ob * kD, tmem_s + (uint32_t)sb * kBN + (uint32_t)kk * 8u, vd + (uint64_t)(kk * (2048 >> 4)),
-                            kIdescPV, (jp > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(bar(kBarVEmpty + st));
-                umma_commit(bar(kBarOFull));
+                    for (int kk = 0; kk < kBN / 16; ++kk)
+                        umma_ts(tmem_o + (uint32_t)ob * kD, tmem_s + (uint32_t)sb * kBN + (uint32_t)kk * 8u, vd + (uint64_t)(kk * (2048 >> 4)),
+                                kIdescPV, (jp > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(bar(kBarVEmpty + st));
+                    umma_commit(bar(kBarOFull));
+                    if (item_done) umma_commit(bar(kBarODone));      // the item's O is complete once everything issued so far has retired
+                }
+                __syncwarp();
                 ++jp;
                 ++gp;
-                if (jp == wp.n_tiles) {
-                    umma_commit(bar(kBarODone));               // the item's O is complete once everything issued so far has retired
+                if (item_done) {
                     jp = 0;
                     more_p = next_item(wp, a);
                 }
             }
-            if (!ok) { *abort_flag = 1; atomicMax(&g_attn5_error, 3u); }
+            if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_attn5_error, 3u); }
         }
     } else {
         // ---------------- softmax: thread `r` owns query row r

@@ -338,30 +338,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer
-        if (lane == 0) {
+        // ---------------- MMA issuer: the warp walks the loop uniformly, one elected lane issues
+        {
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
+            const uint64_t desc0 = umma_desc(smem_addr(smem));
             uint32_t it = 0;
             int j = 0;                                        // tiles done by this block
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++j) {
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
                 const int acc = j & 1;
-                bool ok = mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, abort_flag);   // the epilogue has drained it
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + acc * kBN;
+                ok = mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, abort_flag);   // the epilogue has drained it
+                const uint32_t tmem_d = tmem_u + acc * kBN;
                 for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
                     const int s = it % kStages;
                     if (!mbar_wait(full0 + 8 * s, (it / kStages) & 1, abort_flag)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_addr(smem + s * kStageBytes), b_addr = a_addr + kABytes;
+                    const uint64_t a_desc = desc0 + (uint64_t)((uint32_t)s * (kStageBytes >> 4));
+                    const uint64_t b_desc = a_desc + (uint64_t)(kABytes >> 4);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k) {
-                        // 16 bfloat16 = 32 bytes further along the 128-byte row
-                        umma_bf16(tmem_d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), (kt > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < kBK / 16; ++k)      // 16 bfloat16 = 32 bytes further along the 128-byte row
+                            umma_bf16(tmem_d, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), (kt > 0 || k > 0) ? 1u : 0u);
+                        umma_commit(empty0 + 8 * s);          // the stage is free once the tensor core has read it
+                        if (kt == k_tiles - 1) umma_commit(acc_full0 + 8 * acc);     // the accumulator is complete once its MMAs have retired
                     }
-                    umma_commit(empty0 + 8 * s);          // the stage is free once the tensor core has read it
+                    __syncwarp();
                 }
-                if (!ok) { *abort_flag = 1; atomicMax(&g_tc5_error, 3u); break; }
-                umma_commit(acc_full0 + 8 * acc);        // the accumulator is complete once its MMAs have retired
             }
+            if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_tc5_error, 3u); }
         }
     } else {
         // ---------------- epilogue: warp w reads the lanes of tensor memory it may touch (32 * (w % 4) ...)
