@@ -316,11 +316,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int c = 0; c < kBN; c += 32) tmem_landed(*reinterpret_cast<uint32_t(*)[32]>(&v[c]));
                 if (!all_visible) {
+                    // columns lo..hi of the tile are visible to this row; compared without branches
+                    const int hi = pos - key0;
+                    const int lo = window > 0 ? pos - window + 1 - key0 : -(1 << 30);
 #pragma unroll
-                    for (int i = 0; i < kBN; ++i) {
-                        const int key = key0 + i;
-                        if (!(key <= pos && (window <= 0 || key > pos - window))) v[i] = __float_as_uint(-INFINITY);
-                    }
+                    for (int i = 0; i < kBN; ++i) v[i] = ((i <= hi) & (i >= lo)) ? v[i] : __float_as_uint(-INFINITY);
                 }
                 float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll

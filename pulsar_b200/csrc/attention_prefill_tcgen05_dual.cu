@@ -35,7 +35,10 @@ constexpr int kSoftmaxWarps = 8;          // 4 per head
 constexpr int kMmaWarp = 8;               // warps 8 and 9 issue the MMAs of head A and of head B
 constexpr int kProducerWarp = 10;         // warp 10 brings Q and K, warp 11 brings V
 constexpr int kStages = 2;
-constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int kStageOutBytes = 4096;      // per softmax warp: 32 rows of 64 output columns
+constexpr int kSmemBytes = (2 + 2 * kStages) * kTileBytes + 1024 /* alignment slack */ + 256 /* barriers */ + 1280 /* sequence bounds */ +
+                           kSoftmaxWarps * kStageOutBytes;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory of one block");
 constexpr int kTmemColumns = 512;
 // Registers per thread: the block is launched with kRegsLaunch each (what 384 threads leave of the register file, in
 // steps of 8); the four other warps give up what the eight softmax warps take.  setmaxnreg.inc waits, without a limit,
@@ -88,12 +91,15 @@ __device__ __forceinline__ void hand_over(uint32_t bar, int lane) {
     if (lane == 0) mbar_arrive(bar);
 }
 
+constexpr int kSeqCache = 128;           // sequences whose bounds a block keeps in shared memory
+
 struct Args {
     bf16* out;
     const int* block_table;
     const int* cu_q;
     const int* kv_len;
     int table_stride, n_seqs, n_items, Hq, Hkv, page_shift, rows_per_load, window;
+    int pairs, n_q_tiles, group;      // Hq / 2, n_items / pairs, Hq / Hkv
     float scale;
 };
 
@@ -105,20 +111,25 @@ struct Work {
     const int* table;
 };
 
-__device__ __forceinline__ bool next_item(Work& w, const Args& a) {
+// Where the sequences' bounds are read from: the block's copy in shared memory, or global memory for a large batch.
+struct Seqs {
+    const int* cu_q;
+    const int* kv_len;
+};
+
+__device__ __forceinline__ bool next_item(Work& w, const Args& a, const Seqs& seqs) {
     const int k = w.t;
     const int G = gridDim.x, b = blockIdx.x;
     const int idx = k * G + ((k & 1) ? G - 1 - b : b);
     if (idx >= a.n_items) return false;
-    const int pairs = a.Hq >> 1;
-    const int n_q_tiles = a.n_items / pairs;
-    w.head = 2 * (idx % pairs);
-    w.kvh = w.head / (a.Hq / a.Hkv);
-    int tile = n_q_tiles - 1 - idx / pairs;
+    const unsigned q_tile = (unsigned)idx / (unsigned)a.pairs;          // (one division per item: the counts come with the arguments)
+    w.head = 2 * (idx - (int)q_tile * a.pairs);
+    w.kvh = (int)((unsigned)w.head / (unsigned)a.group);
+    int tile = a.n_q_tiles - 1 - (int)q_tile;
     int s = 0, q0 = 0, q_len = 0;
     for (; s < a.n_seqs; ++s) {
-        q0 = a.cu_q[s];
-        q_len = a.cu_q[s + 1] - q0;
+        q0 = seqs.cu_q[s];
+        q_len = seqs.cu_q[s + 1] - q0;
         const int nt = (q_len + kBM - 1) / kBM;
         if (tile < nt) break;
         tile -= nt;
@@ -127,7 +138,7 @@ __device__ __forceinline__ bool next_item(Work& w, const Args& a) {
     const int m0 = tile * kBM;
     w.rows = min(kBM, q_len - m0);
     w.q_row0 = q0 + m0;
-    const int ctx0 = a.kv_len[s] - q_len;
+    const int ctx0 = seqs.kv_len[s] - q_len;
     w.pos_first = ctx0 + m0;
     w.pos_last = ctx0 + m0 + w.rows - 1;
     w.lo = (a.window > 0 && w.pos_first - a.window + 1 > 0) ? w.pos_first - a.window + 1 : 0;
@@ -149,6 +160,10 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * kStages) * kTileBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* seq_s = reinterpret_cast<int*>(smem + (2 + 2 * kStages) * kTileBytes + 256);      // cu_q[0..n], then kv_len[0..n)
+    unsigned char* out_s = smem + (2 + 2 * kStages) * kTileBytes + 256 + 1280;               // kStageOutBytes per softmax warp
+    const bool cached = a.n_seqs <= kSeqCache;
+    const Seqs seqs = {cached ? seq_s : a.cu_q, cached ? seq_s + kSeqCache + 1 : a.kv_len};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t bar0 = smem_addr(bars);
@@ -156,6 +171,12 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     // V's buffers start finite: a page that is not loaded leaves its place as it was, and 0 * NaN would poison a row.
     for (int i = tid; i < kStages * kTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+    if (cached) {
+        // every role looks an item's sequence up in these bounds, once per item: from shared memory the walk over
+        // the sequences costs a tenth of what dependent loads from global memory do
+        for (int i = tid; i <= a.n_seqs; i += kThreads) seq_s[i] = a.cu_q[i];
+        for (int i = tid; i < a.n_seqs; i += kThreads) seq_s[kSeqCache + 1 + i] = a.kv_len[i];
+    }
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i) {
             const bool from_softmax = (i >= kBarPFull && i < kBarPRest + 2) || (i >= kBarOEmpty && i < kBarOEmpty + 2);
@@ -193,22 +214,8 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             uint32_t g = 0;                                        // key tiles so far, over all items
             Work w;
             w.t = 0;
-            while (ok && next_item(w, a)) {
+            while (ok && next_item(w, a, seqs)) {
                 const int t = w.t - 1;
-                if (pw == 0) {
-                    if (lane == 0) {
-                        for (int x = 0; x < 2 && ok; ++x) {
-                            ok = mbar_wait(bar(kBarQEmpty + x), (t & 1) ^ 1, abort_flag);      // the item before has used it
-                            if (ok) {
-                                const uint32_t dst = smem_addr(q_s) + (uint32_t)x * kTileBytes;
-                                mbar_expect_tx(bar(kBarQFull + x), kTileBytes);
-                                tma_load_2d(dst, &map_q, bar(kBarQFull + x), (w.head + x) * kD, w.q_row0);
-                                tma_load_2d(dst + kHalfBytes, &map_q, bar(kBarQFull + x), (w.head + x) * kD + 64, w.q_row0);
-                            }
-                        }
-                    }
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                }
                 for (int j = 0; j < w.n_tiles && ok; ++j, ++g) {
                     const int key0 = (w.kt0 + j) * kBN;
                     const int st = g % kStages;
@@ -229,6 +236,22 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
                     if (want) tma_load_2d(smem_addr(tiles) + dst_off, map, bar(bar_full + st), half * 64, row);
+                    if (j == 0 && pw == 0) {
+                        // the item's query tiles, behind its first K tile: that one's buffer is free earlier than
+                        // the query buffers, which the item before gives up with its last S products
+                        if (lane == 0) {
+                            for (int x = 0; x < 2 && ok; ++x) {
+                                ok = mbar_wait(bar(kBarQEmpty + x), (t & 1) ^ 1, abort_flag);
+                                if (ok) {
+                                    const uint32_t dst = smem_addr(q_s) + (uint32_t)x * kTileBytes;
+                                    mbar_expect_tx(bar(kBarQFull + x), kTileBytes);
+                                    tma_load_2d(dst, &map_q, bar(kBarQFull + x), (w.head + x) * kD, w.q_row0);
+                                    tma_load_2d(dst + kHalfBytes, &map_q, bar(kBarQFull + x), (w.head + x) * kD + 64, w.q_row0);
+                                }
+                            }
+                        }
+                        ok = __shfl_sync(0xffffffffu, ok, 0);
+                    }
                 }
             }
             if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_dual_error, 2u); }
@@ -252,7 +275,7 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             int js = 0, jp = 0;                                // tile within the item
             uint32_t gs = 0, gp = 0;                           // tile over all items
             uint32_t turn = 0;                                 // this thread's turns so far
-            bool more_s = next_item(ws, a), more_p = next_item(wp, a);
+            bool more_s = next_item(ws, a, seqs), more_p = next_item(wp, a, seqs);
             bool ok = true;
             // The two threads take turns (A, B, A, ...), a turn being O += P[j] V[j] and S[j+1] of the thread's head, so
             // that one head's products run while the other head's softmax warps work; left alone, both heads fall into
@@ -292,7 +315,7 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 __syncwarp();
                 if (last) {
                     js = 0;
-                    more_s = next_item(ws, a);
+                    more_s = next_item(ws, a, seqs);
                 }
             };
             if (more_s) {
@@ -339,7 +362,7 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 end_turn();
                 if (item_done) {
                     jp = 0;
-                    more_p = next_item(wp, a);
+                    more_p = next_item(wp, a, seqs);
                 }
             }
             if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_dual_error, 3u); }
@@ -358,7 +381,7 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         uint32_t g = 0;
         Work w;
         w.t = 0;
-        while (ok && next_item(w, a)) {
+        while (ok && next_item(w, a, seqs)) {
             const int t = w.t - 1;
             const int pos = w.pos_first + min(r, w.rows - 1);     // rows beyond the tile's end repeat the last one
             float m_used = -INFINITY, l_run = 0.0f;
@@ -378,11 +401,11 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int c = 0; c < kBN; c += 32) tmem_landed(*reinterpret_cast<uint32_t(*)[32]>(&v[c]));
                 if (!all_visible) {
+                    // columns lo..hi of the tile are visible to this row; compared without branches
+                    const int hi = pos - key0;
+                    const int lo = window > 0 ? pos - window + 1 - key0 : -(1 << 30);
 #pragma unroll
-                    for (int i = 0; i < kBN; ++i) {
-                        const int key = key0 + i;
-                        if (!(key <= pos && (window <= 0 || key > pos - window))) v[i] = __float_as_uint(-INFINITY);
-                    }
+                    for (int i = 0; i < kBN; ++i) v[i] = ((i <= hi) & (i >= lo)) ? v[i] : __float_as_uint(-INFINITY);
                 }
                 const float tmax = row_max(v);
                 // move the maximum only when it grew by more than the lazy threshold
@@ -425,25 +448,44 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!ok) break;
             fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            bf16* dst = a.out + ((size_t)(w.q_row0 + r) * a.Hq + w.head + x) * kD;
-#pragma unroll 1
-            for (int c = 0; c < kD; c += 32) {
-                uint32_t o[32];
-                tmem_ld32(tmem_ox + c, o);
-                if (r < w.rows) {
+            // the whole row of O into registers, so that the next item's products may overwrite the buffer while
+            // the row is still being normalised and written
+            uint32_t o[kD];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint32_t y[4];
+            for (int c = 0; c < kD; c += 32) tmem_ld32_nowait(tmem_ox + c, *reinterpret_cast<uint32_t(*)[32]>(&o[c]));
+            tmem_wait_ld();
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
-                            y[k] = pack_bf16x2(__uint_as_float(o[i * 8 + 2 * k]) * inv, __uint_as_float(o[i * 8 + 2 * k + 1]) * inv);
-                        reinterpret_cast<uint4*>(dst + c)[i] = make_uint4(y[0], y[1], y[2], y[3]);
-                    }
-                }
-            }
+            for (int c = 0; c < kD; c += 32) tmem_landed(*reinterpret_cast<uint32_t(*)[32]>(&o[c]));
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(kBarOEmpty + x));       // this warp's lanes of the O buffer may be overwritten
+            // The rows go out through shared memory, 64 columns at a time: a thread holds a whole row, and 32 threads
+            // storing 16 bytes each to 32 rows make 32 memory transactions per instruction, which hold up the SM's
+            // load/store pipe (and every barrier poll behind them) for thousands of cycles per item.  Transposed, a
+            // store instruction writes four rows of 128 contiguous bytes.  16-byte chunk c of row q lies at chunk
+            // c ^ (q & 7) of the row's 128 bytes, so that neither the writes nor the reads conflict.
+            uint4* mine = reinterpret_cast<uint4*>(out_s + warp * kStageOutBytes);
+            bf16* base = a.out + ((size_t)(w.q_row0 + wr * 32) * a.Hq + w.head + x) * kD;
+            const int rows_here = w.rows - wr * 32;               // rows of this warp inside the tile
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    uint32_t y[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        y[k] = pack_bf16x2(__uint_as_float(o[h * 64 + c * 8 + 2 * k]) * inv, __uint_as_float(o[h * 64 + c * 8 + 2 * k + 1]) * inv);
+                    mine[lane * 8 + (c ^ (lane & 7))] = make_uint4(y[0], y[1], y[2], y[3]);
+                }
+                __syncwarp();
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int q = k * 4 + (lane >> 3), c = lane & 7;
+                    const uint4 val = mine[q * 8 + (c ^ (q & 7))];
+                    if (q < rows_here) *reinterpret_cast<uint4*>(base + (size_t)q * a.Hq * kD + h * 64 + c * 8) = val;
+                }
+                __syncwarp();
+            }
         }
         if (!ok && lane == 0) {
             *abort_flag = 1;
@@ -516,6 +558,9 @@ int launch_dual(const void* q, const void* k_pool, const void* v_pool, void* out
     a.n_items = (int)items;
     a.Hq = Hq;
     a.Hkv = Hkv;
+    a.pairs = Hq / 2;
+    a.n_q_tiles = n_q_tiles;
+    a.group = Hq / Hkv;
     a.page_shift = log2_exact(page_size);
     a.rows_per_load = rows_per_load;
     a.window = window;
