@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the Qwen3-8B shape on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--shape 8b|14b|32b] [--layers L] [--batch B] [--context C] [--no-points] [--no-e2e]
 
 A step is one decode step.  The default run has the layer sizes of the Qwen3-8B
 configuration (36 layers, hidden 4096, 32/8 heads of 128, intermediate 12288, vocabulary
@@ -40,7 +41,14 @@ QWEN3_8B = dict(
     rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, use_sliding_window=False,
     sliding_window=None, max_window_layers=36, hidden_act="silu", attention_bias=False, initializer_range=0.02,
     eos_token_id=151645)
-FULL_LAYERS = 36
+# The other dense shapes of the family, for measurements at further sizes (--shape); the default run is the 8B shape.
+SHAPES = {
+    "8b": dict(QWEN3_8B),
+    "14b": dict(QWEN3_8B, hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40,
+                max_window_layers=40),
+    "32b": dict(QWEN3_8B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64,
+                max_window_layers=64),
+}
 PAGE = 16
 
 
@@ -85,13 +93,13 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def build_engine(n_layers: int, batch: int, context: int, max_chunk: int):
+def build_engine(shape: dict, n_layers: int, batch: int, context: int, max_chunk: int):
     import torch
     from pulsar_b200.config import config_from_dict
     from pulsar_b200.engine.engine import Engine
     from pulsar_b200.models import build_model
     from pulsar_b200.weights import load_random
-    raw = dict(QWEN3_8B, num_hidden_layers=n_layers, max_window_layers=n_layers)
+    raw = dict(shape, num_hidden_layers=n_layers, max_window_layers=n_layers)
     cfg = config_from_dict(raw)
     model = build_model(cfg, torch.bfloat16)
     load_random(model, 0, 0.02, "cuda:0")
@@ -228,7 +236,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration's 36 (named in config)")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: Qwen3-8B (default), 14B or 32B")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true")
@@ -246,8 +255,13 @@ def main() -> int:
     from pulsar_b200 import ops
     pk = peaks()
     big = 64 if not args.no_points else args.batch
-    engine = build_engine(args.layers, max(big, args.batch), args.context, 2048)
-    raw = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    shape = SHAPES[args.shape]
+    full_layers = shape["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = full_layers
+    engine = build_engine(shape, args.layers, max(big, args.batch), args.context, 2048)
+    raw = dict(shape, num_hidden_layers=args.layers)
+    name = f"Qwen3-{args.shape.upper()} shape"
 
     sampler = ClockSampler()
     seconds, launches, clocks = time_decode(engine, args.batch, args.context, args.steps, warmup, sampler)
@@ -273,15 +287,17 @@ def main() -> int:
                "d2h_bytes_per_step": d2h}
 
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, context 4096); prefill and batch 1/64 alongside",
+        "metric": f"decode tok/s at batch {args.batch} ({name}, context {args.context}); prefill and batch 1/64 alongside",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids, random cache contents for decode",
         "impl": "ours",
-        "config": {"model": "Qwen3-8B shape", "global_batch": args.batch, "seq_len": args.context, "parallelism": "single GPU",
-                   "layers": args.layers, "layers_of_configuration": FULL_LAYERS, "hidden": 4096, "q_heads": 32,
-                   "kv_heads": 8, "head_dim": 128, "intermediate": 12288, "vocab": 151936, "page_size": PAGE,
-                   "prompt_tokens": 2048, "l2": "inputs larger than L2 (weights 15 GB)", "peaks": pk["source"]},
+        "config": {"model": name, "global_batch": args.batch, "seq_len": args.context, "parallelism": "single GPU",
+                   "layers": args.layers, "layers_of_configuration": full_layers, "hidden": shape["hidden_size"],
+                   "q_heads": shape["num_attention_heads"], "kv_heads": shape["num_key_value_heads"],
+                   "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"], "vocab": shape["vocab_size"],
+                   "page_size": PAGE, "prompt_tokens": 2048,
+                   "l2": f"inputs larger than L2 (weights {engine.model.weight_bytes(1) / 1e9:.0f} GB)", "peaks": pk["source"]},
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",

@@ -339,7 +339,8 @@ def test_attention_decode_split(dtype, hq, hkv, d, page, window, n_splits):
     close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window), TOL[dtype])
 
 
-TC_SHAPES = [(32, 8, 128, 16), (5, 5, 64, 16), (16, 1, 128, 32), (8, 2, 64, 8), (12, 4, 128, 64), (7, 7, 128, 4)]
+TC_SHAPES = [(32, 8, 128, 16), (5, 5, 64, 16), (16, 1, 128, 32), (8, 2, 64, 8), (12, 4, 128, 64), (7, 7, 128, 4),
+             (10, 2, 128, 16)]
 
 
 @pytest.mark.parametrize("hq,hkv,d,page", TC_SHAPES)
@@ -390,7 +391,8 @@ def test_attention_prefill_tensor_cores(hq, hkv, d, page, window):
     close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window), TOL[dtype])
 
 
-TCGEN05_ATTN_SHAPES = [(32, 8, 128, 16), (16, 1, 128, 32), (12, 4, 128, 64), (7, 7, 128, 8), (6, 3, 128, 128), (4, 2, 128, 256)]
+TCGEN05_ATTN_SHAPES = [(32, 8, 128, 16), (16, 1, 128, 32), (12, 4, 128, 64), (7, 7, 128, 8), (6, 3, 128, 128), (4, 2, 128, 256),
+                       (10, 2, 128, 16)]
 
 
 @pytest.mark.parametrize("hq,hkv,d,page", TCGEN05_ATTN_SHAPES)
