@@ -447,6 +447,40 @@ def test_attention_prefill_tcgen05_growing_scores():
     close(out, _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, None), TOL[dtype])
 
 
+@pytest.mark.parametrize("window", [None, 5000])
+def test_attention_long_contexts(window):
+    """Tens of thousands of cached tokens: a decoded token at 33,000 and portions that end at 20,000 and 9,000, with
+    one key near the start that stands out (thousands of pages, block tables two thousand entries wide, every
+    split of the decode kernels at work); all three bfloat16 kernels and the CUDA-core decode kernel."""
+    from pulsar_b200 import ops
+    dtype, hq, hkv, d, page = torch.bfloat16, 4, 2, 128, 16
+    scale = 1.0 / math.sqrt(d)
+    g = torch.Generator().manual_seed(21)
+    lens_kv = [33000, 16385, 40]
+    lens_q = [1, 1, 1]
+    case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype, spike=(0, 29000 if window else 7, hq - 1))
+    ref = _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window)
+    for tc in (True, False):
+        for n_splits in (32, 7):
+            out = torch.full((3, hq, d), float("nan"), dtype=dtype, device="cuda")
+            partial = torch.full((3 * hq * n_splits * (d + 2),), float("nan"), dtype=torch.float32, device="cuda")
+            ops.paged_attention_decode(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, partial, dev(case["table"]),
+                                       dev(case["kv"]), scale, window, n_splits, tensor_cores=tc)
+            close(out, ref, TOL[dtype], f"decode, tensor cores {tc}, {n_splits} splits")
+    lens_q, lens_kv = [200, 130], [20000, 9000]
+    case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype, spike=(0, 16000 if window else 11, 1))
+    ref = _attention_ref(case, lens_q, lens_kv, hq, hkv, scale, window)
+    out = torch.full((sum(lens_q), hq, d), float("nan"), dtype=dtype, device="cuda")
+    ops.paged_attention_prefill_tcgen05(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, dev(case["table"]),
+                                        dev(case["cu"]), dev(case["kv"]), ops.prefill_tcgen05_tiles(lens_q), scale, window)
+    assert ops.prefill_tcgen05_error() == 0
+    close(out, ref, TOL[dtype], "tcgen05 portions")
+    out = torch.full((sum(lens_q), hq, d), float("nan"), dtype=dtype, device="cuda")
+    ops.paged_attention_prefill_tc(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, dev(case["table"]),
+                                   dev(case["cu"]), dev(case["kv"]), ops.prefill_tc_tiles(lens_q), scale, window)
+    close(out, ref, TOL[dtype], "mma.sync portions")
+
+
 @pytest.mark.parametrize("d,page", [(128, 16), (64, 8)])
 def test_attention_dispatch_splits_a_mixed_step(d, page):
     """ops.attention on a step whose first sequences bring one token each (the scheduler's order): those take the
