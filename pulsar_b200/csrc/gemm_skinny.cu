@@ -149,11 +149,19 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT*
 // multiple of 64.  kUnroll counts these double-width loads.
 struct Wide { uint4 lo, hi; };
 
+// kEvictFirst: the line is marked as the first to leave L2 (and L2 fetches 256 bytes at a time): weights are read
+// once per step and are far larger than L2, so they should not push out what the step reads again.
+template <bool kEvictFirst>
 __device__ __forceinline__ Wide load_stream32(const void* p) {
     Wide v;
-    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
-                 : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
-                 : "l"(p));
+    if (kEvictFirst)
+        asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.L2::256B.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                     : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
+                     : "l"(p));
+    else
+        asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                     : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
+                     : "l"(p));
     return v;
 }
 __device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
@@ -167,7 +175,7 @@ __device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
     return v;
 }
 
-template <int NT, int MODE, typename OutT, int kUnroll>
+template <int NT, int MODE, typename OutT, int kUnroll, bool kEvictFirst>
 __global__ void __launch_bounds__(kWarps * 32)
 gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
                         int inter) {
@@ -199,8 +207,8 @@ gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, 
     if (first) {
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            wa[u] = load_stream32(wa_p + (size_t)(kb + u) * kWideK);
-            wb[u] = load_stream32(wb_p + (size_t)(kb + u) * kWideK);
+            wa[u] = load_stream32<kEvictFirst>(wa_p + (size_t)(kb + u) * kWideK);
+            wb[u] = load_stream32<kEvictFirst>(wb_p + (size_t)(kb + u) * kWideK);
         }
     }
     pdl_wait();
@@ -222,15 +230,15 @@ gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, 
         if (!loaded) {
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
-                wa[u] = load_stream32(wa_p + (size_t)(kb + u) * kWideK);
-                wb[u] = load_stream32(wb_p + (size_t)(kb + u) * kWideK);
+                wa[u] = load_stream32<kEvictFirst>(wa_p + (size_t)(kb + u) * kWideK);
+                wb[u] = load_stream32<kEvictFirst>(wb_p + (size_t)(kb + u) * kWideK);
             }
         }
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) multiply(wa[u], wb[u], (size_t)(kb + u));
     }
     for (; kb < kb_end; ++kb) {
-        const Wide a = load_stream32(wa_p + (size_t)kb * kWideK), b = load_stream32(wb_p + (size_t)kb * kWideK);
+        const Wide a = load_stream32<kEvictFirst>(wa_p + (size_t)kb * kWideK), b = load_stream32<kEvictFirst>(wb_p + (size_t)kb * kWideK);
         multiply(a, b, (size_t)kb);
     }
     pdl_trigger();
@@ -273,20 +281,34 @@ bool wide_enabled() {       // PULSAR_SKINNY_WIDE=0 keeps the 16-byte loads
     return on;
 }
 
+bool evict_first_enabled() {       // PULSAR_SKINNY_EVICT_FIRST=0: weight loads without the L2 hints
+    static const bool on = [] {
+        const char* v = getenv("PULSAR_SKINNY_EVICT_FIRST");
+        return !(v && v[0] == '0' && v[1] == 0);
+    }();
+    return on;
+}
+
+template <int NT, int kU, bool kEvictFirst>
+int launch_wide(int mode, int out_dtype, const bf16* xp, const bf16* wp, void* out, int M, int N, int K, cudaStream_t stream) {
+    if (mode == kSwiGLU) {
+        const int inter = N / 2;
+        if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
+        return launch_pdl(gemm_skinny_wide_kernel<NT, kSwiGLU, bf16, kU, kEvictFirst>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
+    }
+    if (out_dtype == PB_BF16)
+        return launch_pdl(gemm_skinny_wide_kernel<NT, kPlain, bf16, kU, kEvictFirst>, N / kRows, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, 0);
+    return launch_pdl(gemm_skinny_wide_kernel<NT, kPlain, float, kU, kEvictFirst>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
+}
+
 template <int NT, int kUnroll>
 int launch_u(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)w;
     if (K % 64 == 0 && (((uintptr_t)x | (uintptr_t)w) & 31) == 0 && wide_enabled()) {
         constexpr int kU = kUnroll / 2;                 // the same bytes in flight
-        if (mode == kSwiGLU) {
-            const int inter = N / 2;
-            if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
-            return launch_pdl(gemm_skinny_wide_kernel<NT, kSwiGLU, bf16, kU>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
-        }
-        if (out_dtype == PB_BF16)
-            return launch_pdl(gemm_skinny_wide_kernel<NT, kPlain, bf16, kU>, N / kRows, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, 0);
-        return launch_pdl(gemm_skinny_wide_kernel<NT, kPlain, float, kU>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
+        return evict_first_enabled() ? launch_wide<NT, kU, true>(mode, out_dtype, xp, wp, out, M, N, K, stream)
+                                     : launch_wide<NT, kU, false>(mode, out_dtype, xp, wp, out, M, N, K, stream);
     }
     if (mode == kSwiGLU) {
         const int inter = N / 2;

@@ -20,6 +20,22 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool p
     const int bytes = pred ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
 }
+// The same copy with an L2 cache policy (from l2_policy_evict_first / l2_policy_normal).
+__device__ __forceinline__ void cp_async16_policy(uint32_t dst, const void* src, bool pred, uint64_t policy) {
+    const int bytes = pred ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;\n" ::"r"(dst), "l"(src), "r"(bytes), "l"(policy));
+}
+// Lines fetched under this policy are the first to leave L2: for data that is read once per step and is larger than L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ uint64_t l2_policy_normal() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;\n" : "=l"(policy));
+    return policy;
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
@@ -58,7 +74,8 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 template <int D, int THREADS>
 __device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, const bf16* __restrict__ k_pool,
                                              const bf16* __restrict__ v_pool, const int* __restrict__ table, int key0,
-                                             int first_key, int last_key, int kvh, int Hkv, int page_shift, int tid) {
+                                             int first_key, int last_key, int kvh, int Hkv, int page_shift, int tid,
+                                             uint64_t policy = 0) {
     constexpr int kChunks = D / 8;
     constexpr int kRowsPerPass = THREADS / kChunks;       // a multiple of 8: (row & 7) does not change
     constexpr int kPasses = 64 / kRowsPerPass;
@@ -75,8 +92,13 @@ __device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, con
             const int page = table[key >> page_shift];
             const size_t at = (size_t)(page * Hkv + kvh) * page_elems + (size_t)((key & page_mask) * D + col);
             const uint32_t off = off0 + (uint32_t)(i * kRowsPerPass * kChunks * 16);
-            cp_async16(k_dst + off, k_pool + at, true);
-            cp_async16(v_dst + off, v_pool + at, true);
+            if (policy) {
+                cp_async16_policy(k_dst + off, k_pool + at, true, policy);
+                cp_async16_policy(v_dst + off, v_pool + at, true, policy);
+            } else {
+                cp_async16(k_dst + off, k_pool + at, true);
+                cp_async16(v_dst + off, v_pool + at, true);
+            }
         }
     } else {
 #pragma unroll
@@ -89,8 +111,13 @@ __device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, con
                 at = (size_t)(page * Hkv + kvh) * page_elems + (size_t)((key & page_mask) * D + col);
             }
             const uint32_t off = off0 + (uint32_t)(i * kRowsPerPass * kChunks * 16);
-            cp_async16(k_dst + off, k_pool + at, ok);
-            cp_async16(v_dst + off, v_pool + at, ok);
+            if (policy) {
+                cp_async16_policy(k_dst + off, k_pool + at, ok, policy);
+                cp_async16_policy(v_dst + off, v_pool + at, ok, policy);
+            } else {
+                cp_async16(k_dst + off, k_pool + at, ok);
+                cp_async16(v_dst + off, v_pool + at, ok);
+            }
         }
     }
 }
