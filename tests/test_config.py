@@ -121,3 +121,21 @@ def test_engine_config_rejects_unknown_keys_and_checks_invariants():
     with pytest.raises(ConfigError, match="top_p"):
         EngineConfig.from_dict({"top_p": 0.0})
     assert EngineConfig.from_dict({}).temperature == 0.0 and EngineConfig.from_dict({}).seed == -1
+
+
+def test_decode_splits_choice():
+    """The number of key splits of the decode attention: fills the SMs once while everything fits, stays within
+    one split per 256 tokens of the block table, and takes more than one split where a single one would leave a
+    thin last round of blocks (the measured cases: batch 48 with 8 kv heads, not batch 64)."""
+    from pulsar_b200 import ops
+    assert ops.decode_splits(8, 8, 4096 + 64) == 4
+    assert ops.decode_splits(1, 8, 4096 + 64) == 16
+    assert ops.decode_splits(1, 8, 32768) == 32
+    assert ops.decode_splits(64, 8, 4096 + 64) == 1
+    assert ops.decode_splits(48, 8, 4096 + 64) in (2, 3)
+    for batch in range(1, 300, 7):
+        for heads in (1, 2, 8):
+            for tokens in (16, 300, 4096, 100000):
+                k = ops.decode_splits(batch, heads, tokens)
+                assert 1 <= k <= 32 and k <= max(1, tokens // 256)
+                assert k == ops.decode_splits(batch, heads, tokens)
