@@ -175,12 +175,18 @@ __device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
     return v;
 }
 
-template <int NT, int MODE, typename OutT, int kUnroll, bool kEvictFirst>
-__global__ void __launch_bounds__(kWarps * 32)
-gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
-                        int inter) {
+// kPre > 0: besides the first batch of register loads, every warp asks for its next kPre k-blocks by cp.async into
+// shared memory before the kernel waits for its predecessor, so that twice the bytes are on their way while the
+// kernel before this one ends; a warp copies and reads only its own part (no block barrier), rows padded by 16
+// bytes against bank conflicts.  The sums keep their order.
+template <int NT, int MODE, typename OutT, int kUnroll, bool kEvictFirst, int kPre>
+__device__ __forceinline__ void
+skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
+                 int inter) {
     constexpr int kWideK = 64;                        // k per load: 4 threads x 16 contiguous elements
+    constexpr int kPreRow = kPre * 128 + 16;          // bytes of a row's prefetched part in shared memory
     __shared__ float red[kWarps][kRows][8 * NT + 1];
+    __shared__ __align__(16) unsigned char pre[kPre > 0 ? kWarps : 1][kPre > 0 ? kRows : 1][kPre > 0 ? kPreRow : 16];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     int row_a, row_b;
@@ -211,6 +217,25 @@ gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, 
             wb[u] = load_stream32<kEvictFirst>(wb_p + (size_t)(kb + u) * kWideK);
         }
     }
+    const bool pre_ok = kPre > 0 && first && kb + kUnroll + kPre <= kb_end;      // the same for a whole warp
+    if constexpr (kPre > 0) if (pre_ok) {
+        // 16 rows x kPre * 128 bytes, 16 bytes per lane and copy: one copy instruction covers whole rows' parts
+        constexpr int kChunks = kPre > 0 ? kPre * 8 : 1;      // 16-byte chunks of a row's part
+        constexpr int kRowsPerCopy = 32 / kChunks;
+        static_assert(kPre == 0 || (32 % kChunks == 0 && kRows % kRowsPerCopy == 0), "prefetch shape");
+        const uint64_t policy = l2_policy_evict_first();
+        const int chunk = lane % kChunks, r0 = lane / kChunks;
+#pragma unroll
+        for (int i = 0; i < kRows / kRowsPerCopy; ++i) {
+            const int r = i * kRowsPerCopy + r0;
+            int wrow;
+            if (MODE == kSwiGLU) wrow = r < 8 ? blockIdx.x * 8 + r : inter + blockIdx.x * 8 + (r - 8);
+            else wrow = blockIdx.x * kRows + r;
+            const bf16* src = w + (size_t)wrow * K + (size_t)(kb + kUnroll) * kWideK + chunk * 8;
+            cp_async16_policy(smem_u32(&pre[warp][r][chunk * 16]), src, true, policy);
+        }
+        cp_async_commit();
+    }
     pdl_wait();
     auto multiply = [&](const Wide& a, const Wide& b, size_t kb_at) {
         const uint32_t a1[4] = {a.lo.x, b.lo.x, a.lo.y, b.lo.y};
@@ -226,7 +251,36 @@ gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, 
             mma_bf16(c[n], a4, xv.hi.z, xv.hi.w);
         }
     };
-    for (bool loaded = first; kb + kUnroll <= kb_end; kb += kUnroll, loaded = false) {
+    bool loaded = first;
+    if constexpr (kPre > 0) if (pre_ok) {
+        // the register batch, then (with the next register batch already asked for) the part in shared memory
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) multiply(wa[u], wb[u], (size_t)(kb + u));
+        kb += kUnroll;
+        loaded = kb + kPre + kUnroll <= kb_end;
+        if (loaded) {
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                wa[u] = load_stream32<kEvictFirst>(wa_p + (size_t)(kb + kPre + u) * kWideK);
+                wb[u] = load_stream32<kEvictFirst>(wb_p + (size_t)(kb + kPre + u) * kWideK);
+            }
+        }
+        cp_async_wait<0>();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < kPre; ++j) {
+            Wide a, b;
+            const unsigned char* pa = &pre[warp][g][j * 128 + t * 32];
+            const unsigned char* pb = &pre[warp][g + 8][j * 128 + t * 32];
+            a.lo = *reinterpret_cast<const uint4*>(pa);
+            a.hi = *reinterpret_cast<const uint4*>(pa + 16);
+            b.lo = *reinterpret_cast<const uint4*>(pb);
+            b.hi = *reinterpret_cast<const uint4*>(pb + 16);
+            multiply(a, b, (size_t)(kb + j));
+        }
+        kb += kPre;
+    }
+    for (; kb + kUnroll <= kb_end; kb += kUnroll, loaded = false) {
         if (!loaded) {
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
@@ -269,6 +323,22 @@ gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, 
     }
 }
 
+template <int NT, int MODE, typename OutT, int kUnroll, bool kEvictFirst>
+__global__ void __launch_bounds__(kWarps * 32)
+gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
+                        int inter) {
+    skinny_wide_body<NT, MODE, OutT, kUnroll, kEvictFirst, 0>(x, w, out, M, N, K, inter);
+}
+
+// With the prefetch through shared memory; the register count is held to what lets as many blocks share an SM as
+// without it (three with two loads in flight, two with four).
+template <int NT, int MODE, typename OutT, int kUnroll>
+__global__ void __launch_bounds__(kWarps * 32, kUnroll <= 2 ? 3 : 2)
+gemm_skinny_wide_prefetch_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N,
+                                 int K, int inter) {
+    skinny_wide_body<NT, MODE, OutT, kUnroll, true, 2>(x, w, out, M, N, K, inter);
+}
+
 // kUnroll: k-blocks whose weight loads a thread keeps in flight.  8 costs 128 registers, so that two blocks
 // share an SM; 4 lets three share it.  A product whose blocks all fit two per SM takes 8; one with more blocks
 // takes 4, so that it does not need a second, nearly empty round of blocks (the QKV product of the 8B sizes:
@@ -289,6 +359,14 @@ bool evict_first_enabled() {       // PULSAR_SKINNY_EVICT_FIRST=0: weight loads 
     return on;
 }
 
+bool prefetch_enabled() {          // PULSAR_SKINNY_PREFETCH=0: no part of the weights through shared memory
+    static const bool on = [] {
+        const char* v = getenv("PULSAR_SKINNY_PREFETCH");
+        return !(v && v[0] == '0' && v[1] == 0);
+    }();
+    return on;
+}
+
 template <int NT, int kU, bool kEvictFirst>
 int launch_wide(int mode, int out_dtype, const bf16* xp, const bf16* wp, void* out, int M, int N, int K, cudaStream_t stream) {
     if (mode == kSwiGLU) {
@@ -301,14 +379,27 @@ int launch_wide(int mode, int out_dtype, const bf16* xp, const bf16* wp, void* o
     return launch_pdl(gemm_skinny_wide_kernel<NT, kPlain, float, kU, kEvictFirst>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
 }
 
+template <int kU>
+int launch_prefetch(int mode, int out_dtype, const bf16* xp, const bf16* wp, void* out, int M, int N, int K, cudaStream_t stream) {
+    if (mode == kSwiGLU) {
+        const int inter = N / 2;
+        if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
+        return launch_pdl(gemm_skinny_wide_prefetch_kernel<1, kSwiGLU, bf16, kU>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
+    }
+    if (out_dtype == PB_BF16)
+        return launch_pdl(gemm_skinny_wide_prefetch_kernel<1, kPlain, bf16, kU>, N / kRows, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, 0);
+    return launch_pdl(gemm_skinny_wide_prefetch_kernel<1, kPlain, float, kU>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
+}
+
 template <int NT, int kUnroll>
 int launch_u(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)w;
     if (K % 64 == 0 && (((uintptr_t)x | (uintptr_t)w) & 31) == 0 && wide_enabled()) {
         constexpr int kU = kUnroll / 2;                 // the same bytes in flight
-        return evict_first_enabled() ? launch_wide<NT, kU, true>(mode, out_dtype, xp, wp, out, M, N, K, stream)
-                                     : launch_wide<NT, kU, false>(mode, out_dtype, xp, wp, out, M, N, K, stream);
+        if (!evict_first_enabled()) return launch_wide<NT, kU, false>(mode, out_dtype, xp, wp, out, M, N, K, stream);
+        if (NT == 1 && prefetch_enabled()) return launch_prefetch<kU>(mode, out_dtype, xp, wp, out, M, N, K, stream);
+        return launch_wide<NT, kU, true>(mode, out_dtype, xp, wp, out, M, N, K, stream);
     }
     if (mode == kSwiGLU) {
         const int inter = N / 2;
