@@ -3,13 +3,16 @@
 // to stream W from HBM.
 //
 // The weights take the role of the MMA's 16-row operand and the tokens that of its 8-wide
-// one (mma.m16n8k16, float32 accumulators).  Nothing is staged in shared memory: a thread
+// one (mma.m16n8k16, float32 accumulators).  Weights go from global memory into registers (only
+// the two k-blocks per warp that are asked for before the kernel may start pass through shared
+// memory, see skinny_wide_body): a thread
 // loads 32 contiguous bytes of a weight row (16 where K is no multiple of 64) straight into the
 // registers of A fragments and as many bytes of a token's activations into B fragments; because a dot product does
 // not care about the order of its terms, the k-index that a fragment slot stands for is
 // permuted the same way on both sides, which makes the vector loads legal.  A block owns
 // 16 weight rows; its 8 warps split K, keep 8 vector loads each in flight, and their
-// partial sums are added in warp order through shared memory.
+// partial sums are added in warp order through shared memory.  The 32-byte loads mark their
+// lines as the first to leave L2 (weights are read once and are far larger than L2).
 //
 // Epilogues: plain (bfloat16 or float32 output), or SwiGLU: the block's 16 rows are 8 gate
 // rows and the 8 up rows that belong to them, and it writes silu(gate) * up (float32
