@@ -9,6 +9,9 @@ def __getattr__(name):
     if name in ("Pulsar", "Session", "generate"):
         from . import api
         return getattr(api, name)
+    if name in ("AsyncPulsar", "AsyncSession"):
+        from . import aio
+        return getattr(aio, name)
     if name in ("Engine",):
         from .engine.engine import Engine
         return Engine
