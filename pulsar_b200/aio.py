@@ -69,6 +69,11 @@ class AsyncSession:
     async def get_state(self) -> str:
         return await self._owner._call(lambda e: e.session_state(self._seq_id))
 
+    async def get_context(self):
+        """``(page ids, token ids of each page)`` of what attention reads for this sequence
+        (the reference's ``get_context``, pulsar/src/pulsar/rt/session.py:37-43, without its recall layer)."""
+        return await self._owner._call(lambda e: (e.context_page_ids(self._seq_id), e.context_pages(self._seq_id)))
+
     async def destroy(self) -> None:
         """End the turn in flight, if any, and give the sequence's pages back."""
         self._owner._discard(self._seq_id)

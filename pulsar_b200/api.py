@@ -49,6 +49,11 @@ class Session:
     def get_state(self) -> str:
         return self._engine.session_state(self._seq_id)
 
+    def get_context(self):
+        """``(page ids, token ids of each page)`` of what attention reads for this sequence
+        (pulsar/src/pulsar/rt/session.py:37-43, without the reference's recall layer)."""
+        return self._engine.context_page_ids(self._seq_id), self._engine.context_pages(self._seq_id)
+
     def destroy(self) -> None:
         self._engine.release(self._seq_id)
 

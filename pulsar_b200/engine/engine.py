@@ -118,8 +118,40 @@ class Engine:
         self._sessions[sid] = _Session(params, make_generator(params.seed), [int(t) for t in tokens], 0)
         return sid
 
-    def set_decode_budget(self, seq_id: int, max_tokens: int) -> None:
-        self._session(seq_id).budget = int(max_tokens)
+    def set_decode_budget(self, seq_id: int, max_tokens: Optional[int] = None) -> None:
+        """New tokens allowed in the turns that follow; None: only the stop token ends a turn
+        (engine.cpp:453-456)."""
+        self._session(seq_id).budget = 0 if max_tokens is None else int(max_tokens)
+
+    def active_sequence_count(self) -> int:
+        """Sequences that are running or waiting to run (engine.cpp:458-460)."""
+        return len(self.scheduler.running) + len(self.scheduler.waiting)
+
+    def active_tokens_count(self, seq_id: int) -> int:
+        """Tokens of the sequence whose keys and values are in the cache (engine.cpp:492-494)."""
+        self._drain()
+        return self.cache.length(seq_id) if self.cache.has(seq_id) else 0
+
+    def context_page_ids(self, seq_id: int) -> List[int]:
+        """The pages that attention reads for this sequence, in the order of their tokens (of the first group
+        of cache entries; pages that a window has passed are given back and not listed) (engine.cpp:533-540)."""
+        self._drain()
+        if not self.cache.has(seq_id) or not self.cache.groups:
+            return []
+        return [p for p in self.cache.table(seq_id, 0) if p >= 0]
+
+    def context_pages(self, seq_id: int) -> List[List[int]]:
+        """The token ids held by each of those pages (engine.cpp:542-549)."""
+        self._drain()
+        if not self.cache.has(seq_id) or not self.cache.groups:
+            return []
+        size, held = self.cache.page_size, self.cache.length(seq_id)
+        tokens = [t for t in self.scheduler.seqs[seq_id].tokens[:held]] if seq_id in self.scheduler.seqs else []
+        out = []
+        for logical, page in enumerate(self.cache.table(seq_id, 0)):
+            if page >= 0 and logical * size < held:
+                out.append(tokens[logical * size:min(held, (logical + 1) * size)])
+        return out
 
     def _session(self, seq_id: int) -> _Session:
         try:

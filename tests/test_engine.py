@@ -158,8 +158,22 @@ def test_sessions_turn_by_turn_on_kept_pages(folders):
     s.send([9, 9, 8], 3)
     second = list(s.recv())
     assert second == plain.greedy_generate(cfg, weights, [3, 4, 5, 6, 7] + first + [9, 9, 8], 3)
+    # what the engine tells about a sequence (engine.cpp:458-460, 492-494, 533-549): cached tokens, their pages
+    eng = p.engine
+    everything = [3, 4, 5, 6, 7] + first + [9, 9, 8] + second
+    held = eng.active_tokens_count(s.seq_id)
+    assert held == len(everything) - 1                   # the last sampled token has not been fed yet
+    ids, pages = eng.context_page_ids(s.seq_id), eng.context_pages(s.seq_id)
+    assert len(ids) == len(set(ids)) == -(-held // page) == len(pages)
+    assert [t for pg in pages for t in pg] == everything[:held] and all(len(pg) <= page for pg in pages)
+    assert eng.active_sequence_count() == 0
+    eng.set_decode_budget(s.seq_id, 2)
+    s.send([1])
+    assert eng.active_sequence_count() == 1
+    assert len(list(s.recv())) == 2
     s.destroy()
     assert p.engine.cache.live_requests() == [] and s.get_state() == "unknown"
+    assert eng.active_tokens_count(s.seq_id) == 0 and eng.context_page_ids(s.seq_id) == [] and eng.context_pages(s.seq_id) == []
     with pytest.raises(Exception, match="unknown keys"):
         Pulsar(folders["B"], dict(pagesize=8))
 
