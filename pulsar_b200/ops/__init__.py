@@ -11,13 +11,12 @@ The reference exposes its kernels as ``torch.ops.pulsar.*`` through TorchBind
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
 
 from ..csrc.build import library
-
-import os
 
 F32, BF16 = 0, 1
 # Which product serves bfloat16 projections of more than 16 rows:
