@@ -170,11 +170,14 @@ def test_gemm_simt_is_true_float32(m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 2, 7, 8, 9, 16])
-@pytest.mark.parametrize("n,k", [(48, 96), (4096, 4096), (1024, 12288), (304, 160)])
+@pytest.mark.parametrize("n,k", [(48, 96), (4096, 4096), (1024, 12288), (304, 160), (64, 2048), (32, 1536), (48, 832), (640, 5120)])
 def test_gemm_skinny(m, n, k):
     """The weight-streaming product for a few tokens against float64, plain and with the
     SwiGLU epilogue, float32 and bfloat16 outputs; one weight made large so that a wrong
-    k-permutation of the fragments would show."""
+    k-permutation of the fragments would show.  The widths decide which paths a warp takes: 8, 24 or 10
+    blocks of 64 per warp (register batches, the part prefetched through shared memory, the rest), 4 or 3
+    (too few for the prefetch or for what follows it), 13 blocks over 8 warps (uneven), and widths that are
+    no multiple of 64 (16-byte loads)."""
     from pulsar_b200 import ops
     g = torch.Generator().manual_seed(13)
     a = torch.randn(m, k, generator=g).bfloat16()
