@@ -178,6 +178,24 @@ def test_sessions_turn_by_turn_on_kept_pages(folders):
         Pulsar(folders["B"], dict(pagesize=8))
 
 
+def test_a_malformed_session_override_throws_at_create_session(folders):
+    """pulsar-core/tests/runtime/test_engine.cpp:165-194: a bad knob fails when the session is made, opens nothing,
+    and the next good session is the first one."""
+    raw, seed, page = TINY["B"]
+    eng = _engine(folders["B"], "float32", page)
+    for bad in (dict(top_p=0.0), dict(top_p=1.5), dict(top_k=-1), dict(block_radius=4), dict(temprature=0.7)):
+        with pytest.raises(ValueError):
+            eng.create_session([1, 2, 3], bad)
+    assert eng.active_sequence_count() == 0 and eng.session_state(0) == "unknown"
+    sid = eng.create_session([1, 2, 3], dict(temperature=0.7, top_k=5, top_p=0.9, seed=3))
+    assert sid == 0
+    eng.feed(sid, [], 2)
+    assert eng.active_sequence_count() == 1
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.feed(eng.create_session([1]), [10 ** 9], 2)
+    eng.release(sid)
+
+
 def _drive(eng, prompts, budgets, lookahead, overrides=None, second_turn=None):
     """Feed the prompts and step until nothing is left; the events per sequence, in order."""
     sids = [eng.create_session(p, overrides(i) if overrides else None) for i, p in enumerate(prompts)]
