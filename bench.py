@@ -112,6 +112,16 @@ def build_engine(shape: dict, n_layers: int, batch: int, context: int, max_chunk
     return engine
 
 
+def decode_bytes_of_shape(raw: dict, batch: int, context: float) -> float:
+    """Bytes a decode step must read, from the sizes alone: every weight once, ``batch`` embedding rows and the
+    live cache (bfloat16)."""
+    d, hq, hkv, hd, inter, v, layers = (raw["hidden_size"], raw["num_attention_heads"], raw["num_key_value_heads"],
+                                        raw["head_dim"], raw["intermediate_size"], raw["vocab_size"], raw["num_hidden_layers"])
+    per_layer = 2 * ((hq + 2 * hkv) * hd * d + hq * hd * d + 3 * inter * d) + 4 * (2 * d + 2 * hd)
+    weights = layers * per_layer + 4 * d + 2 * v * d + 2 * batch * d
+    return float(weights + batch * context * layers * 2 * hkv * hd * 2)
+
+
 def decode_bytes(engine, batch: int, context: int) -> float:
     model = engine.model
     kv = 0
@@ -243,13 +253,21 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": "cosmonomic/pulsar cannot be installed offline here: its package "
-                          "needs hatchling, xmake, Python 3.13 and torch 2.14 to build pulsar_core.so (none present)"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import reference_arm
+        why = reference_arm.available()
+        if why is not None:
+            print(json.dumps({"impl": "reference", "unavailable": why}))
+            return 0
+        shape = SHAPES[args.shape]
+        line = reference_arm.run(args, shape, f"Qwen3-{args.shape.upper()} shape", peaks(), prefill_flops,
+                                 decode_bytes_of_shape, ClockSampler)
+        print(json.dumps(line))
+        return 0
     warmup = max(3, args.warmup)
     import torch
     from pulsar_b200 import ops

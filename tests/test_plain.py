@@ -117,3 +117,59 @@ def test_sample_filter_keeps_the_crossing_token():
     assert si.tolist() == [0, 1, 2]
     sp, si = plain.sample_filter(logits, 1.0, 1, 0.99)
     assert si.tolist() == [0]
+
+
+# ---------------------------------------------------------------- the reference's own CUDA kernels
+def _reference_kernel_cases():
+    """tests/golden/make_reference_kernel_golden.py ran the reference's kernels, compiled unchanged, on a B200:
+    rmsnorm, rope, write_kv + the scalar attention ops (and the tensor-core ones on one bfloat16 case)."""
+    from safetensors import safe_open
+    path = os.path.join(GOLDEN, "reference_kernels.safetensors")
+    with safe_open(path, "pt") as f:
+        cases = json.loads(f.metadata()["cases"])
+        tensors = {name: f.get_tensor(name).clone() for name in f.keys()}
+    return cases, tensors
+
+
+def test_plain_rmsnorm_matches_the_references_kernel():
+    cases, t = _reference_kernel_cases()
+    assert len(cases["rmsnorm"]) >= 3
+    for c in cases["rmsnorm"]:
+        x, w, ref = (t[c[k]].to(torch.float64) for k in ("x", "weight", "out"))
+        got = plain.rmsnorm(x, w, c["eps"])
+        assert float(ref[-1].abs().max()) == 0.0 and float(got[-1].abs().max()) == 0.0       # the all-zero row
+        err = float((got - ref).abs().max() / ref.abs().max())
+        assert err < 1e-6, f"rmsnorm width {c['width']}: {err:.2e}"                            # the kernel ran in float32
+
+
+def test_plain_rope_matches_the_references_kernel():
+    cases, t = _reference_kernel_cases()
+    assert len(cases["rope"]) >= 3
+    for c in cases["rope"]:
+        x, ref = t[c["x"]].to(torch.float64), t[c["out"]].to(torch.float64)                # [heads, seq, D]
+        got = plain.rope(x.transpose(0, 1).contiguous(), torch.tensor(c["positions"]), c["theta"]).transpose(0, 1)
+        err = float((got - ref).abs().max())
+        assert err < 1e-6, f"rope head_dim {c['head_dim']} theta {c['theta']}: {err:.2e}"     # up to position 1,000,003
+
+
+def test_plain_attention_matches_the_references_kernels():
+    """The reference's ops hold unrotated keys and rotate key j to position j while reading it
+    (pulsar-core/inc/pulsar/ops.hpp:34-43); the plain implementation rotates each key once, at its
+    position, before plain attention.  Queries are taken as given (already rotated)."""
+    cases, t = _reference_kernel_cases()
+    assert sum(c["op"].endswith("_scalar") for c in cases["attention"]) >= 4
+    for c in cases["attention"]:
+        q_all, k_all, v_all, ref_all = (t[c[k]].to(torch.float64) for k in ("q", "k_unrotated", "v", "out"))
+        bar = 5e-6 if c["dtype"] == "float32" else 1e-2      # seen: 4.5e-7 (scalar, float32), 2.7e-3 (tensor cores, bfloat16)
+        q_at = k_at = 0
+        for n_q, ctx in c["seqs"]:
+            q, ref = q_all[q_at:q_at + n_q], ref_all[q_at:q_at + n_q]
+            k, v = k_all[k_at:k_at + ctx], v_all[k_at:k_at + ctx]
+            q_at, k_at = q_at + n_q, k_at + ctx
+            k_rot = plain.rope(k, torch.arange(ctx), c["theta"])
+            # the n_q queries sit at the last n_q positions of the context: run the whole context and keep those rows
+            q_full = torch.zeros(ctx, *q.shape[1:], dtype=torch.float64)
+            q_full[ctx - n_q:] = q
+            got = plain.attention(q_full, k_rot, v, c["scale"])[ctx - n_q:]
+            err = float((got - ref).abs().max() / ref.abs().max())
+            assert err < bar, f"{c['op']} {c['dtype']} D={c['head_dim']} ({n_q}, {ctx}): {err:.2e}"
