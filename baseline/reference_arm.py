@@ -33,6 +33,9 @@ def available():
     if not os.path.isfile(lib):
         return ("baseline/_ref/pulsar/pulsar_core.so is not built: run `python baseline/build_reference.py --src <checkout>` "
                 "where the reference's sources are (its own build needs xmake, hatchling, Python 3.13 and torch 2.14)")
+    import torch
+    if not torch.cuda.is_available():
+        return "no CUDA device here: the reference's engine runs on a GPU only"
     return None
 
 

@@ -46,8 +46,16 @@ TINY_E = dict(
     rms_norm_eps=4e-6, tie_word_embeddings=False, use_sliding_window=True, sliding_window=150,
     max_window_layers=1, hidden_act="silu", attention_bias=False, initializer_range=0.03, eos_token_id=9)
 
+# Eight key/value heads: a few dozen sequences make more (sequence, kv head) pairs than a decode attention grid
+# has block slots, so the blocks run in rounds and the split rule for that case applies.
+TINY_F = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=336, hidden_size=192, intermediate_size=224,
+    num_hidden_layers=2, num_attention_heads=16, num_key_value_heads=8, head_dim=64, rope_theta=200000.0,
+    rms_norm_eps=5e-6, tie_word_embeddings=False, use_sliding_window=False, sliding_window=None,
+    max_window_layers=2, hidden_act="silu", attention_bias=False, initializer_range=0.03, eos_token_id=13)
+
 TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 4), "D": (TINY_D, 3, 16),
-        "E": (TINY_E, 4, 8)}     # config, seed, page size
+        "E": (TINY_E, 4, 8), "F": (TINY_F, 6, 16)}     # config, seed, page size
 
 
 def make_folder(tmpdir: str, raw: dict, seed: int, store_dtype=torch.float32, std: Optional[float] = None) -> str:
@@ -93,6 +101,15 @@ def rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:
 # deep; bfloat16: the reference's own bar for its bfloat16 kernels
 # (pulsar/tests/test_paged_attention.py:50-55: bf16 2e-2, fp32 1e-4).
 TOL = {"float32": 1e-4, "bfloat16": 2e-2}
+
+WORST = {}      # test name -> worst relative error it saw (printed by ``report``; pytest -s or -rP shows it)
+
+
+def report(test: str, worst: float, dtype: str = "") -> float:
+    """Print the worst error a comparison saw, so that the distance to the bar is on record."""
+    WORST[test] = max(WORST.get(test, 0.0), worst)
+    print(f"[worst error] {test} {dtype}: {worst:.3e} (bar {TOL.get(dtype, float('nan')):.1e})")
+    return worst
 
 
 class Trace:

@@ -1,5 +1,5 @@
 """What bench.py answers without touching a GPU: more than one GPU is refused with one line and exit code 2, and
-the reference arm says in one JSON line why it is unavailable."""
+the reference arm says in one JSON line why it is unavailable (not built, or built but no GPU here)."""
 import json
 import os
 import subprocess

@@ -223,6 +223,52 @@ def _drive(eng, prompts, budgets, lookahead, overrides=None, second_turn=None):
     return [seen[sid] for sid in sids]
 
 
+@pytest.mark.parametrize("lookahead", [False, True])
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_bfloat16_tokens_of_the_schedulers_own_mixed_steps_follow_the_plain_logits(folders, name, lookahead):
+    """Four requests fed at once with a token budget far below their prompts: the scheduler's own steps hold the
+    decoded tokens of the requests that are through their prompts first and portions of the others behind them
+    (the order in which the attention dispatch splits a step between its decode and its prompt kernels).  Every
+    token that comes out is checked against the plain logits of its own prefix."""
+    raw, seed, page = TINY[name]
+    cfg, weights = helpers.read_folder(folders[name])
+    w16 = helpers.as_bf16_matrices(weights)
+    rng = random.Random(77)
+    prompts = [helpers.random_tokens(rng, n, raw["vocab_size"]) for n in (9, 150, 61, 230)]
+    budgets = [30, 12, 22, 9]
+    eng = _engine(folders[name], "bfloat16", page, max_chunk_size=40, num_pages=256)
+    shapes = []
+    run_step = eng.runner.step
+
+    def spy(entries, sampled_ids=None):
+        shapes.append([len(e.tokens) for e in entries])
+        return run_step(entries, sampled_ids)
+    eng.runner.step = spy
+    sids = [eng.create_session(p) for p in prompts]
+    for sid, b in zip(sids, budgets):
+        eng.feed(sid, [], b)
+    out = {sid: [] for sid in sids}
+    while eng.has_work():
+        for sid, tok, _ in eng.step(1, lookahead=lookahead):
+            out[sid].append(tok)
+    assert [len(out[s]) for s in sids] == budgets
+    mixed = [q for q in shapes if q[0] == 1 and max(q) > 1]
+    assert len(mixed) >= 4, shapes                       # decoded tokens first, portions behind them
+    for q in mixed:
+        n_dec = next(i for i, n in enumerate(q) if n > 1)
+        assert all(n > 1 for n in q[n_dec:]), q
+    worst = 0.0
+    for sid, prompt in zip(sids, prompts):
+        seq = list(prompt)
+        for tok in out[sid]:
+            row = plain.forward(cfg, w16, seq, torch.float64)[-1]
+            gap = float(row.max() - row[tok]) / float(row.abs().max())
+            worst = max(worst, gap)
+            assert gap <= TOL["bfloat16"], f"sequence {sid}: token {tok} at position {len(seq)} is {gap:.2e} below the best"
+            seq.append(tok)
+    helpers.report(f"mixed_steps[{name}]", worst, "bfloat16")
+
+
 @pytest.mark.parametrize("name,dtype", [("B", "float32"), ("D", "bfloat16")])
 def test_stepping_one_pass_ahead_gives_the_same_tokens(folders, name, dtype):
     """Engine.step launches the next pass before it reads the last one's tokens (they are fed on the
@@ -323,25 +369,35 @@ def test_command_line(folders, tmp_path):
     assert got == [plain.greedy_generate(cfg, weights, p, 5) for p in ([1, 2, 3, 4], [9, 8, 7])]
 
 
+LAYER_SIZES = {      # hidden, intermediate, query heads (8 kv heads of 128 each): the dense sizes of the family
+    "8b": (4096, 12288, 32), "14b": (5120, 17408, 40), "32b": (5120, 25600, 64)}
+
+
 @pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
-def test_layer_sizes_of_qwen3_8b(tmp_path_factory, dtype):
-    """Two layers with the real layer sizes (hidden 4096, 32/8 heads of 128, intermediate 12288) and a
-    vocabulary that is no power of two: the sizes at which the weight-streaming, tcgen05 and
-    tensor-core attention kernels run in the benchmark.  A prompt in portions, then single tokens,
-    beside a second request; logits against the plain implementation (float32 on the CPU here)."""
+@pytest.mark.parametrize("shape", ["8b", "14b", "32b"])
+def test_layer_sizes_of_the_family(tmp_path_factory, shape, dtype):
+    """Two layers with the real layer sizes (8B: hidden 4096, 32/8 heads of 128, intermediate 12288; 14B: hidden
+    5120, groups of 5 query heads, intermediate 17408; 32B: groups of 8, intermediate 25600) and a vocabulary
+    that is no power of two: the sizes at which the weight-streaming, tcgen05 and tensor-core attention kernels
+    run in the benchmark.  A prompt in portions, then single tokens, beside a second request; then twenty short
+    requests that bring one token each in the same step (more rows than the weight-streaming product takes).
+    Logits against the plain implementation (float32 on the CPU here)."""
     from pulsar_b200.replay import Replay
-    raw = dict(helpers.TINY_B, vocab_size=15193, hidden_size=4096, intermediate_size=12288, num_hidden_layers=2,
-               num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    hidden, inter, heads = LAYER_SIZES[shape]
+    raw = dict(helpers.TINY_B, vocab_size=15193, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=2,
+               num_attention_heads=heads, num_key_value_heads=8, head_dim=128, rope_theta=1000000.0, rms_norm_eps=1e-6,
                max_window_layers=2, initializer_range=0.02)
-    folder = helpers.make_folder(tmp_path_factory.mktemp("layers8b"), raw, 5)
+    folder = helpers.make_folder(tmp_path_factory.mktemp("layers" + shape), raw, 5, store_dtype=torch.bfloat16)
     cfg, weights = helpers.read_folder(folder)
-    if dtype == "bfloat16":
-        weights = helpers.as_bf16_matrices(weights)
+    weights = {n: t.to(torch.float32) for n, t in weights.items()}
     rng = random.Random(12)
     reqs = {"a": helpers.random_tokens(rng, 150, 15193), "b": helpers.random_tokens(rng, 41, 15193)}
+    for i in range(20):
+        reqs[f"s{i}"] = helpers.random_tokens(rng, 3 + (i * 7) % 11, 15193)
     ref = {rid: plain.forward(cfg, weights, toks, torch.float32) for rid, toks in reqs.items()}
-    rp = Replay(folder, dtype, 256, page_size=16)
+    rp = Replay(folder, dtype, 256 + 20 * 64, page_size=16, max_running=24)
     got = {}
+    fed = {rid: 0 for rid in reqs}
 
     def run(step, entries, end=()):
         logits = rp.run_step({"step": step, "entries": [{"id": r, "tokens": t, "want": list(range(len(t)))} for r, t in entries],
@@ -352,13 +408,17 @@ def test_layer_sizes_of_qwen3_8b(tmp_path_factory, dtype):
                 got[(r, fed[r] + k)] = logits[i]
                 i += 1
             fed[r] += len(t)
-    fed = {"a": 0, "b": 0}
     a, b = reqs["a"], reqs["b"]
     run(0, [("a", a[:100])])
     run(1, [("a", a[100:130]), ("b", b[:33])])                  # a later portion beside a first portion
     for i in range(8):                                          # single tokens of both
         run(2 + i, [("a", a[130 + i:131 + i]), ("b", b[33 + i:34 + i])])
     run(10, [("a", a[138:150])], end=["a", "b"])
-    assert len(got) == 150 + 41
+    short = [f"s{i}" for i in range(20)]
+    run(11, [(r, reqs[r][:-2]) for r in short])                 # twenty first portions in one step
+    run(12, [(r, reqs[r][-2:-1]) for r in short])               # twenty single tokens in one step
+    run(13, [(r, reqs[r][-1:]) for r in short], end=short)
+    assert len(got) == sum(len(t) for t in reqs.values())
     worst = max(helpers.rel_err(row, ref[rid][pos]) for (rid, pos), row in got.items())
+    helpers.report(f"layer_sizes[{shape}]", worst, dtype)
     assert worst < TOL[dtype], f"worst relative error {worst:.3e}"

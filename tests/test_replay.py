@@ -34,7 +34,7 @@ def _reference(folder, dtype, requests):
     return {rid: helpers.plain_logits(cfg, w, toks) for rid, toks in requests.items()}
 
 
-def _replay(folder, dtype, trace, max_tokens, page_size, max_running=8):
+def _replay(folder, dtype, trace, max_tokens, page_size, max_running=8, inspect=None):
     from pulsar_b200.replay import Replay
     rp = Replay(folder, dtype, max_tokens, page_size=page_size, max_running=max_running)
     got = {}
@@ -46,6 +46,8 @@ def _replay(folder, dtype, trace, max_tokens, page_size, max_running=8):
     rp.cache.check_consistency()
     assert rp.cache.live_requests() == []
     assert all(f == g.allocator.n for f, g in zip(rp.cache.n_free_pages(), rp.cache.groups))
+    if inspect is not None:
+        inspect(rp)
     return got
 
 
@@ -56,7 +58,7 @@ def _compare(got, ref, dtype):
         err = helpers.rel_err(row, ref[rid][pos])
         worst = max(worst, err)
         assert err < TOL[dtype], f"request {rid} position {pos}: error {err:.3e} (first wrong place)"
-    return worst
+    return helpers.report(os.environ.get("PYTEST_CURRENT_TEST", "replay").split("::")[-1].split(" ")[0], worst, dtype)
 
 
 def _round64(n):
@@ -112,6 +114,57 @@ def test_mixed_with_page_reuse(folders, name, dtype):
     assert budget < sum(_round64(n) for n in lengths)
     got = _replay(folders[name], dtype, trace, budget, page, max_running=4)
     assert len(got) == sum(lengths)
+    _compare(got, ref, dtype)
+
+
+# Ragged contexts of the reference's decode-attention test (pulsar/tests/test_paged_attention.py:21-45), shortened
+# where the tiny models would make the plain implementation slow.
+RAGGED = [1, 7, 16, 33, 40, 65, 100, 129]
+
+
+def trace_many_decoding(requests, tail, per_step, order):
+    """Prompts (all but the last ``tail`` tokens) whole, ``per_step`` requests to a step, the last row wanted; then
+    ``tail`` steps in which every request brings one token.  All requests end with the last step."""
+    t = helpers.Trace()
+    for at in range(0, len(order), per_step):
+        t.step([(rid, requests[rid][:-tail], [len(requests[rid]) - tail - 1]) for rid in order[at:at + per_step]])
+    for i in range(tail, 0, -1):
+        t.step([(rid, [requests[rid][-i]], [0]) for rid in order], end=order if i == 1 else [])
+    return t
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,n", [("D", 20), ("E", 40), ("F", 40), ("F", 72), ("D", 72)])
+def test_steps_of_many_single_tokens(folders, name, n, dtype):
+    """The decode step of a large batch: 20, 40 and 72 requests with ragged contexts, then seven steps in which
+    all of them bring one token (in bfloat16 more than 16 rows take the product for many tokens and a gating
+    kernel of its own; with 8 kv heads 40 requests are more (sequence, kv head) pairs than the decode attention
+    has block slots, so its blocks run in rounds; from the fourth such step on the captured graph is replayed).
+    Two waves of requests on a pool that holds one: every page of the second wave was used by the first.
+    Every row against the plain implementation."""
+    raw, seed, page = TINY[name]
+    rng = random.Random(seed + 70 + n)
+    tail = 7
+    waves = []
+    for w in range(2):
+        lens = [RAGGED[(i + 3 * w) % len(RAGGED)] % 70 + tail + 1 + (i % 5) for i in range(n)]
+        waves.append({f"w{w}r{i}": helpers.random_tokens(rng, ln, raw["vocab_size"]) for i, ln in enumerate(lens)})
+    ref = {}
+    for reqs in waves:
+        ref.update(_reference(folders[name], dtype, reqs))
+    budget = max(sum(-(-len(t) // 64) * 64 for t in reqs.values()) for reqs in waves)
+    trace = helpers.Trace()
+    for reqs in waves:
+        order = list(reqs)
+        sub = trace_many_decoding(reqs, tail, 9, order)
+        for rec in sub.records:
+            trace.step([(e["id"], e["tokens"], e["want"]) for e in rec["entries"]], end=rec["end"])
+
+    def inspect(rp):
+        assert rp.runner.graph_replays >= 2 * (tail - 3), rp.runner.graph_replays      # the captured step ran
+
+    got = _replay(folders[name], dtype, trace, budget, page, max_running=n, inspect=inspect)
+    assert len(got) == 2 * n * (tail + 1)
     _compare(got, ref, dtype)
 
 
