@@ -229,7 +229,8 @@ def test_bfloat16_tokens_of_the_schedulers_own_mixed_steps_follow_the_plain_logi
     """Four requests fed at once with a token budget far below their prompts: the scheduler's own steps hold the
     decoded tokens of the requests that are through their prompts first and portions of the others behind them
     (the order in which the attention dispatch splits a step between its decode and its prompt kernels).  Every
-    token that comes out is checked against the plain logits of its own prefix."""
+    row of logits that a token is sampled from is compared with the plain logits at its position, and the token
+    with the plain logits' choice."""
     raw, seed, page = TINY[name]
     cfg, weights = helpers.read_folder(folders[name])
     w16 = helpers.as_bf16_matrices(weights)
@@ -237,12 +238,19 @@ def test_bfloat16_tokens_of_the_schedulers_own_mixed_steps_follow_the_plain_logi
     prompts = [helpers.random_tokens(rng, n, raw["vocab_size"]) for n in (9, 150, 61, 230)]
     budgets = [30, 12, 22, 9]
     eng = _engine(folders[name], "bfloat16", page, max_chunk_size=40, num_pages=256)
-    shapes = []
+    shapes, rows, fed = [], [], {}
     run_step = eng.runner.step
 
     def spy(entries, sampled_ids=None):
         shapes.append([len(e.tokens) for e in entries])
-        return run_step(entries, sampled_ids)
+        logits = run_step(entries, sampled_ids)
+        i = 0
+        for e in entries:
+            fed[e.rid] = fed.get(e.rid, 0) + len(e.tokens)
+            for w in e.want:
+                rows.append((e.rid, fed[e.rid] - len(e.tokens) + w, logits[i].to("cpu", copy=True)))
+                i += 1
+        return logits
     eng.runner.step = spy
     sids = [eng.create_session(p) for p in prompts]
     for sid, b in zip(sids, budgets):
@@ -257,15 +265,19 @@ def test_bfloat16_tokens_of_the_schedulers_own_mixed_steps_follow_the_plain_logi
     for q in mixed:
         n_dec = next(i for i, n in enumerate(q) if n > 1)
         assert all(n > 1 for n in q[n_dec:]), q
+    # the logits every token was sampled from, against the plain logits of the sequence as it came out
+    ref = {sid: plain.forward(cfg, w16, list(p) + out[sid], torch.float64) for sid, p in zip(sids, prompts)}
+    assert len(rows) == sum(budgets)
     worst = 0.0
-    for sid, prompt in zip(sids, prompts):
-        seq = list(prompt)
-        for tok in out[sid]:
-            row = plain.forward(cfg, w16, seq, torch.float64)[-1]
+    for sid, pos, row in rows:
+        err = helpers.rel_err(row, ref[sid][pos])
+        worst = max(worst, err)
+        assert err < TOL["bfloat16"], f"sequence {sid} position {pos}: error {err:.3e}"
+    for sid, prompt in zip(sids, prompts):               # and each token is the plain logits' choice up to rounding
+        for i, tok in enumerate(out[sid]):
+            row = ref[sid][len(prompt) + i - 1]
             gap = float(row.max() - row[tok]) / float(row.abs().max())
-            worst = max(worst, gap)
-            assert gap <= TOL["bfloat16"], f"sequence {sid}: token {tok} at position {len(seq)} is {gap:.2e} below the best"
-            seq.append(tok)
+            assert gap <= TOL["bfloat16"], f"sequence {sid}: token {tok} is {gap:.2e} below the best"
     helpers.report(f"mixed_steps[{name}]", worst, "bfloat16")
 
 
