@@ -17,12 +17,10 @@ import asyncio
 from concurrent.futures import ThreadPoolExecutor
 from typing import Any, Callable, Dict, Optional, Sequence
 
+from .engine.engine import EngineFailed       # the engine raised while stepping: every open stream ends with this,
+                                              # and the instance refuses further work
+
 _END = object()
-
-
-class EngineFailed(RuntimeError):
-    """The engine raised while stepping; every open stream ends with this, and the instance refuses
-    further work (the reference poisons its engine box the same way)."""
 
 
 class TokenStream:

@@ -446,6 +446,13 @@ PB_EXPORT int pb_prefill_tcgen05_error(void) {
     return (int)v > dual ? (int)v : dual;
 }
 
+// As pb_gemm_tcgen05_wait_control, for the two attention kernels: ``addresses`` receives two device addresses
+// (the one-head kernel's error word, the two-head kernel's).
+PB_EXPORT int pb_prefill_tcgen05_wait_control(long long limit, int error, void** addresses) {
+    if (wait_control(g_attn5_error, limit, error, addresses) != 0) return -1;
+    return dual_wait_control(limit, error, addresses ? addresses + 1 : nullptr);
+}
+
 // q, out [N, Hq, D] bfloat16; pools [n_pages, Hkv, page_size, D] bfloat16 with finite contents;
 // n_q_tiles = sum over sequences of ceil(q_len / pb_prefill_tcgen05_tile()).
 PB_EXPORT int pb_paged_attention_prefill_tcgen05(int dtype, const void* q, const void* k_pool, const void* v_pool, void* out,

@@ -526,6 +526,8 @@ int dual_error() {
     return (int)v;
 }
 
+int dual_wait_control(long long limit, int error, void** address) { return wait_control(g_dual_error, limit, error, address); }
+
 // Arguments as those of the one-head launch; n_q_tiles counts tiles of 128 query rows.
 int launch_dual(const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table, int table_stride,
                 const int* cu_q, const int* kv_len, int n_tokens, int n_seqs, int n_q_tiles, int n_pages, int Hq, int Hkv,

@@ -118,6 +118,7 @@ inline int log2_exact(int v) {
 // an even number of query heads; arguments as those of the exported launch.
 bool dual_supported(int Hq, int Hkv);
 int dual_error();
+int dual_wait_control(long long limit, int error, void** address);
 int launch_dual(const void* q, const void* k_pool, const void* v_pool, void* out, const int* block_table, int table_stride,
                 const int* cu_q, const int* kv_len, int n_tokens, int n_seqs, int n_q_tiles, int n_pages, int Hq, int Hkv,
                 int page_size, float scale, int window, cudaStream_t stream);

@@ -385,6 +385,24 @@ PB_EXPORT int pb_move_ids(int* ids, const int* dst, const int* src, const int* s
     return launch_status();
 }
 
+namespace {
+struct WordList { const unsigned int* p[8]; };
+__global__ void gather_words_kernel(WordList words, int n, int* out) {
+    if ((int)threadIdx.x < n) out[threadIdx.x] = (int)*(volatile const unsigned int*)words.p[threadIdx.x];
+}
+}  // namespace
+
+// out[i] = *words[i] for up to 8 device words, in the stream: the error words of the kernels with bounded waits,
+// gathered so that one copy takes them to the host beside a step's results.
+PB_EXPORT int pb_gather_words(const void* const* words, int n, int* out, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (n > 8) return PB_ERR_TOO_LARGE;
+    WordList w;
+    for (int i = 0; i < 8; ++i) w.p[i] = i < n ? (const unsigned int*)words[i] : nullptr;
+    gather_words_kernel<<<1, 32, 0, stream>>>(w, n, out);
+    return launch_status();
+}
+
 PB_EXPORT int pb_embed(int dtype, const void* table, const int* ids, float* out, int n, int width, int vocab,
                        cudaStream_t stream) {
     if (n <= 0) return 0;

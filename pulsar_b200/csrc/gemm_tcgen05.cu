@@ -510,6 +510,38 @@ PB_EXPORT int pb_gemm_tcgen05_error(void) {
     return (int)v;
 }
 
+// limit > 0: the new limit of the kernel's bounded waits in clock cycles; error >= 0: the new value of the error
+// word; address: receives the word's device address.  Returns 0, or -1 when a CUDA call failed.
+PB_EXPORT int pb_gemm_tcgen05_wait_control(long long limit, int error, void** address) {
+    return wait_control(g_tc5_error, limit, error, address);
+}
+
+namespace {
+// One thread waits, with the limit of the bounded waits, on a barrier that nobody arrives on, gives up and sets the
+// error word: the give-up path of the kernels above, alone (no copy in flight, no tensor memory held).
+__global__ void wait_selftest_kernel() {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_addr(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait(smem_addr(&bar), 0, &abort_flag)) {
+            abort_flag = 1;
+            atomicMax(&g_tc5_error, 9u);
+        }
+        asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_addr(&bar)) : "memory");
+    }
+}
+}  // namespace
+
+// Runs the kernel above: afterwards the error word reads 9.  With the first limit it takes about two seconds;
+// set a short limit first.
+PB_EXPORT int pb_gemm_tcgen05_wait_selftest(cudaStream_t stream) {
+    wait_selftest_kernel<<<1, 32, 0, stream>>>();
+    return launch_status();
+}
+
 // mode 0: out[M, N] = x W^T (out_dtype bfloat16 or float32).  mode 1: W = [gate rows; up rows], N = 2 * inter,
 // out[M, inter] = silu(x Wg^T) * (x Wu^T) in bfloat16.  x [M, K] and W [N, K] bfloat16, 16-byte aligned.
 PB_EXPORT int pb_gemm_tcgen05(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K,

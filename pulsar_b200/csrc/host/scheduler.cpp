@@ -56,8 +56,12 @@ int Scheduler::extend_request(int64_t rid, const int* tokens, int n, int max_new
     if (it == seqs_.end()) return kUnknownRequest;
     if (is_running(rid)) return kStillRunning;
     Sequence& s = it->second;
+    if (n < 0) return kBadArgument;
     if (pages((int)s.tokens.size() + n + std::max(0, max_new_tokens)) > capacity_pages()) return kNeverFits;
     if (s.unread) return kHasUnread;
+    // Nothing new and nothing left over to run (every token is cached already, as after a pass that ran one step
+    // ahead and cached a stop token): a step could not bring a single token, so the request is not queued.
+    if (n == 0 && (int)s.tokens.size() - s.n_cached <= 0) return kBadArgument;
     s.tokens.insert(s.tokens.end(), tokens, tokens + n);
     s.max_new_tokens = max_new_tokens;
     s.n_generated = 0;
@@ -204,6 +208,7 @@ int Scheduler::plan_once(bool allow_preempt, std::vector<PlanEntry>* out_ptr) {
         running_.push_back(rid);
         s.admitted_at = admissions_++;
         const int n = std::min(s.pending(), budget);
+        if (n <= 0) continue;                      // admitted with nothing to run (never queued so by extend_request)
         out.push_back(PlanEntry{rid, s.n_cached, n, n == s.pending()});
         planned_pages += pages_for(rid, n);
         budget -= n;

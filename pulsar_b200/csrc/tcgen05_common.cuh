@@ -9,7 +9,9 @@
 
 namespace pb {
 
-constexpr long long kWaitLimit = 4000000000LL;   // clock cycles (about two seconds)
+// The limit of every bounded wait, in clock cycles (about two seconds at first).  One copy per translation unit;
+// the host changes it with set_wait_limit (tests make a wait run out with a limit of a millisecond).
+static __device__ long long g_wait_limit = 4000000000LL;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -32,11 +34,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;                 // the usual case costs no clock read
     const long long t0 = clock64();
+    const long long limit = *(volatile long long*)&g_wait_limit;
     while (!mbar_try_wait(bar, parity)) {
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitLimit) return false;
+        if (clock64() - t0 > limit) return false;
     }
     return true;
+}
+
+// Host side of the bounded waits of one translation unit: a new limit (> 0), a new value of the error word
+// (>= 0; tests and recovery write it), and the word's device address, so that a caller can read it in the
+// stream, beside its results, without a synchronisation of its own.
+inline int wait_control(unsigned int& error_word, long long limit, int error, void** address) {
+    if (limit > 0 && cudaMemcpyToSymbol(g_wait_limit, &limit, sizeof(limit)) != cudaSuccess) return -1;
+    if (error >= 0) {
+        const unsigned int v = (unsigned int)error;
+        if (cudaMemcpyToSymbol(error_word, &v, sizeof(v)) != cudaSuccess) return -1;
+    }
+    if (address != nullptr && cudaGetSymbolAddress(address, error_word) != cudaSuccess) return -1;
+    return 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {

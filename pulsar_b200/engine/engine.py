@@ -13,6 +13,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager
 from ..config.engine_config import EngineConfig
 from ..sampling.sampler import GenerationParams, Sampler, make_generator
@@ -29,6 +30,13 @@ class _Session:
     budget: int                   # new tokens allowed in the current turn
     state: str = "idle"           # "idle", "active", "parked"
     scheduled: bool = False       # known to the scheduler
+    ended_on_stop: bool = False   # the last turn ended with the stop token
+
+
+class EngineFailed(RuntimeError):
+    """The engine met a failure it cannot step past (a kernel gave up a bounded wait, so what the device computed
+    is not to be trusted) and refuses further work; ``__cause__`` is the failure.  The reference's Python layer
+    poisons its engine the same way (pulsar/src/pulsar/rt/sync.py:21-34; rt/streaming.py:9-18)."""
 
 
 @dataclass
@@ -39,6 +47,7 @@ class _Inflight:
     host: torch.Tensor                     # pinned; filled when ``event`` has passed
     event: torch.cuda.Event
     generator_states: Dict[int, torch.Tensor]      # of stochastic sequences, before their draw
+    status: Optional[torch.Tensor] = None          # pinned; the kernels' wait error words behind this pass
     void: set = field(default_factory=set)         # sequences that had ended before this pass: its token is dropped
 
 
@@ -95,7 +104,10 @@ class Engine:
         self._inflight: Optional[_Inflight] = None          # the pass whose tokens have not been read yet
         self._unclaimed: List[Tuple[int, int, bool]] = []   # events booked outside ``step``
         self._host_ids: List[Optional[torch.Tensor]] = [None, None, None]
+        self._host_status = [torch.zeros(4, dtype=torch.int32, pin_memory=True) for _ in self._host_ids]
+        self._status_dev = torch.zeros(4, dtype=torch.int32, device=cfg.device)
         self._host_next = 0
+        self._failed: Optional[BaseException] = None
 
     # ------------------------------------------------------------------ sessions
     def _params(self, overrides: Optional[Dict[str, Any]]) -> GenerationParams:
@@ -108,8 +120,13 @@ class Engine:
         p.validate()
         return p
 
+    def _alive(self) -> None:
+        if self._failed is not None:
+            raise EngineFailed(f"the engine failed earlier and refuses further work: {self._failed}") from self._failed
+
     def create_session(self, tokens: Sequence[int] = (), overrides: Optional[Dict[str, Any]] = None) -> int:
         """A new sequence with its first tokens (they are not scheduled before ``feed``)."""
+        self._alive()
         if len(self._sessions) >= self.config.max_sessions:
             raise RuntimeError(f"max_sessions ({self.config.max_sessions}) reached")
         params = self._params(overrides)
@@ -162,6 +179,7 @@ class Engine:
     def feed(self, seq_id: int, tokens: Sequence[int], max_tokens: Optional[int] = None) -> None:
         """Add tokens to the sequence and schedule it; it will emit up to ``max_tokens``
         new tokens (default: the budget set before, else unlimited until eos)."""
+        self._alive()
         s = self._session(seq_id)
         self._drain()                   # a pass in flight may still owe this sequence a token
         if s.state == "active":
@@ -176,6 +194,10 @@ class Engine:
             if not (0 <= t < self.model.spec.vocab_size):
                 raise ValueError(f"token id {t} outside the vocabulary [0, {self.model.spec.vocab_size})")
         cap = budget if budget < (1 << 30) else 0
+        if s.scheduled and not new and s.ended_on_stop:
+            # Stepping one pass ahead has cached the stop token by now, stepping one pass at a time has not: a
+            # turn without tokens would run nothing in the one mode and the stop token in the other.  Refused in both.
+            raise ValueError(f"sequence {seq_id} ended on the stop token: a further turn needs at least one token")
         if s.scheduled:
             self.scheduler.extend_request(seq_id, new, cap if cap else self._room_left(seq_id, len(new)))
         else:
@@ -185,6 +207,7 @@ class Engine:
             s.scheduled = True
         s.pending = []
         s.state = "active"
+        s.ended_on_stop = False
 
     def _room_left(self, seq_id, n_new: int) -> int:
         """Largest decode budget the pool allows (used when only eos stops a sequence)."""
@@ -230,19 +253,30 @@ class Engine:
         slot = self._host_ids[self._host_next]
         if slot is None or slot.numel() < len(sampled):
             slot = self._host_ids[self._host_next] = torch.empty(max(64, len(sampled)), dtype=torch.int32, pin_memory=True)
+        status = self._host_status[self._host_next]
         self._host_next = (self._host_next + 1) % len(self._host_ids)
         host = slot[:len(sampled)]
         if sampled:
             host.copy_(ids, non_blocking=True)
+        # the error words of the kernels with bounded waits travel with the ids: no synchronisation of their own
+        ops.gather_wait_words(self._status_dev)
+        status.copy_(self._status_dev, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         for r in sampled:
             self.scheduler.on_sampled(r)
-        return _Inflight(sampled, {r: i for i, r in enumerate(sampled)}, host, event, states)
+        return _Inflight(sampled, {r: i for i, r in enumerate(sampled)}, host, event, states, status)
 
     def _collect(self, flight: "_Inflight") -> List[Tuple[int, int, bool]]:
         """Wait for a pass's sampled ids and book them: events ``(seq_id, token, finished)``."""
         flight.event.synchronize()
+        if flight.status is not None:
+            what = ops.describe_wait_words(flight.status[:3].tolist())
+            if what is not None:
+                # the pass's tokens come from a kernel that gave up: none of them is booked, and nothing runs after it
+                self._failed = ops.DeviceWaitError(what)
+                self._inflight = None
+                raise EngineFailed(f"a forward pass did not complete: {what}") from self._failed
         events = []
         for rid, tok in zip(flight.sampled, flight.host.tolist()):
             if rid not in self.scheduler.seqs:
@@ -257,6 +291,7 @@ class Engine:
             if finished:
                 self.scheduler.park(rid)            # pages stay until release (engine.cpp:770-788)
                 self._sessions[rid].state = "parked"
+                self._sessions[rid].ended_on_stop = self.eos_id >= 0 and int(tok) == self.eos_id
                 nxt = self._inflight
                 if nxt is not None and nxt is not flight and rid in nxt.row_of:
                     nxt.void.add(rid)
@@ -272,6 +307,7 @@ class Engine:
     def step_once(self) -> List[Tuple[int, int, bool]]:
         """One forward pass.  Returns the events ``(seq_id, token, finished)`` of the
         sequences whose logits were sampled in it."""
+        self._alive()
         self._drain()
         if self._unclaimed:
             events, self._unclaimed = self._unclaimed, []
@@ -291,6 +327,7 @@ class Engine:
         not idle while the host books tokens and decides the next step; one pass may then
         still be in flight when the call returns, and the next call picks it up.  A sequence
         that ends on a stop token has by then run one token too far; that token is discarded."""
+        self._alive()
         events: List[Tuple[int, int, bool]] = self._unclaimed
         self._unclaimed = []
         while len(events) < n:

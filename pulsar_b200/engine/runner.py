@@ -14,6 +14,7 @@ from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import ctypes
+import gc
 
 import torch
 
@@ -252,11 +253,18 @@ class ModelRunner:
         torch.cuda.synchronize(self.device)
         launches = ops.LAUNCHES
         self._capturing = True
+        # No garbage collection while the stream captures: an object that is collected then (an engine of an earlier
+        # test, say) frees pinned memory, events or graphs of its own, and some of those calls are not allowed
+        # during a capture and spoil it.
+        collecting = gc.isenabled()
+        gc.disable()
         try:
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx)
         finally:
             self._capturing = False
+            if collecting:
+                gc.enable()
         launches = ops.LAUNCHES - launches            # kernels of this library inside the captured step
         if self.scratch_epoch != epoch:                   # grew during capture: do not keep it
             self._graph_epoch = -1

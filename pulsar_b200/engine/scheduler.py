@@ -206,6 +206,8 @@ class Scheduler:
             raise SchedulerError(f"request {rid!r} would outgrow the pool")
         if rc == _HAS_UNREAD:
             raise SchedulerError(f"request {rid!r} still has a sampled token that was not read")
+        if rc == host.BAD_ARGUMENT:
+            raise SchedulerError(f"request {rid!r}: a further turn needs at least one token to run")
         if rc < 0:
             raise SchedulerError(f"request {rid!r}: the host runtime answered {rc}")
 

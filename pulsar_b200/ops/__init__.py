@@ -58,6 +58,10 @@ _SIGNATURES = {
     "pb_gemm_tcgen05": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_gemm_tcgen05_supported": [_I, _I, _I, _I],
     "pb_gemm_tcgen05_error": [],
+    "pb_gemm_tcgen05_wait_control": [ctypes.c_longlong, _I, _P],
+    "pb_gemm_tcgen05_wait_selftest": [_P],
+    "pb_prefill_tcgen05_wait_control": [ctypes.c_longlong, _I, _P],
+    "pb_gather_words": [_P, _I, _P, _P],
     "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P],
     "pb_sample_workspace": [_I],
@@ -283,6 +287,81 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bo
 def gemm_tcgen05_error() -> int:
     """0 unless a block of the tcgen05 product ever gave up a bounded wait (synchronises)."""
     return int(fn("pb_gemm_tcgen05_error")())
+
+
+# ---------------------------------------------------------------- bounded waits: limit and error words
+# The kernels that wait on barriers (the tcgen05 product, the two tcgen05 attention kernels) bound every wait by
+# a clock limit; a block whose wait runs out sets its kernel's error word, lets its copies land, frees its tensor
+# memory and returns, and what the kernel wrote is then not to be trusted.  The reference's engine turns a step
+# that cannot go on into an exception (pulsar-core/src/runtime/engine.cpp:809-814) and its Python layer
+# poisons the engine (pulsar/src/pulsar/rt/sync.py:21-34); the words below are how this engine learns of it.
+WAIT_WORD_NAMES = ("tcgen05 product", "tcgen05 attention, one head per block", "tcgen05 attention, two heads per block")
+WAIT_ROLES = {2: "the TMA producer", 3: "the MMA issuer", 4: "the epilogue or softmax warps", 9: "the wait self-test"}
+_wait_words = {}
+
+
+class DeviceWaitError(KernelError):
+    """A kernel gave up a bounded wait: its output, and everything computed from it, is not valid."""
+
+
+def wait_word_addresses() -> "ctypes.Array":
+    """Device addresses of the three error words of the current device (looked up once per device)."""
+    dev = torch.cuda.current_device()
+    got = _wait_words.get(dev)
+    if got is None:
+        got = (ctypes.c_void_p * 3)()
+        one = (ctypes.c_void_p * 1)()
+        two = (ctypes.c_void_p * 2)()
+        if fn("pb_gemm_tcgen05_wait_control")(0, -1, one) != 0 or fn("pb_prefill_tcgen05_wait_control")(0, -1, two) != 0:
+            raise KernelError("the addresses of the wait error words could not be had")
+        got[0], got[1], got[2] = one[0], two[0], two[1]
+        _wait_words[dev] = got
+    return got
+
+
+def gather_wait_words(out: torch.Tensor) -> None:
+    """out[:3] (int32, device) = the three error words, read in the stream behind whatever was launched before."""
+    _cuda(out)
+    assert out.dtype == torch.int32 and out.numel() >= 3
+    check(fn("pb_gather_words")(wait_word_addresses(), 3, _p(out), stream()), "gather_words")
+
+
+def set_wait_limit(cycles: int) -> None:
+    """The limit of every bounded wait, in clock cycles (4e9 at first, about two seconds)."""
+    if cycles <= 0:
+        raise ValueError("the wait limit must be positive")
+    if fn("pb_gemm_tcgen05_wait_control")(int(cycles), -1, None) != 0 or \
+            fn("pb_prefill_tcgen05_wait_control")(int(cycles), -1, None) != 0:
+        raise KernelError("the wait limit could not be set")
+
+
+def set_wait_words(value: int) -> None:
+    """Write all three error words (0 clears them once a failure has been dealt with)."""
+    if fn("pb_gemm_tcgen05_wait_control")(0, int(value), None) != 0 or \
+            fn("pb_prefill_tcgen05_wait_control")(0, int(value), None) != 0:
+        raise KernelError("the wait error words could not be written")
+
+
+def wait_selftest() -> None:
+    """One thread waits on a barrier nobody arrives on until the limit runs out and sets the product's error word to 9."""
+    check(fn("pb_gemm_tcgen05_wait_selftest")(stream()), "wait_selftest")
+
+
+def describe_wait_words(words) -> Optional[str]:
+    """None when all words are 0, else which kernel gave up and in which role."""
+    bad = [(WAIT_WORD_NAMES[i], int(w)) for i, w in enumerate(words) if int(w) != 0]
+    if not bad:
+        return None
+    return "; ".join(f"{name}: {WAIT_ROLES.get(w, 'role ' + str(w))} gave up a bounded wait" for name, w in bad)
+
+
+def check_wait_words() -> None:
+    """Read the three words now (synchronises) and raise DeviceWaitError if one is set."""
+    words = (gemm_tcgen05_error(), prefill_tcgen05_error())
+    if any(words):
+        buf = torch.zeros(4, dtype=torch.int32, device="cuda")
+        gather_wait_words(buf)
+        raise DeviceWaitError(describe_wait_words(buf[:3].tolist()))
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

@@ -5,6 +5,7 @@ from typing import Optional
 
 import torch
 
+from . import ops
 from .cache.manager import CacheManager
 from .engine.loading import load_model
 from .engine.runner import ModelRunner, StepEntry
@@ -36,6 +37,7 @@ class Replay:
                 out = logits.cpu()
             else:
                 torch.cuda.current_stream().synchronize()
+            ops.check_wait_words()          # a kernel that gave up a bounded wait must not pass for a result
         for rid in record.get("end", []):
             if self.cache.has(rid):
                 self.runner.finish(rid)

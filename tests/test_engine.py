@@ -223,6 +223,96 @@ def _drive(eng, prompts, budgets, lookahead, overrides=None, second_turn=None):
     return [seen[sid] for sid in sids]
 
 
+def test_a_turn_without_tokens_after_the_stop_token_is_refused_in_both_stepping_modes(folders):
+    """Stepping one pass ahead has cached the stop token when the turn ends, stepping one pass at a time has not.
+    A further turn without a token is refused in both (nothing is queued, the engine goes on working); a further
+    turn with a token gives the same tokens in both; a turn that a budget ended may go on without a token."""
+    raw, seed, page = TINY["B"]
+    rng = random.Random(4)
+    prompt = helpers.random_tokens(rng, 21, raw["vocab_size"])
+    free = _drive(_engine(folders["B"], "float32", page), [prompt], [12], lookahead=False)[0]
+    eos = free[5][0]
+    first_stop = [t for t, _ in free].index(eos)
+    runs = []
+    for lookahead in (False, True):
+        eng = _engine(folders["B"], "float32", page, eos_id=eos)
+        sid = eng.create_session(prompt)
+        eng.feed(sid, [], 12)
+        seen = []
+        while eng.has_work():
+            seen += eng.step(1) if lookahead else eng.step_once()
+        assert [t for _, t, _ in seen] == [t for t, _ in free[:first_stop + 1]] and seen[-1][2]
+        with pytest.raises(ValueError, match="stop token"):
+            eng.feed(sid, [])
+        assert not eng.has_work() and eng.session_state(sid) == "parked"
+        eng.feed(sid, [5], 4)
+        more = []
+        while eng.has_work():
+            more += eng.step(1) if lookahead else eng.step_once()
+        # that turn ended on its budget (or on the stop token): without the stop token it may go on without a token
+        if more[-1][1] != eos:
+            eng.feed(sid, [], 3)
+            while eng.has_work():
+                more += eng.step(1) if lookahead else eng.step_once()
+        runs.append([(t, f) for _, t, f in more])
+        eng.cache.check_consistency()
+        eng.release(sid)
+    assert runs[0] == runs[1] and len(runs[0]) >= 2
+
+
+def test_a_wait_that_runs_out_sets_its_error_word():
+    """The give-up path of the kernels with bounded waits, alone: one thread waits on a barrier that nobody arrives on,
+    with the limit set to a millisecond; the kernel returns, the error word says so, the context stays usable."""
+    from pulsar_b200 import ops
+    assert ops.gemm_tcgen05_error() == 0
+    try:
+        ops.set_wait_limit(2_000_000)
+        ops.wait_selftest()
+        torch.cuda.synchronize()
+        assert ops.gemm_tcgen05_error() == 9
+        words = torch.zeros(4, dtype=torch.int32, device="cuda")
+        ops.gather_wait_words(words)
+        assert words.tolist()[:3] == [9, 0, 0]
+        assert "wait self-test" in ops.describe_wait_words(words.tolist()[:3])
+        with pytest.raises(ops.DeviceWaitError):
+            ops.check_wait_words()
+    finally:
+        ops.set_wait_limit(4_000_000_000)
+        ops.set_wait_words(0)
+    assert ops.gemm_tcgen05_error() == 0 and ops.prefill_tcgen05_error() == 0
+    a = torch.randn(64, 64, device="cuda")
+    assert torch.isfinite(a @ a).all()                  # the context still works
+
+
+@pytest.mark.parametrize("lookahead", [False, True])
+def test_an_error_word_behind_a_pass_becomes_an_exception_and_the_engine_refuses_further_work(folders, lookahead):
+    """A kernel that gave up a bounded wait leaves its error word set; the engine reads the words with the pass's
+    sampled ids, books none of its tokens, raises, and refuses everything after it."""
+    from pulsar_b200 import ops
+    from pulsar_b200.engine.engine import EngineFailed
+    raw, seed, page = TINY["A"]
+    eng = _engine(folders["A"], "bfloat16", page)
+    sid = eng.create_session(helpers.random_tokens(random.Random(1), 9, raw["vocab_size"]))
+    eng.feed(sid, [], 20)
+    got = eng.step(2, lookahead=lookahead)
+    assert len(got) >= 2
+    try:
+        ops.set_wait_words(3)               # as if the MMA issuer of a block had given up
+        with pytest.raises(EngineFailed, match="MMA issuer") as info:
+            for _ in range(3):
+                eng.step(1, lookahead=lookahead)
+        assert isinstance(info.value.__cause__, ops.DeviceWaitError)
+    finally:
+        ops.set_wait_words(0)
+    for call in (lambda: eng.step(1), lambda: eng.step_once(), lambda: eng.feed(sid, [1]), lambda: eng.create_session([1])):
+        with pytest.raises(EngineFailed, match="refuses further work"):
+            call()
+    eng.release(sid)                            # giving pages back still works
+    assert eng.cache.live_requests() == []
+    eng2 = _engine(folders["A"], "bfloat16", page)          # and a new engine on the same device runs
+    assert len(eng2.generate([[1, 2, 3]], 4)[0]) == 4
+
+
 @pytest.mark.parametrize("lookahead", [False, True])
 @pytest.mark.parametrize("name", ["D", "E"])
 def test_bfloat16_tokens_of_the_schedulers_own_mixed_steps_follow_the_plain_logits(folders, name, lookahead):
