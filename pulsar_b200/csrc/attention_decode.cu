@@ -205,7 +205,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ partial, T* __re
         if (threadIdx.x == 0) l_s = l_part;
     }
     __syncthreads();
-    const float inv = 1.0f / l_s;
+    const float inv = l_s > 0.0f ? 1.0f / l_s : 0.0f;     // a sequence without keys (kv_len 0): zeros, not 0 * inf
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float o = 0.0f;
         for (int i = 0; i < n_splits; i += 8) {          // eight loads in flight, added in split order

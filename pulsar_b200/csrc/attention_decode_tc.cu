@@ -230,7 +230,7 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
             l_all += l_s[w * 16 + h] * f;
         }
         if (direct) {
-            out[((size_t)s * Hq + (size_t)kvh * G + h) * D + d] = __float2bfloat16_rn(acc / l_all);
+            out[((size_t)s * Hq + (size_t)kvh * G + h) * D + d] = __float2bfloat16_rn(l_all > 0.0f ? acc / l_all : 0.0f);
         } else {
             float* dst = partial + (((size_t)s * Hq + (size_t)kvh * G + h) * n_splits + split) * stride;
             __stcg(dst + d, acc);
@@ -268,7 +268,7 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
         const float* hb = base + (size_t)h * n_splits * stride;
         float acc = 0.0f;
         for (int sp = 0; sp < n_splits; ++sp) acc = fmaf(__ldcg(hb + sp * stride + d), w_s[h * n_splits + sp], acc);
-        out[((size_t)s * Hq + (size_t)kvh * G + h) * D + d] = __float2bfloat16_rn(acc / lsum_s[h]);
+        out[((size_t)s * Hq + (size_t)kvh * G + h) * D + d] = __float2bfloat16_rn(lsum_s[h] > 0.0f ? acc / lsum_s[h] : 0.0f);
     }
 }
 

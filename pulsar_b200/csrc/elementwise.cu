@@ -142,27 +142,24 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
 }
 
 // ---------------------------------------------------------------- rotary tables
-// cos/sin [N, half] of angle = position * quadrants_per_position[j] * pi/2.  The
-// product is formed in float64 and whole quadrants are removed there (exact), so only
-// a remainder below half a quadrant is rounded to float32 before sincosf.
+// cos/sin [N, half] of angle = position * quadrants_per_position[j] * pi/2.  The angle is kept in
+// half-turns (angle / pi) in float64; whole turns are taken off there, which is exact, and what is
+// left is folded into [-1/2, 1/2] half-turns (sin(pi r) = sin(pi (sign(r) - r)), the cosine changes
+// sign; exact too).  Only that remainder is rounded to float32, and sincospif takes it from there,
+// so the rounding of the argument never grows with the position.  (The reference reduces by whole
+// quadrants and picks among four cases: pulsar-core/src/kernels/rope_common.cuh:19-43.)
 __global__ void rope_table_kernel(const int* __restrict__ positions, const double* __restrict__ quadrants_per_position,
                                   float* __restrict__ cos_out, float* __restrict__ sin_out, int half) {
     const int t = blockIdx.x;
     const double p = (double)positions[t];
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
-        const double quadrants = p * quadrants_per_position[j];
-        const double whole = nearbyint(quadrants);
-        const float reduced = (float)(quadrants - whole) * 1.57079632679489662f;
-        float s, c;
-        sincosf(reduced, &s, &c);
-        float co, si;
-        switch ((int)((long long)whole) & 3) {
-            case 0: co = c; si = s; break;
-            case 1: co = -s; si = c; break;
-            case 2: co = -c; si = -s; break;
-            default: co = s; si = -c; break;
-        }
-        cos_out[(size_t)t * half + j] = co;
+        const double half_turns = p * quadrants_per_position[j] * 0.5;
+        double r = half_turns - 2.0 * rint(half_turns * 0.5);          // in [-1, 1]
+        const bool folded = fabs(r) > 0.5;
+        if (folded) r = copysign(1.0, r) - r;
+        float si, co;
+        sincospif((float)r, &si, &co);
+        cos_out[(size_t)t * half + j] = folded ? -co : co;
         sin_out[(size_t)t * half + j] = si;
     }
 }

@@ -1,7 +1,7 @@
 // Host-side accounting of the paged cache: page pools with LIFO free lists, one block table per
 // request and group of layers, early release behind attention windows, state slots.  Plain C++
 // (no CUDA): the device only ever sees the block tables and slot indices that the step packer
-// (step_packer.cpp) writes into a pinned buffer.
+// (ph_step_pack in api.cpp) writes into a pinned buffer.
 //
 // What the reference's ActiveBuffer does for its one kind of layer
 // (pulsar-core/src/runtime/kv/active_buffer.cpp:32-82 pools and free list, :152-228

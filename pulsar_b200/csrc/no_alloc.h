@@ -22,8 +22,8 @@
 // Arguments are those of pb_paged_attention_decode without `partial`:
 //   dtype 0 float32 / 1 bfloat16; q, out [n_seqs, Hq, D]; pools [pages, Hkv, page_size, D];
 //   block_table int32 [n_seqs, table_stride]; kv_len int32 [n_seqs] (context lengths
-//   including the query token); window 0 = all keys.  Returns 0, a negative refusal, or
-//   a cudaError_t.
+//   including the query token; a sequence with kv_len 0 gets zeros); window 0 = all keys.
+//   Returns 0, a negative refusal, or a cudaError_t.
 #pragma once
 
 #include <cuda_runtime.h>

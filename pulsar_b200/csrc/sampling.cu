@@ -20,6 +20,8 @@
 // slice, whose last block per row draws the token.
 #include "common.cuh"
 
+#include <climits>
+
 namespace {
 
 using namespace pb;
@@ -69,7 +71,8 @@ struct SampleWork {                               // device scratch of one call
     float2* part;                                 // [rows][slices]: maximum and sum of exp((x - maximum) / T) of a slice
     unsigned int* cnt;                            // [levels][rows][bins]
     unsigned long long* mass;                     // [levels][rows][bins]
-    float* slice_mass;                            // [rows][slices]: surviving mass of a slice
+    float* slice_mass;                            // [rows][slices]: mass of a slice above the threshold
+    int* slice_ties;                              // [rows][slices]: tokens of a slice at the threshold
     unsigned int* tickets;                        // [rows]
 };
 
@@ -242,13 +245,18 @@ sample_draw_kernel(const float* __restrict__ logits, int rows, int vocab, const 
     __shared__ unsigned int s_cnt[kSampleThreads];
     __shared__ unsigned long long s_mass[kSampleThreads];
     __shared__ float scan_s[kSampleThreads];
-    __shared__ int s_pick;
+    __shared__ int s_pick, s_ties;
     __shared__ bool s_last;
     __shared__ Best best_s[32];
     const int r = blockIdx.y, slices = gridDim.x;
     if (!(temperature[r] > 0.0f)) return;
     const RowParams p = row_params(r, w.part, slices, vocab, temperature, top_k, top_p);
+    // threshold: the smallest surviving probability.  allow: how many of the tokens whose probability EQUALS it
+    // survive, the first ones in index order: a sort keeps exactly k tokens and the nucleus rule looks at the mass
+    // strictly before each token (pulsar-core/src/runtime/sampler.cpp:30-40), so equal probabilities at the cut are
+    // not all in or all out.
     float threshold = 0.0f;
+    int allow = INT_MAX;
     if (p.use_k || p.use_p) {
         unsigned int carried_cnt = 0, bits = 0;
         unsigned long long carried_mass = 0;
@@ -257,37 +265,65 @@ sample_draw_kernel(const float* __restrict__ logits, int rows, int vocab, const 
             bits = (bits << 10) | (unsigned int)pick_bin(w.cnt + at, w.mass + at, p, carried_cnt, carried_mass, s_cnt, s_mass, &s_pick);
         }
         threshold = __uint_as_float(bits);
+        // carried_*: count and mass of what lies strictly above the threshold (fewer than k, mass <= top_p)
+        if (p.use_k) allow = p.k - (int)carried_cnt;
+        if (p.use_p) {
+            const unsigned long long each = (unsigned long long)(threshold * kMassScale);
+            const unsigned long long room = p.tp_q >= carried_mass ? p.tp_q - carried_mass : 0;
+            const unsigned long long by_mass = each > 0 ? room / each + 1 : (unsigned long long)INT_MAX;
+            if (by_mass < (unsigned long long)allow) allow = (int)by_mass;
+        }
+        if (allow < 1) allow = 1;
     }
     const float* row = logits + (size_t)r * vocab;
-    // thread t owns a contiguous range of the slice's indices
-    auto scan_slice = [&](int slice, float target, float before_slice) -> int {
+    // thread t owns a contiguous range of the slice's indices.  ``ties_before``: tokens at the threshold in the
+    // slices before this one.  With target < 0 only the slice's mass above the threshold (s_mass[0]) and its
+    // number of tokens at the threshold (s_ties) are wanted.
+    auto scan_slice = [&](int slice, float target, float before_slice, int ties_before) -> int {
         int begin, end;
         slice_range(vocab, slices, slice, begin, end);
         const int per = (end - begin + kSampleThreads - 1) / kSampleThreads;
         const int b0 = min(end, begin + (int)threadIdx.x * per), e0 = min(end, b0 + per);
         float mine = 0.0f;
+        int my_ties = 0;
         for (int i = b0; i < e0; ++i) {
             const float q = prob(row[i], p);
-            if (q >= threshold) mine += q;
+            if (q > threshold) mine += q;
+            else if (q == threshold) ++my_ties;
         }
         __syncthreads();
         scan_s[threadIdx.x] = mine;
+        s_cnt[threadIdx.x] = (unsigned int)my_ties;
         __syncthreads();
         if (threadIdx.x == 0) {      // serial prefix over the partials: fixed order, negligible time
             float run = before_slice;
-            for (int t = 0; t < kSampleThreads; ++t) { const float v = scan_s[t]; scan_s[t] = run; run += v; }
+            int ties = ties_before;
+            const bool count_ties = target >= 0.0f;
+            for (int t = 0; t < kSampleThreads; ++t) {
+                const int n = (int)s_cnt[t];
+                const int in = count_ties ? max(0, min(n, allow - min(ties, allow))) : 0;
+                const float v = scan_s[t] + (float)in * threshold;
+                scan_s[t] = run;
+                s_cnt[t] = (unsigned int)ties;             // ties before thread t's range
+                run += v;
+                ties += n;
+            }
             s_mass[0] = (unsigned long long)__float_as_uint(run);
+            s_ties = ties - ties_before;
             s_pick = -1;
         }
         __syncthreads();
-        if (target < 0.0f) return -1;                 // only the slice's mass was wanted
+        if (target < 0.0f) return -1;
         const float before = scan_s[threadIdx.x];
-        if (mine > 0.0f && target >= before && target < before + mine) {
+        int ties = (int)s_cnt[threadIdx.x];
+        const float my_mass = mine + (float)max(0, min(my_ties, allow - min(ties, allow))) * threshold;
+        if (my_mass > 0.0f && target >= before && target < before + my_mass) {
             float run = before;
             int chosen = -1, last = -1;
             for (int i = b0; i < e0; ++i) {
                 const float q = prob(row[i], p);
-                if (q >= threshold) {
+                const bool in = q > threshold || (q == threshold && ties++ < allow);
+                if (in) {
                     last = i;
                     run += q;
                     if (target < run) { chosen = i; break; }
@@ -298,9 +334,10 @@ sample_draw_kernel(const float* __restrict__ logits, int rows, int vocab, const 
         __syncthreads();
         return s_pick;
     };
-    scan_slice(blockIdx.x, -1.0f, 0.0f);
+    scan_slice(blockIdx.x, -1.0f, 0.0f, 0);
     if (threadIdx.x == 0) {
         w.slice_mass[(size_t)r * slices + blockIdx.x] = __uint_as_float((unsigned int)s_mass[0]);
+        w.slice_ties[(size_t)r * slices + blockIdx.x] = s_ties;
         __threadfence();
         s_last = atomicAdd(w.tickets + r, 1u) == (unsigned int)slices - 1;
     }
@@ -308,17 +345,28 @@ sample_draw_kernel(const float* __restrict__ logits, int rows, int vocab, const 
     if (!s_last) return;
     __threadfence();
     // the row's last block: which slice holds the target, then which token
+    auto slice_total = [&](int s, int ties_before) -> float {
+        const float above = *reinterpret_cast<volatile float*>(w.slice_mass + (size_t)r * slices + s);
+        const int n = *reinterpret_cast<volatile int*>(w.slice_ties + (size_t)r * slices + s);
+        return above + (float)max(0, min(n, allow - min(ties_before, allow))) * threshold;
+    };
     float total = 0.0f;
-    for (int s = 0; s < slices; ++s) total += *reinterpret_cast<volatile float*>(w.slice_mass + (size_t)r * slices + s);
+    int ties = 0;
+    for (int s = 0; s < slices; ++s) {
+        total += slice_total(s, ties);
+        ties += *reinterpret_cast<volatile int*>(w.slice_ties + (size_t)r * slices + s);
+    }
     const float target = uniform[r] * total;
     float before = 0.0f;
     int slice = -1;
+    ties = 0;
     for (int s = 0; s < slices; ++s) {
-        const float v = *reinterpret_cast<volatile float*>(w.slice_mass + (size_t)r * slices + s);
+        const float v = slice_total(s, ties);
         if (v > 0.0f && target < before + v) { slice = s; break; }
         before += v;
+        ties += *reinterpret_cast<volatile int*>(w.slice_ties + (size_t)r * slices + s);
     }
-    int pick = slice >= 0 ? scan_slice(slice, target, before) : -1;
+    int pick = slice >= 0 ? scan_slice(slice, target, before, ties) : -1;
     if (pick < 0) pick = block_argmax(row, vocab, best_s);      // rounding left the target past the last survivor
     if (threadIdx.x == 0) {
         out[r] = pick;
@@ -389,7 +437,7 @@ PB_EXPORT int pb_sample_workspace(int rows) {
     if (rows <= 0) return 0;
     const long long r = rows;
     const long long bytes = r * kMaxSlices * sizeof(float2) + (long long)kLevels * r * kBins * (sizeof(unsigned int) + sizeof(unsigned long long)) +
-                            r * kMaxSlices * sizeof(float) + r * sizeof(unsigned int) + 256;
+                            r * kMaxSlices * (sizeof(float) + sizeof(int)) + r * sizeof(unsigned int) + 256;
     return (int)((bytes + 1023) / 1024);
 }
 
@@ -421,6 +469,8 @@ PB_EXPORT int pb_sample(const float* logits, int rows, int vocab, const float* t
     w.part = reinterpret_cast<float2*>(at);
     at += (size_t)rows * kMaxSlices * sizeof(float2);
     w.slice_mass = reinterpret_cast<float*>(at);
+    at += (size_t)rows * kMaxSlices * sizeof(float);
+    w.slice_ties = reinterpret_cast<int*>(at);
     cudaError_t rc = cudaMemsetAsync(workspace, 0, zeroed, stream);
     if (rc != cudaSuccess) return (int)rc;
     const dim3 grid(slices, rows);

@@ -30,6 +30,9 @@ F32, BF16 = 0, 1
 GEMM_BACKEND = os.environ.get("PULSAR_GEMM", "auto")
 # Attention of prompt portions in bfloat16: "auto" = the tcgen05 kernel where it applies, "mma" = never.
 ATTENTION_BACKEND = os.environ.get("PULSAR_ATTENTION", "auto")
+# The library product (torch.mm) must add its partial sums in float32: by default PyTorch lets cuBLAS reduce
+# split-K partial sums of bfloat16 products in bfloat16.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 _ERRORS = {-2: "unsupported dtype", -3: "unsupported size or argument", -4: "size exceeds the kernel's limit"}
 

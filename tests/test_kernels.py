@@ -375,6 +375,30 @@ def test_attention_decode_tensor_cores(hq, hkv, d, page, window, n_splits):
     assert torch.equal(outs[0], outs[3]), "second fused launch on the same tickets"
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_splits", [1, 3])
+def test_attention_decode_of_a_sequence_without_keys_gives_zeros(dtype, n_splits):
+    """The exported entry points take kv_len 0 (the engine never sends it): every split of such a sequence is empty,
+    and the merge must give zeros, not 0 * inf; its neighbours in the batch are untouched by it."""
+    from pulsar_b200 import ops
+    hq, hkv, d, page = 8, 2, 64, 16
+    g = torch.Generator().manual_seed(4)
+    lens_kv = [40, 1, 90]
+    case = _paged_case(g, [1, 1, 1], lens_kv, hq, hkv, d, page, dtype)
+    scale = 1.0 / math.sqrt(d)
+    ref = _attention_ref(case, [1, 1, 1], lens_kv, hq, hkv, scale, None)
+    kv = case["kv"].clone()
+    kv[1] = 0
+    variants = [(False, False)] + ([(True, True), (True, False)] if dtype == torch.bfloat16 else [])
+    for tc, fused in variants:
+        out = torch.full((3, hq, d), float("nan"), dtype=dtype, device="cuda")
+        partial = torch.full((3 * hq * n_splits * (d + 2),), float("nan"), dtype=torch.float32, device="cuda")
+        ops.paged_attention_decode(dev(case["q"]), dev(case["kp"]), dev(case["vp"]), out, partial, dev(case["table"]),
+                                   dev(kv), scale, None, n_splits, tensor_cores=tc, fused=fused)
+        assert float(out[1].float().abs().max()) == 0.0, (tc, fused)
+        close(out[[0, 2]], ref[[0, 2]], TOL[dtype], f"neighbours of the empty sequence, tensor cores {tc}, fused {fused}")
+
+
 @pytest.mark.parametrize("hq,hkv,d,page", TC_SHAPES)
 @pytest.mark.parametrize("window", [None, 37, 200])
 def test_attention_prefill_tensor_cores(hq, hkv, d, page, window):
@@ -648,6 +672,32 @@ def test_sample_large_vocabulary_many_blocks_per_row(vocab):
         ops.sample(dev(logits[r:r + 1]), one, dev(temp[r:r + 1]), dev(top_k[r:r + 1]), dev(top_p[r:r + 1]), dev(uniform[r:r + 1]),
                    any_greedy=False)
         assert int(one.cpu()) == got[r]
+
+
+@pytest.mark.parametrize("vocab", [40, 5000])
+def test_sample_keeps_exactly_k_when_probabilities_tie_at_the_cut(vocab):
+    """Equal logits at the cut (bfloat16 heads and tied embeddings make them): a sort keeps exactly k tokens and the
+    nucleus rule looks at the mass strictly before each token, so of the tied tokens only the first ones in index
+    order survive (pulsar-core/src/runtime/sampler.cpp:30-40; the plain implementation's stable sort)."""
+    from pulsar_b200 import ops
+    logits = torch.full((vocab,), -4.0)
+    tied = [3, 9, 17, 21, vocab - 2]                   # five tokens share the top probability, across slices of the row
+    logits[tied] = 2.0
+    logits[30] = 1.0
+    rows = 48
+    uniform = (torch.arange(rows, dtype=torch.float32) + 0.5) / rows
+    for top_k, top_p, want in ((2, 1.0, tied[:2]), (4, 1.0, tied[:4]), (6, 1.0, tied + [30]), (0, 0.35, None), (3, 0.35, None)):
+        out = torch.empty(rows, dtype=torch.int32, device="cuda")
+        ops.sample(dev(logits.repeat(rows, 1)), out, dev(torch.ones(rows)), dev(torch.full((rows,), top_k, dtype=torch.int32)),
+                   dev(torch.full((rows,), top_p)), dev(uniform))
+        _, si = _survivors(logits, 1.0, top_k, top_p)
+        keep = sorted(si.tolist())
+        if want is not None:
+            assert keep == sorted(want)
+        got = sorted(set(out.cpu().tolist()))
+        assert set(got) <= set(keep), (top_k, top_p, got, keep)        # nothing outside the surviving set is drawn
+        if len(keep) <= 8:
+            assert got == keep, (top_k, top_p, got, keep)              # and every survivor is reached by some uniform
 
 
 def test_sample_mixed_rows_and_greedy_ignores_filters():

@@ -7,7 +7,10 @@ at start-up, or the loop may not take the allocator's lock), so
 results in a fixed array inside the library.  This test calls it twice in a row, with
 different sizes, so that whatever the first call left in the shared array would show in
 the second, and compares both results with the entry point that takes the caller's
-scratch.  It also checks that a problem beyond the array's size is refused.
+scratch: the two run the same kernels on the same inputs and merge the splits in a fixed
+order, so the results must be equal bit for bit.  The device's free memory, as the driver
+reports it, must not move across the second call (the first may look up the array's address).
+It also checks that a problem beyond the array's size is refused.
 
 The file sorts last on purpose: a run that stops at the first failure has then already
 run every other test.
@@ -62,16 +65,18 @@ def test_no_alloc_entry_matches_existing_entry_twice_in_a_row(dtype):
         ops.paged_attention_decode(q, kp, vp, want, partial, table, lens, scale, window or None, n_splits,
                                    tensor_cores=False)     # the entry point this one is a variant of
         got = torch.full_like(q, float("nan"))
-        mem_before = torch.cuda.memory_allocated()
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]          # the driver's count: a cudaMalloc inside the library would show
         rc = lib.pb_paged_attention_decode_noalloc(code, q.data_ptr(), kp.data_ptr(), vp.data_ptr(), got.data_ptr(),
                                                    table.data_ptr(), table.shape[1], lens.data_ptr(), n_seqs, hq, hkv, d,
                                                    page, scale, window, n_splits, stream)
         assert rc == 0, f"status {rc}"
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == mem_before
-        tol = 2e-5 if dtype == torch.float32 else 1.6e-2        # the bars of tests/test_kernels.py
-        err = float((got.double() - want.double()).abs().max() / want.double().abs().max())
-        assert err < tol, f"call {seed}: relative error {err:.3e}"
+        if seed > 0:                                        # the first call on a device may look up the symbol's address
+            assert torch.cuda.mem_get_info()[0] == free_before
+        assert torch.isfinite(got.float()).all()
+        assert torch.equal(got, want), (f"call {seed}: the entry point and its variant with the caller's scratch differ by "
+                                        f"{float((got.double() - want.double()).abs().max()):.3e}")
 
 
 def test_no_alloc_entry_refuses_what_does_not_fit():
