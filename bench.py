@@ -108,7 +108,8 @@ def build_engine(shape: dict, n_layers: int, batch: int, context: int, max_chunk
                                                 max_sessions=batch, max_running=batch, max_chunk_size=max_chunk,
                                                 eos_id=-1, temperature=0.0))
     for g in engine.cache.groups:                 # random keys and values: attention is not degenerate
-        g.pool.normal_(0.0, 1.0)
+        for pool in g.pools.values():
+            pool.normal_(0.0, 1.0)
     return engine
 
 
@@ -124,10 +125,7 @@ def decode_bytes_of_shape(raw: dict, batch: int, context: float) -> float:
 
 def decode_bytes(engine, batch: int, context: int) -> float:
     model = engine.model
-    kv = 0
-    for need in engine.cache.needs:
-        if need.kind == "paged_kv":
-            kv += 2 * need.n_kv_heads * need.head_dim * engine.cache.dtype.itemsize
+    kv = sum(need.bytes_per_token(engine.cache.dtype) for need in engine.cache.needs if need.kind == "paged_kv")
     return float(model.weight_bytes(batch) + batch * context * kv)
 
 

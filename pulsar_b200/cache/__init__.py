@@ -1,1 +1,1 @@
-from .manager import CacheError, CacheManager, CacheNeed, OutOfPages, PageAllocator
+from .manager import CachedTensor, CacheError, CacheManager, CacheNeed, OutOfPages, PageAllocator

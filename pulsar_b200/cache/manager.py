@@ -13,9 +13,12 @@ the entries that declare such state (none do for Qwen3 dense, the slot exists an
 The accounting lives in the host runtime (C++, csrc/host/cache.cpp) and is tested without a GPU
 (``PageAllocator``, ``CacheManager`` with ``device=None``).
 
-Physical layout of a group's pool: ``[entries, 2 (k, v), pages, kv_heads, page_size,
-head_dim]``, so that one (page, kv head) tile of keys is contiguous
-(``page_size * head_dim`` elements) for bulk copies.
+A mixer declares the tensors it caches per token (``CachedTensor``: a name, heads, a width per
+head); keys and values of equal shape are the usual case, a mixer may as well cache keys and
+values of different widths, or one tensor only.  Every declared tensor has a pool of its own,
+``[entries, pages, heads, page_size, width]``, so that one (page, head) tile is contiguous
+(``page_size * width`` elements) for bulk copies; the tensors of a group share page ids and
+block tables.
 """
 from __future__ import annotations
 
@@ -37,18 +40,38 @@ class CacheError(RuntimeError):
 
 
 @dataclass(frozen=True)
+class CachedTensor:
+    """One tensor a mixer caches for every token: ``heads`` rows of ``width`` elements."""
+    name: str
+    heads: int
+    width: int
+    dtype: Optional[torch.dtype] = None         # None: the engine's activation dtype
+
+
+@dataclass(frozen=True)
 class CacheNeed:
-    """What one cache entry needs.  kind: "paged_kv", "state" or "none"."""
+    """What one cache entry needs.  kind: "paged_kv" (``tensors`` per token, in pages), "state" or "none"."""
     kind: str
-    n_kv_heads: int = 0
-    head_dim: int = 0
+    tensors: Tuple[CachedTensor, ...] = ()
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: Optional[torch.dtype] = None   # None: the engine's activation dtype
 
     @staticmethod
+    def paged(tensors: Sequence[CachedTensor], window: Optional[int] = None) -> "CacheNeed":
+        tensors = tuple(tensors)
+        names = [t.name for t in tensors]
+        if not tensors or len(set(names)) != len(names) or any(t.heads <= 0 or t.width <= 0 for t in tensors):
+            raise ValueError(f"a paged cache entry needs tensors with distinct names and positive sizes, found {tensors}")
+        return CacheNeed("paged_kv", tensors, window)
+
+    @staticmethod
     def paged_kv(n_kv_heads: int, head_dim: int, window: Optional[int] = None) -> "CacheNeed":
-        return CacheNeed("paged_kv", n_kv_heads, head_dim, window)
+        """Keys and values of one shape: tensors "k" and "v"."""
+        return CacheNeed.paged((CachedTensor("k", n_kv_heads, head_dim), CachedTensor("v", n_kv_heads, head_dim)), window)
+
+    def bytes_per_token(self, default_dtype: torch.dtype) -> int:
+        return sum(t.heads * t.width * (t.dtype or default_dtype).itemsize for t in self.tensors)
 
     @staticmethod
     def state(shape: Sequence[int], dtype: Optional[torch.dtype] = None) -> "CacheNeed":
@@ -114,7 +137,7 @@ class _Group:
     need: CacheNeed                   # kind paged_kv; window shared by the group
     entries: List[int]                # cache entries that live in this group
     allocator: Optional[_GroupPages]
-    pool: Optional[torch.Tensor] = None   # [entries, 2, pages, Hkv, page, D]
+    pools: Optional[Dict[str, torch.Tensor]] = None   # tensor name -> [entries, pages, heads, page, width]
 
 
 class CacheManager:
@@ -139,7 +162,7 @@ class CacheManager:
         for e, need in enumerate(self.needs):
             if need.kind != "paged_kv":
                 continue
-            key = (need.n_kv_heads, need.head_dim, need.window)
+            key = (need.tensors, need.window)
             if key not in key_to_group:
                 key_to_group[key] = len(self.groups)
                 self.groups.append(_Group(need, [], None))
@@ -162,8 +185,8 @@ class CacheManager:
         for g, (grp, c) in enumerate(zip(self.groups, counts)):
             grp.allocator = _GroupPages(self, g)
             if device is not None:
-                grp.pool = torch.zeros((len(grp.entries), 2, c, grp.need.n_kv_heads, self.page_size, grp.need.head_dim),
-                                       dtype=dtype, device=device)
+                grp.pools = {t.name: torch.zeros((len(grp.entries), c, t.heads, self.page_size, t.width),
+                                                 dtype=t.dtype or dtype, device=device) for t in grp.need.tensors}
         self.state: Dict[int, torch.Tensor] = {}
         for e, need in enumerate(self.needs):
             if need.kind == "state" and device is not None:
@@ -331,10 +354,14 @@ class CacheManager:
             self._raise(rc, rid, f"a position in [{start}, {start + n})")
         return list(out[:n])
 
+    def pools(self, entry: int) -> Dict[str, torch.Tensor]:
+        """The entry's pools by tensor name, each ``[pages, heads, page_size, width]``."""
+        g, i = self.group_of_entry[entry], self.index_in_group[entry]
+        return {name: pool[i] for name, pool in self.groups[g].pools.items()}
+
     def kv_pools(self, entry: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        g = self.group_of_entry[entry]
-        pool = self.groups[g].pool[self.index_in_group[entry]]
-        return pool[0], pool[1]
+        pools = self.pools(entry)
+        return pools["k"], pools["v"]
 
     def n_free_pages(self) -> List[int]:
         return [self._lib.ph_n_free_pages(self._h, g) for g in range(self._n_groups)]

@@ -96,6 +96,12 @@ class ModelSpec:
     tie_word_embeddings: Optional[bool] = None    # None: decided by the head tensor's presence
     init_std: float = 0.02
     eos_token_id: int = -1
+    # What sits around the blocks.  Qwen3 dense uses none of it.
+    embedding_multiplier: float = 1.0             # the embedding row is scaled by this before the first block
+    logit_scale: float = 1.0                      # logits are scaled by this ...
+    logit_softcap: Optional[float] = None         # ... and then capped: cap * tanh(logits / cap)
+    position_axes: int = 1                        # axes of a token's position; axis 0 is its index in the sequence
+    ignore: Tuple[str, ...] = ()                  # tensor-name patterns (fnmatch) that a folder may hold and nobody reads
 
     @property
     def n_cache_entries(self) -> int:

@@ -35,7 +35,7 @@ using namespace pb;
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                             int width, int vocab) {
+                             int width, int vocab, float scale) {
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * width;
@@ -44,7 +44,16 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
         return;
     }
     const T* row = table + (size_t)id * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_float(row[i]) * scale;
+}
+
+// logits *= scale, then cap * tanh(logits / cap) where cap > 0: what some architectures put behind their head.
+__global__ void scale_cap_kernel(float* __restrict__ x, size_t n, float scale, float cap) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = x[i] * scale;
+        if (cap > 0.0f) v = cap * tanhf(v / cap);
+        x[i] = v;
+    }
 }
 
 // ---------------------------------------------------------------- residual add + RMSNorm
@@ -400,12 +409,22 @@ PB_EXPORT int pb_gather_words(const void* const* words, int n, int* out, cudaStr
     return launch_status();
 }
 
-PB_EXPORT int pb_embed(int dtype, const void* table, const int* ids, float* out, int n, int width, int vocab,
+// x[i] = cap > 0 ? cap * tanh(x[i] * scale / cap) : x[i] * scale, in place, for n float32 values.
+PB_EXPORT int pb_scale_cap(float* x, long long n, float scale, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    scale_cap_kernel<<<(int)blocks, 256, 0, stream>>>(x, (size_t)n, scale, cap);
+    return launch_status();
+}
+
+// out[t] = table[ids[t]] * scale (float32 out; scale 1 for most architectures).
+PB_EXPORT int pb_embed(int dtype, const void* table, const int* ids, float* out, int n, int width, int vocab, float scale,
                        cudaStream_t stream) {
     if (n <= 0) return 0;
     const int b = block_for(width);
-    if (dtype == PB_F32) embed_kernel<float><<<n, b, 0, stream>>>((const float*)table, ids, out, width, vocab);
-    else if (dtype == PB_BF16) embed_kernel<__nv_bfloat16><<<n, b, 0, stream>>>((const __nv_bfloat16*)table, ids, out, width, vocab);
+    if (dtype == PB_F32) embed_kernel<float><<<n, b, 0, stream>>>((const float*)table, ids, out, width, vocab, scale);
+    else if (dtype == PB_BF16) embed_kernel<__nv_bfloat16><<<n, b, 0, stream>>>((const __nv_bfloat16*)table, ids, out, width, vocab, scale);
     else return PB_ERR_BAD_DTYPE;
     return launch_status();
 }

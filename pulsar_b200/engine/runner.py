@@ -28,11 +28,15 @@ class StepEntry:
     """The next ``tokens`` of request ``rid``; ``want`` lists the indices among these
     tokens whose logits are returned (in this order).  ``token_src`` (for an entry of one
     token) says that the token is not known on the host yet: it is element ``token_src`` of
-    the device tensor of sampled ids that the step is given, and ``tokens`` holds a stand-in."""
+    the device tensor of sampled ids that the step is given, and ``tokens`` holds a stand-in.
+    ``positions`` (only for a model whose positions have more than one axis): one list per further
+    axis, each as long as ``tokens``; axis 0 is always the token's index in its sequence, and an axis
+    that is not given repeats it."""
     rid: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
     token_src: Optional[int] = None
+    positions: Optional[Sequence[Sequence[int]]] = None
 
 
 class StepError(ValueError):
@@ -56,6 +60,7 @@ class ModelRunner:
             raise RuntimeError(f"the engine runs on a CUDA device only (asked for '{device}'); there is no CPU path")
         self.dtype = model.dtype
         self.vocab = model.spec.vocab_size
+        self.position_axes = int(getattr(model.spec, "position_axes", 1))
         self._scratch: Dict[str, torch.Tensor] = {}
         self.scratch_epoch = 0
         self._staging: List[Optional[torch.Tensor]] = [None] * self.N_STAGING
@@ -66,7 +71,7 @@ class ModelRunner:
         self.steps_run = 0
         # Decode steps (one token per request) are launch-bound: their kernel sequence is
         # captured once per (batch size, block-table width) and replayed.
-        self.cuda_graphs = bool(cuda_graphs)
+        self.cuda_graphs = bool(cuda_graphs) and bool(getattr(model, "graph_safe", True))
         self._graphs: Dict[tuple, Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._graph_seen: Dict[tuple, int] = {}
         self._graph_epoch = -1
@@ -94,8 +99,8 @@ class ModelRunner:
         need = self.cache.needs[entry]
         if need.kind == "paged_kv":
             g = self.cache.group_of_entry[entry]
-            k, v = self.cache.kv_pools(entry)
-            return CacheView("paged_kv", k, v, ctx.group_tables[g], ctx.group_slots[g], self.cache.page_size, group=g)
+            return CacheView("paged_kv", self.cache.pools(entry), ctx.group_tables[g], ctx.group_slots[g],
+                             self.cache.page_size, group=g)
         if need.kind == "state":
             return CacheView("state", state=self.cache.state[entry], page_size=self.cache.page_size)
         return CacheView("none", page_size=self.cache.page_size)
@@ -135,6 +140,10 @@ class ModelRunner:
             if e.token_src is not None and (n_tok != 1 or sampled_ids is None or not (0 <= e.token_src < sampled_ids.numel())):
                 raise StepError(f"request {e.rid!r}: a token taken from the device needs an entry of one token and "
                                 f"a tensor of sampled ids that has element {e.token_src}")
+            if e.positions is not None and (len(e.positions) != self.position_axes - 1
+                                            or any(len(axis) != n_tok for axis in e.positions)):
+                raise StepError(f"request {e.rid!r}: positions must give {self.position_axes - 1} further axes of "
+                                f"{n_tok} values each (the model's positions have {self.position_axes} axes)")
             if len(e.want) and (min(e.want) < 0 or max(e.want) >= n_tok):
                 bad = [w for w in e.want if not (0 <= int(w) < n_tok)][0]
                 raise StepError(f"request {e.rid!r}: wanted index {bad} outside its {n_tok} tokens")
@@ -217,6 +226,17 @@ class ModelRunner:
             ctx.group_tables.append(views[8 + 2 * g])
         if moved:
             ops.move_ids(ctx.token_ids, views[-2], views[-1], sampled_ids)
+        if self.position_axes > 1:
+            # Further axes of the positions travel in a copy of their own (no architecture of this package has them).
+            axes = torch.empty((self.position_axes, n), dtype=torch.int32, pin_memory=True)
+            at = 0
+            for e, start, q in zip(entries, starts, q_lens):
+                own = torch.arange(start, start + q, dtype=torch.int32)
+                axes[0, at:at + q] = own
+                for a in range(1, self.position_axes):
+                    axes[a, at:at + q] = own if e.positions is None else torch.tensor(list(e.positions[a - 1]), dtype=torch.int32)
+                at += q
+            ctx.position_axes = axes.to(self.device, non_blocking=True)
         return ctx
 
     def step(self, entries: Sequence[StepEntry], sampled_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -230,7 +250,7 @@ class ModelRunner:
         return logits
 
     def _forward(self, ctx: StepContext) -> torch.Tensor:
-        if not (self.cuda_graphs and ctx.all_decode):
+        if not (self.cuda_graphs and ctx.all_decode) or self.position_axes > 1:
             return self.model.forward(ctx)
         if self._graph_epoch != self.scratch_epoch:       # a buffer moved: every captured address is stale
             self._graphs.clear()

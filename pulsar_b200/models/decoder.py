@@ -25,6 +25,10 @@ class DecoderModel(Part):
     def __init__(self, spec: ModelSpec, dtype: torch.dtype):
         if dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"compute dtype {dtype} must be float32 or bfloat16")
+        if spec.position_axes < 1:
+            raise ValueError("a model's positions have at least one axis (the index in the sequence)")
+        if spec.logit_softcap is not None and not (spec.logit_softcap > 0.0):
+            raise ValueError("logit_softcap must be positive")
         self.spec, self.dtype = spec, dtype
         self.blocks = [BLOCKS.get(b.kind)(b, dtype) for b in spec.blocks]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, spec.final_norm_name[: -len("weight")], dtype,
@@ -54,6 +58,11 @@ class DecoderModel(Part):
 
     def cache_needs(self) -> List[CacheNeed]:
         return list(self._needs)
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a step of this model may be captured into a CUDA graph (every part says so)."""
+        return all(getattr(b, "graph_safe", True) for b in self.blocks) and getattr(self.final_norm, "graph_safe", True)
 
     # ---------------------------------------------------------------- weights
     def weight_specs(self) -> List[WeightSpec]:
@@ -90,7 +99,7 @@ class DecoderModel(Part):
         """Logits float32 [len(ctx.logit_rows), vocab] for the tokens of ``ctx``."""
         s = self.spec
         residual = ctx.scratch("residual", (ctx.n_tokens, s.hidden), torch.float32)
-        ops.embed(self.embed, ctx.token_ids, residual)
+        ops.embed(self.embed, ctx.token_ids, residual, s.embedding_multiplier)
         delta = None
         for call in s.run_order:
             delta = self.blocks[call.block].forward(ctx, residual, delta, ctx.cache(call.cache))
@@ -99,4 +108,6 @@ class DecoderModel(Part):
         if rows.numel():
             h = self.final_norm.forward(ctx, residual, delta, rows=rows)
             ops.linear(h, self.head, logits)
+            if s.logit_scale != 1.0 or s.logit_softcap is not None:
+                ops.scale_cap(logits, s.logit_scale, s.logit_softcap)
         return logits

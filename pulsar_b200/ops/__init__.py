@@ -38,7 +38,8 @@ _ERRORS = {-2: "unsupported dtype", -3: "unsupported size or argument", -4: "siz
 
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _SIGNATURES = {
-    "pb_embed": [_I, _P, _P, _P, _I, _I, _I, _P],
+    "pb_embed": [_I, _P, _P, _P, _I, _I, _I, _F, _P],
+    "pb_scale_cap": [_P, ctypes.c_longlong, _F, _F, _P],
     "pb_move_ids": [_P, _P, _P, _P, _I, _P],
     "pb_add_rmsnorm": [_I, _P, _P, _P, _P, _P, _I, _I, _F, _I, _P],
     "pb_rope_table": [_P, _P, _P, _P, _I, _I, _P],
@@ -124,12 +125,19 @@ def _p(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] (float32) = table[ids[t]]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] (float32) = table[ids[t]] * scale."""
     _cuda(table, ids, out)
     assert ids.dtype == torch.int32 and out.dtype == torch.float32 and out.shape == (ids.numel(), table.shape[1])
     check(fn("pb_embed")(code(table.dtype), _p(table), _p(ids), _p(out), ids.numel(), table.shape[1], table.shape[0],
-                         stream()), "embed")
+                         float(scale), stream()), "embed")
+
+
+def scale_cap(x: torch.Tensor, scale: float = 1.0, cap: Optional[float] = None) -> None:
+    """In place on float32 values: x *= scale, then cap * tanh(x / cap) where a cap is given."""
+    _cuda(x)
+    assert x.dtype == torch.float32
+    check(fn("pb_scale_cap")(_p(x), x.numel(), float(scale), float(cap or 0.0), stream()), "scale_cap")
 
 
 def move_ids(ids: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, src_ids: torch.Tensor) -> None:

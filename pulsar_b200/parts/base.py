@@ -35,13 +35,20 @@ class WeightSpec:
 class CacheView:
     """What a mixer sees of its cache entry in one step."""
     kind: str                                    # "paged_kv", "state", "none"
-    k_pool: Optional[torch.Tensor] = None        # [pages, Hkv, page, D]
-    v_pool: Optional[torch.Tensor] = None
+    pools: Optional[Dict[str, torch.Tensor]] = None   # cached tensor name -> [pages, heads, page, width]
     block_table: Optional[torch.Tensor] = None   # int32 [S, width], logical page -> page id
     slots: Optional[torch.Tensor] = None         # int32 [N], page * page_size + offset of each new token
     page_size: int = 0
     state: Optional[torch.Tensor] = None         # [max_requests, *state_shape]
     group: int = -1
+
+    @property
+    def k_pool(self) -> Optional[torch.Tensor]:
+        return self.pools.get("k") if self.pools else None
+
+    @property
+    def v_pool(self) -> Optional[torch.Tensor]:
+        return self.pools.get("v") if self.pools else None
 
 
 @dataclass
@@ -70,6 +77,7 @@ class StepContext:
         self.all_decode = self.max_q_len == 1
         # int32 device arrays
         self.token_ids = self.positions = self.seq_of_token = None      # [N]
+        self.position_axes = None               # [axes, N] where the model's positions have more than one axis, else None
         self.cu_q = self.kv_len = self.state_slots = None               # [S+1], [S], [S]
         self.logit_rows = None                                          # [R]
         self.group_tables: List[torch.Tensor] = []                      # per group [S, width]
@@ -85,6 +93,11 @@ class StepContext:
 
 class Part:
     """Common base: weights by name."""
+
+    # A step of single tokens is captured into a CUDA graph and replayed while its shape stays the same.  A part
+    # whose ``forward`` decides anything on the host from the step's contents (``ctx.host``: lengths, slots) would
+    # replay stale decisions: it sets this to False, and a model that holds such a part is never captured.
+    graph_safe: bool = True
 
     def weight_specs(self) -> List[WeightSpec]:
         return []
@@ -109,7 +122,8 @@ class Norm(Part):
 
 class PositionEncoding:
     """tables(ctx) -> whatever its mixers consume, computed once per step from
-    ``ctx.positions`` and shared by all layers with an equal specification."""
+    ``ctx.positions`` (or, for positions of several axes, ``ctx.position_axes``) and shared
+    by all layers with an equal specification."""
 
     def tables(self, ctx: StepContext):
         raise NotImplementedError
@@ -137,6 +151,11 @@ class Block(Part):
     cache) -> the new pending delta (``residual`` is updated in place)."""
 
     mixer: Mixer
+    parts: Tuple[Part, ...] = ()
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", True) for p in self.parts)
 
     def forward(self, ctx: StepContext, residual: torch.Tensor, delta: Optional[torch.Tensor],
                 cache: CacheView) -> torch.Tensor:

@@ -5,11 +5,13 @@ it needs when the model is constructed; a missing name is reported one at a time
 tensors are ignored and shapes are not checked (pulsar/src/pulsar/checkpoint.py:122-142;
 pulsar-core/src/model/qwen3.cpp:19-22, 48-72).  Here the headers are compared with what
 the model's parts declare before any data moves, and one error lists every missing
-tensor, every unexpected tensor and every wrong shape or dtype.
+tensor, every unexpected tensor and every wrong shape or dtype.  An architecture may list
+name patterns of tensors that its checkpoints carry and nobody reads (``ModelSpec.ignore``).
 """
 from __future__ import annotations
 
-from typing import Dict, List
+from fnmatch import fnmatchcase
+from typing import Dict, List, Sequence
 
 import torch
 
@@ -46,10 +48,12 @@ def held_dtype(spec: WeightSpec, compute_dtype: torch.dtype) -> torch.dtype:
     raise ValueError(f"weight '{spec.name}': unknown role '{spec.role}'")
 
 
-def check_entries(where: str, specs: List[WeightSpec], entries: Dict[str, TensorEntry]) -> None:
+def check_entries(where: str, specs: List[WeightSpec], entries: Dict[str, TensorEntry], ignore: Sequence[str] = ()) -> None:
+    """``ignore``: name patterns (fnmatch) of tensors that the folder may hold although no part reads them
+    (buffers that checkpoints of an architecture carry along); a tensor that a part wants is never ignored."""
     by_name = {s.name: s for s in specs}
     missing = [s.name for s in specs if not s.optional and s.name not in entries]
-    unexpected = sorted(n for n in entries if n not in by_name)
+    unexpected = sorted(n for n in entries if n not in by_name and not any(fnmatchcase(n, pat) for pat in ignore))
     wrong = []
     for s in specs:
         e = entries.get(s.name)
@@ -79,7 +83,7 @@ def load_weights(model, model_dir: str, device) -> None:
             entries[name] = e
             owner[name] = f
     specs = model.weight_specs()
-    check_entries(model_dir, specs, entries)
+    check_entries(model_dir, specs, entries, getattr(getattr(model, "spec", None), "ignore", ()))
     tensors: Dict[str, torch.Tensor] = {}
     for s in specs:
         if s.name not in entries:

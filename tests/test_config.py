@@ -4,8 +4,9 @@ import copy
 import pytest
 
 from helpers import TINY_A, TINY_B, TINY_C
-from pulsar_b200.config import (ARCHITECTURES, ConfigError, EngineConfig, Qwen3Config, architecture_name,
+from pulsar_b200.config import (ARCHITECTURES, ConfigError, EngineConfig, architecture_name,
                                 config_from_dict)
+from pulsar_b200.models.qwen3 import Qwen3Config
 
 
 def test_reads_the_architectures_own_keys():

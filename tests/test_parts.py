@@ -1,8 +1,13 @@
 """The parts of a layer, each alone against its plain formula, and the ways they are put
 together: different mixers in different layers, a run order that names a layer twice and
 lets a layer read another layer's cache, and a toy mixer with state of its own that is
-defined here, registered, built, loaded and stepped without touching the package (GPU)."""
+defined here, registered, built, loaded and stepped without touching the package; likewise a
+feed-forward with routing, other position encodings (one with two axes), a mixer that caches
+keys and values of different widths, and an architecture with an embedding multiplier, capped
+logits and an ignored buffer (GPU)."""
+import json
 import math
+import os
 import random
 from dataclasses import dataclass
 
@@ -184,6 +189,8 @@ def _register_toy():
     from pulsar_b200.parts.base import Mixer, WeightSpec
 
     class ToyRecurrent(Mixer):
+        graph_safe = False              # loops over the step's requests on the host
+
         def __init__(self, spec, prefix, dtype):
             self.spec, self.prefix, self.dtype = spec, prefix, dtype
             self.width = spec.option("state_width")
@@ -328,6 +335,8 @@ def _register_routed():
     from pulsar_b200.parts.base import FeedForward, PositionEncoding, WeightSpec
 
     class ToyRouted(FeedForward):
+        graph_safe = False              # picks its rows on the host
+
         def __init__(self, spec, prefix, dtype):
             self.spec, self.prefix, self.dtype = spec, prefix, dtype
             self.n_experts = spec.option("n_experts")
@@ -456,3 +465,313 @@ def test_toy_routed_feed_forward_and_another_position_encoding(tmp_path):
         FEED_FORWARDS.unregister("toy_routed")
         POSITIONS.unregister("toy_scaled_rope")
         ARCHITECTURES.unregister("ToyRoutedForCausalLM")
+
+
+# ------------------------------------------------------------------ a mixer that caches keys and values of different widths,
+# in an architecture with an embedding multiplier, capped logits and a buffer in its checkpoints that nobody reads
+def _register_asymmetric():
+    """Attention without position encoding whose keys are 48 wide and whose values are 32 wide: two cached tensors
+    of different shapes, declared by the mixer, in pools of their own.  The toy reads and writes its pages with
+    plain tensor operations (it is a test of the cache's interface, not a kernel)."""
+    from pulsar_b200.cache import CachedTensor, CacheNeed
+    from pulsar_b200.config import (ARCHITECTURES, MIXERS, BlockSpec, FeedForwardSpec, LayerCall, MixerSpec, ModelSpec,
+                                    NormSpec)
+    from pulsar_b200.parts.base import Mixer, WeightSpec
+
+    class ToyAsymmetric(Mixer):
+        KEY, VALUE = 48, 32
+        graph_safe = False              # loops over the step's requests on the host
+
+        def __init__(self, spec, prefix, dtype):
+            self.spec, self.prefix, self.dtype = spec, prefix, dtype
+
+        def weight_specs(self):
+            s, p = self.spec, self.prefix
+            return [WeightSpec(p + "q.weight", (s.n_heads * self.KEY, s.hidden)),
+                    WeightSpec(p + "k.weight", (s.n_kv_heads * self.KEY, s.hidden)),
+                    WeightSpec(p + "v.weight", (s.n_kv_heads * self.VALUE, s.hidden)),
+                    WeightSpec(p + "o.weight", (s.hidden, s.n_heads * self.VALUE))]
+
+        def load(self, tensors):
+            self.w = {n: tensors[self.prefix + n + ".weight"].float() for n in "qkvo"}
+
+        def cache_need(self):
+            return CacheNeed.paged((CachedTensor("key", self.spec.n_kv_heads, self.KEY),
+                                    CachedTensor("value", self.spec.n_kv_heads, self.VALUE)))
+
+        def forward(self, ctx, h, cache):
+            s, n, ps = self.spec, ctx.n_tokens, cache.page_size
+            x = h.float()
+            q = (x @ self.w["q"].T).view(n, s.n_heads, self.KEY)
+            k = (x @ self.w["k"].T).view(n, s.n_kv_heads, self.KEY)
+            v = (x @ self.w["v"].T).view(n, s.n_kv_heads, self.VALUE)
+            keys, values = cache.pools["key"], cache.pools["value"]            # [pages, heads, page, width]
+            assert keys.shape[1:] == (s.n_kv_heads, ps, self.KEY) and values.shape[1:] == (s.n_kv_heads, ps, self.VALUE)
+            slots = cache.slots.long()
+            keys[slots // ps, :, slots % ps] = k.to(keys.dtype)
+            values[slots // ps, :, slots % ps] = v.to(values.dtype)
+            out = torch.empty(n, s.n_heads, self.VALUE, dtype=torch.float32, device=h.device)
+            row, group = 0, s.n_heads // s.n_kv_heads
+            for i, (n_q, kv_len) in enumerate(zip(ctx.host.q_lens, ctx.host.kv_lens)):
+                pages = cache.block_table[i, :-(-kv_len // ps)].long()
+                kk = keys[pages].permute(0, 2, 1, 3).reshape(-1, s.n_kv_heads, self.KEY)[:kv_len].float()
+                vv = values[pages].permute(0, 2, 1, 3).reshape(-1, s.n_kv_heads, self.VALUE)[:kv_len].float()
+                for t in range(n_q):
+                    p = kv_len - n_q + t
+                    for hd in range(s.n_heads):
+                        sc = (kk[:p + 1, hd // group] @ q[row, hd]) * s.scale
+                        out[row, hd] = torch.softmax(sc, 0) @ vv[:p + 1, hd // group]
+                    row += 1
+            return (out.view(n, -1) @ self.w["o"].T).to(h.dtype)
+
+    @dataclass(frozen=True)
+    class AsymConfig:
+        vocab_size: int
+        hidden_size: int
+        embedding_multiplier: float
+        logit_scale: float
+        logit_softcap: float
+        ignore: tuple
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["vocab_size"], raw["hidden_size"], raw["embedding_multiplier"], raw["logit_scale"],
+                       raw["logit_softcap"], tuple(raw.get("ignore", ())))
+
+        def to_dict(self):
+            return dict(architectures=["ToyAsymmetricForCausalLM"], vocab_size=self.vocab_size, hidden_size=self.hidden_size,
+                        embedding_multiplier=self.embedding_multiplier, logit_scale=self.logit_scale,
+                        logit_softcap=self.logit_softcap, ignore=list(self.ignore))
+
+        def model_spec(self):
+            norm = NormSpec("rmsnorm", self.hidden_size, 1e-5)
+            mixer = MixerSpec("toy_asymmetric", self.hidden_size, n_heads=4, n_kv_heads=2, scale=0.2)
+            ffn = FeedForwardSpec("swiglu", self.hidden_size, 72)
+            blocks = tuple(BlockSpec("prenorm", mixer, ffn, norm, norm, f"a.{i}.",
+                                     (("mixer", "mix."), ("feed_forward", "ffn."), ("mixer_norm", "n1."),
+                                      ("feed_forward_norm", "n2."))) for i in range(2))
+            return ModelSpec("ToyAsymmetricForCausalLM", self.vocab_size, self.hidden_size, blocks,
+                             (LayerCall(0, 0), LayerCall(1, 1)), norm, embed_name="a.embed.weight",
+                             final_norm_name="a.norm.weight", head_name=None, init_std=0.15,
+                             embedding_multiplier=self.embedding_multiplier, logit_scale=self.logit_scale,
+                             logit_softcap=self.logit_softcap, ignore=self.ignore)
+
+    MIXERS.register("toy_asymmetric", ToyAsymmetric, replace=True)
+    ARCHITECTURES.register("ToyAsymmetricForCausalLM", AsymConfig.from_dict, replace=True)
+
+
+def _plain_asymmetric(raw, w, tokens):
+    t = len(tokens)
+    x = w["a.embed.weight"][torch.tensor(tokens)] * raw["embedding_multiplier"]
+    causal = torch.tril(torch.ones(t, t, dtype=torch.bool))
+    for i in range(2):
+        p = f"a.{i}."
+        h = plain.rmsnorm(x, w[p + "n1.weight"], 1e-5)
+        q = (h @ w[p + "mix.q.weight"].T).view(t, 4, 48)
+        k = (h @ w[p + "mix.k.weight"].T).view(t, 2, 48)
+        v = (h @ w[p + "mix.v.weight"].T).view(t, 2, 32)
+        o = torch.empty(t, 4, 32, dtype=torch.float64)
+        for hd in range(4):
+            sc = (q[:, hd] @ k[:, hd // 2].T * 0.2).masked_fill(~causal, float("-inf"))
+            o[:, hd] = torch.softmax(sc, -1) @ v[:, hd // 2]
+        x = x + o.reshape(t, 128) @ w[p + "mix.o.weight"].T
+        h2 = plain.rmsnorm(x, w[p + "n2.weight"], 1e-5)
+        x = x + plain.swiglu_mlp(h2, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+    logits = plain.rmsnorm(x, w["a.norm.weight"], 1e-5) @ w["a.embed.weight"].T * raw["logit_scale"]
+    return raw["logit_softcap"] * torch.tanh(logits / raw["logit_softcap"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cached_tensors_of_different_widths_an_ignored_buffer_and_what_sits_around_the_blocks(tmp_path, dtype):
+    from safetensors.torch import load_file, save_file
+    from pulsar_b200.config import ARCHITECTURES, MIXERS, config_from_dict
+    from pulsar_b200.replay import Replay
+    from pulsar_b200.weights import WeightError, write_model_folder
+    _register_asymmetric()
+    try:
+        raw = dict(architectures=["ToyAsymmetricForCausalLM"], vocab_size=91, hidden_size=56, embedding_multiplier=3.5,
+                   logit_scale=0.4, logit_softcap=2.5, ignore=["a.*.mix.rotary.inv_freq", "a.position_ids"])
+        folder = write_model_folder(config_from_dict(raw), str(tmp_path / "m"), 21)
+        path = os.path.join(folder, "model.safetensors")
+        tensors = load_file(path)
+        tensors["a.0.mix.rotary.inv_freq"] = torch.arange(8, dtype=torch.float32)      # what checkpoints carry along
+        tensors["a.position_ids"] = torch.arange(16, dtype=torch.int64)
+        save_file(tensors, path)
+        _, weights = helpers.read_folder(folder)
+        w = {k: v.double() for k, v in weights.items()}
+        if dtype == "bfloat16":
+            w = {k: v.double() for k, v in helpers.as_bf16_matrices(weights).items()}
+        rng = random.Random(5)
+        reqs = {f"r{i}": helpers.random_tokens(rng, n, 91) for i, n in enumerate([21, 9, 30, 13])}
+        ref = {rid: _plain_asymmetric(raw, w, toks) for rid, toks in reqs.items()}
+        rp = Replay(folder, dtype, 2 * 64, page_size=4, max_running=2)        # room for two requests: pages are used again
+        group = rp.cache.groups[0]
+        assert {n: tuple(p.shape[2:]) for n, p in group.pools.items()} == {"key": (2, 4, 48), "value": (2, 4, 32)}
+        trace = helpers.trace_mixed(reqs, rng, max_live=2, portion=(2, 6), decode_tail=3)
+        got = {}
+        for rec, rows in zip(trace.records, trace.rows):
+            logits = rp.run_step(rec)
+            for i, key in enumerate(rows):
+                got[key] = logits[i]
+        assert len(got) == sum(len(t) for t in reqs.values())
+        worst = max(helpers.rel_err(row, ref[rid][pos]) for (rid, pos), row in got.items())
+        helpers.report("asymmetric_cache", worst, dtype)
+        assert worst < TOL[dtype]
+        assert float(torch.stack(list(got.values())).abs().max()) <= 2.5 + 1e-6         # the cap holds
+        rp.cache.check_consistency()
+        # without the patterns the same folder is refused, and the message names the buffers
+        with pytest.raises(WeightError) as info:
+            Replay(write_config(folder, dict(raw, ignore=[])), dtype, 64, page_size=4)
+        assert sorted(info.value.unexpected) == ["a.0.mix.rotary.inv_freq", "a.position_ids"] and not info.value.missing
+    finally:
+        MIXERS.unregister("toy_asymmetric")
+        ARCHITECTURES.unregister("ToyAsymmetricForCausalLM")
+
+
+def write_config(folder, raw):
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(raw, f)
+    return folder
+
+
+def test_a_preempted_request_of_the_recurrent_toy_mixer_starts_from_fresh_state(tmp_path):
+    """So few pages that the scheduler preempts a request and computes it again from its tokens: the state slot it
+    gets then starts at zero, and the tokens that come out are the plain implementation's."""
+    from pulsar_b200.config import ARCHITECTURES, MIXERS, config_from_dict
+    from pulsar_b200.engine.engine import Engine
+    from pulsar_b200.weights import write_model_folder
+    _register_toy()
+    try:
+        raw = dict(architectures=["ToyRecurrentForCausalLM"], vocab_size=97, hidden_size=48, num_hidden_layers=3,
+                   state_width=24, decay=0.9, eps=1e-5)
+        folder = write_model_folder(config_from_dict(raw), str(tmp_path), 7)
+        _, weights = helpers.read_folder(folder)
+        w = {k: v.double() for k, v in weights.items()}
+        rng = random.Random(3)
+        prompts = [helpers.random_tokens(rng, n, 97) for n in (14, 9, 12)]
+        new = 22
+
+        def plain_generate(prompt):
+            seq, out = list(prompt), []
+            for _ in range(new):
+                tok = int(torch.argmax(_plain_toy(raw, w, seq)[-1]))
+                out.append(tok)
+                seq.append(tok)
+            return out
+        want = [plain_generate(p) for p in prompts]
+        eng = Engine(folder, dict(dtype="float32", page_size=4, num_pages=20, max_sessions=4, max_running=3,
+                                  max_chunk_size=16, eos_id=-1))            # 80 tokens of cache for 101 needed
+        got = eng.generate(prompts, new)
+        assert eng.scheduler.n_preemptions >= 1
+        assert got == want
+        eng.cache.check_consistency()
+    finally:
+        MIXERS.unregister("toy_recurrent")
+        ARCHITECTURES.unregister("ToyRecurrentForCausalLM")
+
+
+# ------------------------------------------------------------------ positions with two axes
+def _register_two_axes():
+    """A rotary encoding whose lower frequencies turn with a second axis of the position (as encodings for
+    images and video have it), and an architecture that declares two axes."""
+    from pulsar_b200.config import (ARCHITECTURES, POSITIONS, BlockSpec, FeedForwardSpec, LayerCall, MixerSpec, ModelSpec,
+                                    NormSpec, PositionSpec)
+    from pulsar_b200.parts.base import PositionEncoding
+
+    class TwoAxisRope(PositionEncoding):
+        def __init__(self, spec):
+            self.spec = spec
+
+        def tables(self, ctx):
+            key = ("two_axes", self.spec)
+            if key not in ctx.shared:
+                half = self.spec.rotary_dim // 2
+                inv = torch.tensor([self.spec.theta ** (-2.0 * j / self.spec.rotary_dim) for j in range(half)],
+                                   dtype=torch.float64, device=ctx.device)
+                axes = ctx.position_axes.double()                       # [2, N]
+                which = (torch.arange(half, device=ctx.device) >= half // 2).long()      # upper half of the pairs: axis 1
+                ang = axes[which].T * inv[None, :]                      # [N, half]
+                ctx.shared[key] = (torch.cos(ang).float().contiguous(), torch.sin(ang).float().contiguous())
+            return ctx.shared[key]
+
+    @dataclass(frozen=True)
+    class AxesConfig:
+        vocab_size: int
+        hidden_size: int
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["vocab_size"], raw["hidden_size"])
+
+        def to_dict(self):
+            return dict(architectures=["ToyAxesForCausalLM"], vocab_size=self.vocab_size, hidden_size=self.hidden_size)
+
+        def model_spec(self):
+            norm = NormSpec("rmsnorm", self.hidden_size, 1e-5)
+            mixer = MixerSpec("attention", self.hidden_size, n_heads=4, n_kv_heads=2, head_dim=16, scale=0.25,
+                              qk_norm_eps=1e-5, position=PositionSpec("toy_two_axis_rope", 16, 16, 50.0))
+            blocks = (BlockSpec("prenorm", mixer, FeedForwardSpec("swiglu", self.hidden_size, 80), norm, norm, "x.0.",
+                                (("mixer", "attn."), ("feed_forward", "ffn."), ("mixer_norm", "n1."),
+                                 ("feed_forward_norm", "n2."))),)
+            return ModelSpec("ToyAxesForCausalLM", self.vocab_size, self.hidden_size, blocks, (LayerCall(0, 0),), norm,
+                             embed_name="x.embed.weight", final_norm_name="x.norm.weight", head_name=None, init_std=0.2,
+                             position_axes=2)
+
+    POSITIONS.register("toy_two_axis_rope", TwoAxisRope, replace=True)
+    ARCHITECTURES.register("ToyAxesForCausalLM", AxesConfig.from_dict, replace=True)
+
+
+def _plain_two_axes(w, tokens, second_axis):
+    t = len(tokens)
+    x = w["x.embed.weight"][torch.tensor(tokens)]
+    inv = torch.tensor([50.0 ** (-2.0 * j / 16) for j in range(8)], dtype=torch.float64)
+    pos = torch.stack([torch.arange(t).double(), torch.tensor(second_axis).double()])
+    ang = pos[(torch.arange(8) >= 4).long()].T * inv[None, :]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rot(z):
+        a, b = z[..., :8], z[..., 8:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+    h = plain.rmsnorm(x, w["x.0.n1.weight"], 1e-5)
+    q = plain.rmsnorm((h @ w["x.0.attn.q_proj.weight"].T).view(t, 4, 16), w["x.0.attn.q_norm.weight"], 1e-5)
+    k = plain.rmsnorm((h @ w["x.0.attn.k_proj.weight"].T).view(t, 2, 16), w["x.0.attn.k_norm.weight"], 1e-5)
+    v = (h @ w["x.0.attn.v_proj.weight"].T).view(t, 2, 16)
+    x = x + plain.attention(rot(q), rot(k), v, 0.25).reshape(t, 64) @ w["x.0.attn.o_proj.weight"].T
+    h2 = plain.rmsnorm(x, w["x.0.n2.weight"], 1e-5)
+    x = x + plain.swiglu_mlp(h2, w["x.0.ffn.gate_proj.weight"], w["x.0.ffn.up_proj.weight"], w["x.0.ffn.down_proj.weight"])
+    return plain.rmsnorm(x, w["x.norm.weight"], 1e-5) @ w["x.embed.weight"].T
+
+
+def test_positions_with_two_axes_reach_a_position_encoding_defined_here(tmp_path):
+    from pulsar_b200.config import ARCHITECTURES, POSITIONS, config_from_dict
+    from pulsar_b200.engine.runner import StepEntry, StepError
+    from pulsar_b200.replay import Replay
+    from pulsar_b200.weights import write_model_folder
+    _register_two_axes()
+    try:
+        raw = dict(architectures=["ToyAxesForCausalLM"], vocab_size=77, hidden_size=40)
+        folder = write_model_folder(config_from_dict(raw), str(tmp_path), 31)
+        _, weights = helpers.read_folder(folder)
+        w = {k: v.double() for k, v in weights.items()}
+        rng = random.Random(13)
+        toks = helpers.random_tokens(rng, 26, 77)
+        second = [rng.randrange(0, 9) for _ in toks]                    # a second axis that does not follow the first
+        ref = _plain_two_axes(w, toks, second)
+        rp = Replay(folder, "float32", 64, page_size=8)
+        rows, at = [], 0
+        for n in (7, 2, 1, 1, 9, 6):                                    # portions and single tokens
+            rows.append(rp.runner.step([StepEntry("a", toks[at:at + n], list(range(n)), positions=[second[at:at + n]])]).cpu())
+            at += n
+        assert at == len(toks)
+        err = helpers.rel_err(torch.cat(rows), ref)
+        helpers.report("two_axes", err, "float32")
+        assert err < TOL["float32"]
+        # an axis that is not given repeats the index in the sequence
+        rp.runner.finish("a")
+        same = rp.runner.step([StepEntry("b", toks, list(range(len(toks))))]).cpu()
+        assert helpers.rel_err(same, _plain_two_axes(w, toks, list(range(len(toks))))) < TOL["float32"]
+        with pytest.raises(StepError, match="axes"):
+            rp.runner.step([StepEntry("c", toks[:3], [2], positions=[[1, 2]])])
+    finally:
+        POSITIONS.unregister("toy_two_axis_rope")
+        ARCHITECTURES.unregister("ToyAxesForCausalLM")
