@@ -182,13 +182,38 @@ __device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
 // shared memory before the kernel waits for its predecessor, so that twice the bytes are on their way while the
 // kernel before this one ends; a warp copies and reads only its own part (no block barrier), rows padded by 16
 // bytes against bank conflicts.  The sums keep their order.
-template <int NT, int MODE, typename OutT, int kUnroll, bool kEvictFirst, int kPre>
+//
+// Two fused forms take the RMSNorm between two projections, and the residual addition before it, into the
+// projections themselves (a decode step then has no norm kernel between its products):
+//   kAcc     float32 output that is ADDED to what ``out`` holds (the residual stream; the projection's result never
+//            exists in bfloat16).  With ``fuse.next_w`` the block also prepares the norm that follows for its 16
+//            columns: y = bfloat16(x_new * next_w) and the block's part of sum_k x_new[token, k]^2.
+//   kScaled  the tokens come as such a prepared y; the sums of token m are scaled by rsqrt(sum / K + eps), the sum
+//            being the prepared parts added in block order (float32, fixed order: the same bits every time).
+// rmsnorm(x) W^T = rsqrt(mean(x^2) + eps) * ((x * norm_w) W^T): the per-token factor commutes with the product.
+constexpr int kMaxParts = 512;      // blocks of the product that prepared a norm: widths up to 8192
+
+struct SkinnyFuse {
+    const float* next_w;      // kAcc: weight of the norm that follows, or null
+    bf16* y;                  // kAcc: [M, N] prepared operand
+    float* part_out;          // kAcc: [gridDim.x, M] parts of the sums of squares
+    const float* part_in;     // kScaled: [n_parts, M]
+    int n_parts;
+    float eps;
+};
+
+template <int NT, int MODE, typename OutT, int kUnroll, bool kEvictFirst, int kPre, bool kScaled = false, bool kAcc = false>
 __device__ __forceinline__ void
 skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
-                 int inter) {
+                 int inter, const SkinnyFuse fuse = SkinnyFuse{}) {
     constexpr int kWideK = 64;                        // k per load: 4 threads x 16 contiguous elements
     constexpr int kPreRow = kPre * 128 + 16;          // bytes of a row's prefetched part in shared memory
     __shared__ float red[kWarps][kRows][8 * NT + 1];
+    __shared__ float scale_s[kScaled ? 8 * NT : 1];                 // kScaled: rsqrt(mean(x^2) + eps) per token
+    // kScaled: a copy of fuse.part_in.  Where part of the weights is prefetched through shared memory, the copy
+    // takes that buffer's place once a warp has read its part of it (1,024 floats in each warp's region).
+    __shared__ __align__(16) float parts_s[(kScaled && kPre == 0) ? kMaxParts * 8 * NT : 4];
+    __shared__ float square_s[kAcc ? 8 * NT : 1][kAcc ? kRows : 1]; // kAcc: x_new^2 of the block's columns
     __shared__ __align__(16) unsigned char pre[kPre > 0 ? kWarps : 1][kPre > 0 ? kRows : 1][kPre > 0 ? kPreRow : 16];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -240,6 +265,16 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
         cp_async_commit();
     }
     pdl_wait();
+    // What the epilogue needs from the kernel before this one is asked for now and used at the end, so that no warp
+    // waits for it: the parts of the sums of squares (copied to shared memory), the residual's old value.
+    float old_value = 0.0f, next_weight = 0.0f;
+    if constexpr (kAcc) {
+        if (tid < kRows * M) {
+            const int col = blockIdx.x * kRows + tid % kRows;
+            old_value = to_float(out[(size_t)(tid / kRows) * N + col]);
+            if (fuse.next_w != nullptr) next_weight = __ldg(fuse.next_w + col);
+        }
+    }
     auto multiply = [&](const Wide& a, const Wide& b, size_t kb_at) {
         const uint32_t a1[4] = {a.lo.x, b.lo.x, a.lo.y, b.lo.y};
         const uint32_t a2[4] = {a.lo.z, b.lo.z, a.lo.w, b.lo.w};
@@ -283,6 +318,20 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
         }
         kb += kPre;
     }
+    auto part_slot = [&](int f) -> float* {
+        if constexpr (kPre > 0) return reinterpret_cast<float*>(&pre[f >> 10][0][0]) + (f & 1023);
+        else return parts_s + f;
+    };
+    if constexpr (kScaled) {
+        // asked for now, used at the very end: no warp waits for it.  Each warp copies 1,024 floats at most, into its
+        // own region (which it has finished reading).
+        static_assert(kPre == 0 || kRows * kPreRow >= 4096, "a warp's region holds 1,024 floats");
+        __syncwarp();
+        const int chunks = fuse.n_parts * M / 4;                    // 16-byte chunks (n_parts is a multiple of 4)
+        const int end = min(chunks, (warp + 1) * 256);
+        for (int i = warp * 256 + lane; i < end; i += 32) cp_async16(smem_u32(part_slot(4 * i)), fuse.part_in + 4 * i, true);
+        cp_async_commit();
+    }
     for (; kb + kUnroll <= kb_end; kb += kUnroll, loaded = false) {
         if (!loaded) {
 #pragma unroll
@@ -306,6 +355,17 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
         red[warp][g + 8][n * 8 + 2 * t] = c[n][2];
         red[warp][g + 8][n * 8 + 2 * t + 1] = c[n][3];
     }
+    if constexpr (kScaled) {
+        cp_async_wait<0>();
+        __syncthreads();
+        for (int token = warp; token < M; token += kWarps) {        // the parts in block order, then a fixed tree
+            float sum = 0.0f;
+            for (int b = lane; b < fuse.n_parts; b += 32) sum += *part_slot(b * M + token);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) scale_s[token] = rsqrtf(sum / (float)K + fuse.eps);
+        }
+    }
     __syncthreads();
     if (MODE == kSwiGLU) {
         for (int i = tid; i < 8 * M; i += kWarps * 32) {
@@ -313,15 +373,40 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
             float gate = 0.0f, up = 0.0f;
 #pragma unroll
             for (int wi = 0; wi < kWarps; ++wi) { gate += red[wi][r][token]; up += red[wi][r + 8][token]; }
+            if constexpr (kScaled) { gate *= scale_s[token]; up *= scale_s[token]; }
             out[(size_t)token * inter + blockIdx.x * 8 + r] = from_float<OutT>(gate / (1.0f + expf(-gate)) * up);
         }
     } else {
-        for (int i = tid; i < kRows * M; i += kWarps * 32) {
-            const int token = i / kRows, r = i % kRows;
+        static_assert(kRows * 8 * NT <= kWarps * 32, "one output per thread");
+        const int token = tid / kRows, r = tid % kRows;
+        if (tid < kRows * M) {
             float acc = 0.0f;
 #pragma unroll
             for (int wi = 0; wi < kWarps; ++wi) acc += red[wi][r][token];
-            out[(size_t)token * N + blockIdx.x * kRows + r] = from_float<OutT>(acc);
+            if constexpr (kScaled) acc *= scale_s[token];
+            const int col = blockIdx.x * kRows + r;
+            OutT* dst = out + (size_t)token * N + col;
+            if constexpr (kAcc) {
+                const float x_new = old_value + acc;
+                *dst = from_float<OutT>(x_new);
+                if (fuse.next_w != nullptr) {
+                    fuse.y[(size_t)token * N + col] = __float2bfloat16_rn(x_new * next_weight);
+                    square_s[token][r] = x_new * x_new;
+                }
+            } else {
+                *dst = from_float<OutT>(acc);
+            }
+        }
+        if constexpr (kAcc) {
+            if (fuse.next_w != nullptr) {
+                __syncthreads();
+                if (tid < M) {
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int rr = 0; rr < kRows; ++rr) sum += square_s[tid][rr];
+                    fuse.part_out[(size_t)blockIdx.x * M + tid] = sum;
+                }
+            }
         }
     }
 }
@@ -340,6 +425,22 @@ __global__ void __launch_bounds__(kWarps * 32, kUnroll <= 2 ? 3 : 2)
 gemm_skinny_wide_prefetch_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N,
                                  int K, int inter) {
     skinny_wide_body<NT, MODE, OutT, kUnroll, true, 2>(x, w, out, M, N, K, inter);
+}
+
+// The tokens come prepared (see SkinnyFuse): the norm's per-token factor is applied to the sums.
+template <int NT, int MODE, int kUnroll, int kPre>
+__global__ void __launch_bounds__(kWarps * 32, kUnroll <= 2 ? 3 : 2)
+gemm_skinny_scaled_kernel(const bf16* __restrict__ y, const bf16* __restrict__ w, bf16* __restrict__ out, int M, int N, int K,
+                          int inter, const SkinnyFuse fuse) {
+    skinny_wide_body<NT, MODE, bf16, kUnroll, true, kPre, true, false>(y, w, out, M, N, K, inter, fuse);
+}
+
+// The projection's result added to the float32 residual stream in place (and the next norm prepared).
+template <int NT, int kUnroll, int kPre>
+__global__ void __launch_bounds__(kWarps * 32, kUnroll <= 2 ? 3 : 2)
+gemm_skinny_accumulate_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ out, int M, int N,
+                              int K, const SkinnyFuse fuse) {
+    skinny_wide_body<NT, kPlain, float, kUnroll, true, kPre, false, true>(x, w, out, M, N, K, 0, fuse);
 }
 
 // kUnroll: k-blocks whose weight loads a thread keeps in flight.  8 costs 128 registers, so that two blocks
@@ -438,6 +539,65 @@ PB_EXPORT int pb_gemm_skinny_supported(int mode, int M, int N, int K) {
     if (mode == kSwiGLU) return (N % 16 == 0) ? 1 : 0;       // N = 2 * inter, inter % 8 == 0
     if (mode != kPlain) return 0;
     return (N % kRows == 0) ? 1 : 0;
+}
+
+// The fused forms take what the 32-byte loads take: K a multiple of 64, 32-byte aligned operands.
+PB_EXPORT int pb_gemm_skinny_fused_supported(int mode, int M, int N, int K) {
+    return (pb_gemm_skinny_supported(mode, M, N, K) && K % 64 == 0) ? 1 : 0;
+}
+
+// residual[M, N] (float32) += x[M, K] W[N, K]^T.  With next_w (float32 [N], the weight of the RMSNorm that follows) also
+// y[M, N] = bfloat16(residual * next_w) and parts[N / 16, M] = each block's part of sum_n residual[m, n]^2, for
+// pb_gemm_skinny_scaled.
+PB_EXPORT int pb_gemm_skinny_accumulate(const void* x, const void* w, float* residual, int M, int N, int K, const float* next_w,
+                                        void* y, float* parts, cudaStream_t stream) {
+    if (!pb_gemm_skinny_fused_supported(kPlain, M, N, K)) return PB_ERR_BAD_SIZE;
+    if ((((uintptr_t)x | (uintptr_t)w) & 31) != 0) return PB_ERR_BAD_SIZE;
+    if (next_w != nullptr && (y == nullptr || parts == nullptr)) return PB_ERR_BAD_SIZE;
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)w;
+    SkinnyFuse fuse{};
+    fuse.next_w = next_w;
+    fuse.y = (bf16*)y;
+    fuse.part_out = parts;
+    const int tiles = N / kRows;
+    const bool many = tiles > 2 * sm_count();
+#define PB_ACC(NT, KU, PRE) \
+    return launch_pdl(gemm_skinny_accumulate_kernel<NT, KU, PRE>, tiles, kWarps * 32, 0, stream, xp, wp, residual, M, N, K, fuse)
+    if (M <= 8) { if (many) PB_ACC(1, 2, 2); PB_ACC(1, 4, 2); }
+    if (many) PB_ACC(2, 2, 0);
+    PB_ACC(2, 4, 0);
+#undef PB_ACC
+}
+
+// out = (y W^T) * rsqrt(sum_m / K + eps) per token m, sum_m = the n_parts parts of parts[n_parts, M] added in order:
+// with y and parts from pb_gemm_skinny_accumulate this is rmsnorm(residual) W^T.  mode 0: bfloat16 [M, N]; mode 1: the
+// SwiGLU form, bfloat16 [M, N / 2].
+PB_EXPORT int pb_gemm_skinny_scaled(int mode, const void* y, const void* w, void* out, int M, int N, int K, const float* parts,
+                                    int n_parts, float eps, cudaStream_t stream) {
+    if (!pb_gemm_skinny_fused_supported(mode, M, N, K) || parts == nullptr || n_parts <= 0) return PB_ERR_BAD_SIZE;
+    if (n_parts > kMaxParts || n_parts % 4 || (((uintptr_t)parts) & 15)) return PB_ERR_BAD_SIZE;
+    if ((((uintptr_t)y | (uintptr_t)w) & 31) != 0) return PB_ERR_BAD_SIZE;
+    const bf16* yp = (const bf16*)y;
+    const bf16* wp = (const bf16*)w;
+    SkinnyFuse fuse{};
+    fuse.part_in = parts;
+    fuse.n_parts = n_parts;
+    fuse.eps = eps;
+    const int tiles = (mode == kSwiGLU) ? N / 2 / 8 : N / kRows;
+    const int inter = mode == kSwiGLU ? N / 2 : 0;
+    const bool many = tiles > 2 * sm_count();
+#define PB_SCALED(NT, MODE, KU, PRE) \
+    return launch_pdl(gemm_skinny_scaled_kernel<NT, MODE, KU, PRE>, tiles, kWarps * 32, 0, stream, yp, wp, (bf16*)out, M, N, K, inter, fuse)
+    if (M <= 8) {
+        if (mode == kSwiGLU) { if (many) PB_SCALED(1, kSwiGLU, 2, 2); PB_SCALED(1, kSwiGLU, 4, 2); }
+        if (many) PB_SCALED(1, kPlain, 2, 2);
+        PB_SCALED(1, kPlain, 4, 2);
+    }
+    if (mode == kSwiGLU) { if (many) PB_SCALED(2, kSwiGLU, 2, 0); PB_SCALED(2, kSwiGLU, 4, 0); }
+    if (many) PB_SCALED(2, kPlain, 2, 0);
+    PB_SCALED(2, kPlain, 4, 0);
+#undef PB_SCALED
 }
 
 // mode 0: out[M, N] (out_dtype bfloat16 or float32).  mode 1: W = [gate rows; up rows] with N = 2 * inter,

@@ -101,7 +101,9 @@ class DecoderModel(Part):
         residual = ctx.scratch("residual", (ctx.n_tokens, s.hidden), torch.float32)
         ops.embed(self.embed, ctx.token_ids, residual, s.embedding_multiplier)
         delta = None
-        for call in s.run_order:
+        for i, call in enumerate(s.run_order):
+            following = self.blocks[s.run_order[i + 1].block] if i + 1 < len(s.run_order) else None
+            ctx.next_norm = getattr(following, "mixer_norm", None)
             delta = self.blocks[call.block].forward(ctx, residual, delta, ctx.cache(call.cache))
         rows = ctx.logit_rows
         logits = ctx.scratch("logits", (rows.numel(), s.vocab_size), torch.float32)

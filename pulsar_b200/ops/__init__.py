@@ -59,6 +59,9 @@ _SIGNATURES = {
     "pb_prefill_tcgen05_error": [],
     "pb_gemm_skinny": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_gemm_skinny_supported": [_I, _I, _I, _I],
+    "pb_gemm_skinny_fused_supported": [_I, _I, _I, _I],
+    "pb_gemm_skinny_accumulate": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
+    "pb_gemm_skinny_scaled": [_I, _P, _P, _P, _I, _I, _I, _P, _I, _F, _P],
     "pb_gemm_tcgen05": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_gemm_tcgen05_supported": [_I, _I, _I, _I],
     "pb_gemm_tcgen05_error": [],
@@ -275,6 +278,70 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: boo
     _cuda(a, w, out)
     assert out.shape == (m, n // 2 if swiglu else n)
     check(fn("pb_gemm_skinny")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream()), "gemm_skinny")
+    return True
+
+
+# Steps of up to 16 tokens (bfloat16): the output and down projections add their result to the float32 residual
+# stream inside the product (no bfloat16 rounding of it, no addition in the norm kernel), and the down projection
+# prepares the next layer's first norm, which the q/k/v product then applies itself (one norm kernel per layer
+# less).  PULSAR_FUSED_NORM=0 turns both off.  The same for the norm in front of gate/up is built and tested but
+# off: that product has thousands of short-lived blocks, and what each of them adds at its end costs more than the
+# norm kernel it saves (measured: 3.77 against 3.61 ms per step at batch 8); PULSAR_FUSED_NORM_MLP=1 turns it on.
+FUSED_NORM = os.environ.get("PULSAR_FUSED_NORM", "1") != "0"
+FUSED_NORM_MLP = os.environ.get("PULSAR_FUSED_NORM_MLP", "0") != "0"
+
+
+def _aligned32(*tensors) -> bool:
+    return all(t.data_ptr() % 32 == 0 for t in tensors)
+
+
+def fused_projection_supported(m: int, w: torch.Tensor, swiglu: bool = False) -> bool:
+    """Whether ``linear_prenormed`` / ``linear_accumulate`` take ``m`` tokens against the weight ``w`` [N, K]."""
+    return bool(FUSED_NORM and w.dtype == torch.bfloat16 and w.is_cuda and w.data_ptr() % 32 == 0
+                and fn("pb_gemm_skinny_fused_supported")(1 if swiglu else 0, m, w.shape[0], w.shape[1]))
+
+
+def linear_accumulate(a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, next_norm_weight: Optional[torch.Tensor] = None,
+                      prepared: Optional[torch.Tensor] = None, parts: Optional[torch.Tensor] = None) -> bool:
+    """residual (float32) += a @ w.T for up to 16 tokens: the projection's result goes into the residual stream
+    without a bfloat16 rounding and without a kernel for the addition.  With ``next_norm_weight`` (the weight of
+    the RMSNorm that follows) the kernel also prepares that norm: ``prepared`` [M, N] bfloat16 = residual *
+    weight and ``parts`` [N / 16, M] float32 = each block's part of the rows' sums of squares, which
+    ``linear_prenormed`` takes.  Returns False, having done nothing, when the sizes or dtypes are not the kernel's."""
+    m, k = a.shape
+    n = w.shape[0]
+    if (not FUSED_NORM or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or residual.dtype != torch.float32
+            or w.shape[1] != k or residual.shape != (m, n)):
+        return False
+    if not fn("pb_gemm_skinny_fused_supported")(0, m, n, k) or not _aligned32(a, w):
+        return False
+    _cuda(a, w, residual, next_norm_weight, prepared, parts)
+    if next_norm_weight is not None:
+        assert next_norm_weight.dtype == torch.float32 and next_norm_weight.numel() == n
+        assert prepared.dtype == torch.bfloat16 and prepared.shape == (m, n)
+        assert parts.dtype == torch.float32 and parts.numel() >= (n // 16) * m
+    check(fn("pb_gemm_skinny_accumulate")(_p(a), _p(w), _p(residual), m, n, k, _p(next_norm_weight), _p(prepared), _p(parts),
+                                          stream()), "gemm_skinny_accumulate")
+    return True
+
+
+def linear_prenormed(prepared: torch.Tensor, parts: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor,
+                     swiglu: bool = False) -> bool:
+    """out = rmsnorm(residual) @ w.T (or its SwiGLU form) from what ``linear_accumulate`` prepared: the product of
+    ``prepared`` (residual * norm weight, bfloat16) with each token's sums scaled by rsqrt(mean(residual^2) + eps),
+    the mean from ``parts``.  Returns False, having done nothing, when the sizes or dtypes are not the kernel's."""
+    m, k = prepared.shape
+    n = w.shape[0]
+    if (not FUSED_NORM or prepared.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16
+            or w.shape[1] != k or parts.dtype != torch.float32 or k % 64 or k // 16 > 512):
+        return False
+    mode = 1 if swiglu else 0
+    if not fn("pb_gemm_skinny_fused_supported")(mode, m, n, k) or not _aligned32(prepared, w):
+        return False
+    _cuda(prepared, parts, w, out)
+    assert out.shape == (m, n // 2 if swiglu else n) and parts.numel() >= (k // 16) * m
+    check(fn("pb_gemm_skinny_scaled")(mode, _p(prepared), _p(w), _p(out), m, n, k, _p(parts), k // 16, float(eps), stream()),
+          "gemm_skinny_scaled")
     return True
 
 

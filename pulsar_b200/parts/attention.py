@@ -10,6 +10,7 @@ from ..cache.manager import CacheNeed
 from ..config.registry import MIXERS, POSITIONS
 from ..config.specs import MixerSpec
 from .base import CacheView, Mixer, StepContext, WeightSpec
+from .norm import RMSNorm, accumulate_and_prepare
 
 
 @MIXERS.register("attention")
@@ -74,6 +75,35 @@ class Attention(Mixer):
         n_kv = s.n_kv_heads if s.own_kv else 0
         qkv = ctx.scratch("attn.qkv", (n, (s.n_heads + 2 * n_kv) * s.head_dim))
         ops.linear(h, self.w_qkv, qkv)
+        o = self._attend(ctx, qkv, cache)
+        out = ctx.scratch("attn.out", (n, s.hidden))
+        ops.linear(o.view(n, s.n_heads * s.head_dim), self.w_o, out)
+        return out
+
+    def forward_normed(self, ctx: StepContext, residual: torch.Tensor, norm, cache: CacheView, next_norm=None) -> bool:
+        s = self.spec
+        n = ctx.n_tokens
+        if n > 16 or not isinstance(norm, RMSNorm) or self.dtype != torch.bfloat16:
+            return False
+        if not (ops.fused_projection_supported(n, self.w_qkv) and ops.fused_projection_supported(n, self.w_o)):
+            return False
+        n_kv = s.n_kv_heads if s.own_kv else 0
+        qkv = ctx.scratch("attn.qkv", (n, (s.n_heads + 2 * n_kv) * s.head_dim))
+        prepared = ctx.prepared_norms.pop(id(norm), None)
+        if prepared is None or not ops.linear_prenormed(prepared[0], prepared[1], norm.spec.eps, self.w_qkv, qkv):
+            ops.linear(norm.forward(ctx, residual, None), self.w_qkv, qkv)
+        o = self._attend(ctx, qkv, cache)
+        ctx.prepared_norms.clear()              # the residual changes now
+        if not accumulate_and_prepare(ctx, o.view(n, s.n_heads * s.head_dim), self.w_o, residual,
+                                      next_norm if ops.FUSED_NORM_MLP else None):
+            raise ops.KernelError("attention: the output projection refused sizes it had declared supported")
+        return True
+
+    def _attend(self, ctx: StepContext, qkv: torch.Tensor, cache: CacheView) -> torch.Tensor:
+        """Per-head norm, rotation and cache write of the projected row, then attention: o [N, heads, head_dim]."""
+        s = self.spec
+        n = ctx.n_tokens
+        n_kv = s.n_kv_heads if s.own_kv else 0
         q = ctx.scratch("attn.q", (n, s.n_heads, s.head_dim))
         if self.position is not None:
             cos, sin = self.position.tables(ctx)
@@ -86,6 +116,4 @@ class Attention(Mixer):
                                s.qk_norm_eps or 0.0, s.n_heads, n_kv, s.head_dim, rotary, cache.page_size)
         o = ctx.scratch("attn.o", (n, s.n_heads, s.head_dim))
         ops.attention(ctx, q, cache, o, s.scale, s.window)
-        out = ctx.scratch("attn.out", (n, s.hidden))
-        ops.linear(o.view(n, s.n_heads * s.head_dim), self.w_o, out)
-        return out
+        return o

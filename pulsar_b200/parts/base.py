@@ -83,6 +83,10 @@ class StepContext:
         self.group_tables: List[torch.Tensor] = []                      # per group [S, width]
         self.group_slots: List[torch.Tensor] = []                       # per group [N]
         self.shared: Dict[object, object] = {}                          # per-step tables shared by layers
+        # What a product has prepared for the norm that follows it, by that norm's id: (residual * norm weight in
+        # the activation dtype, parts of the rows' sums of squares).  Valid while nothing else touches the residual.
+        self.prepared_norms: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+        self.next_norm = None                   # the first norm of the block that runs after the current one, if known
 
     def scratch(self, tag: str, shape: Sequence[int], dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return self.runner.scratch(tag, tuple(shape), dtype or self.dtype)
@@ -138,12 +142,25 @@ class Mixer(Part):
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: CacheView) -> torch.Tensor:
         raise NotImplementedError
 
+    def forward_normed(self, ctx: StepContext, residual: torch.Tensor, norm: Norm, cache: CacheView,
+                       next_norm: Optional[Norm] = None) -> bool:
+        """Optional short cut for steps of a few tokens: this part applies ``norm`` to the float32 ``residual``
+        itself and adds its contribution to ``residual`` inside its last product, so that neither the norm nor the
+        addition is a kernel of its own.  ``next_norm`` is the norm that will be applied to the residual next (by
+        whoever follows); the part may prepare it (``ctx.prepared_norms``).  Returns False, having done nothing,
+        when it cannot (the block then runs the norm and ``forward``)."""
+        return False
+
 
 class FeedForward(Part):
     """forward(ctx, h [N, hidden]) -> delta [N, hidden]."""
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_normed(self, ctx: StepContext, residual: torch.Tensor, norm: Norm, next_norm: Optional[Norm] = None) -> bool:
+        """As ``Mixer.forward_normed``."""
+        return False
 
 
 class Block(Part):

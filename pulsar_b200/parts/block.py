@@ -36,8 +36,15 @@ class PreNormBlock(Block):
         return sum(p.weight_bytes() for p in self.parts)
 
     def forward(self, ctx: StepContext, residual: torch.Tensor, delta: Optional[torch.Tensor],
-                cache: CacheView) -> torch.Tensor:
-        h = self.mixer_norm.forward(ctx, residual, delta)
-        delta = self.mixer.forward(ctx, h, cache)
+                cache: CacheView) -> Optional[torch.Tensor]:
+        # With nothing pending, a part may take the norm before it and the addition behind it into its own products
+        # (steps of a few tokens); otherwise the norm kernel adds what is pending and normalises.
+        if delta is not None or not self.mixer.forward_normed(ctx, residual, self.mixer_norm, cache, self.feed_forward_norm):
+            ctx.prepared_norms.clear()
+            h = self.mixer_norm.forward(ctx, residual, delta)
+            delta = self.mixer.forward(ctx, h, cache)
+        if delta is None and self.feed_forward.forward_normed(ctx, residual, self.feed_forward_norm, ctx.next_norm):
+            return None
+        ctx.prepared_norms.clear()
         h = self.feed_forward_norm.forward(ctx, residual, delta)
         return self.feed_forward.forward(ctx, h)

@@ -9,6 +9,7 @@ from .. import ops
 from ..config.registry import FEED_FORWARDS
 from ..config.specs import FeedForwardSpec
 from .base import FeedForward, StepContext, WeightSpec
+from .norm import RMSNorm, accumulate_and_prepare
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -36,6 +37,21 @@ class SwiGLU(FeedForward):
 
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
+
+    def forward_normed(self, ctx: StepContext, residual: torch.Tensor, norm, next_norm=None) -> bool:
+        s, n = self.spec, ctx.n_tokens
+        if n > 16 or not isinstance(norm, RMSNorm) or self.dtype != torch.bfloat16:
+            return False
+        if not (ops.fused_projection_supported(n, self.w_gate_up, swiglu=True) and ops.fused_projection_supported(n, self.w_down)):
+            return False
+        act = ctx.scratch("mlp.act", (n, s.intermediate))
+        prepared = ctx.prepared_norms.pop(id(norm), None) if ops.FUSED_NORM_MLP else None
+        if prepared is None or not ops.linear_prenormed(prepared[0], prepared[1], norm.spec.eps, self.w_gate_up, act, swiglu=True):
+            ops.gated_linear(ctx, norm.forward(ctx, residual, None), self.w_gate_up, act)
+        ctx.prepared_norms.clear()              # the residual changes now
+        if not accumulate_and_prepare(ctx, act, self.w_down, residual, next_norm):
+            raise ops.KernelError("swiglu: the down projection refused sizes it had declared supported")
+        return True
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         s, n = self.spec, ctx.n_tokens

@@ -35,3 +35,19 @@ class RMSNorm(Norm):
         out = ctx.scratch(self.tag + (".rows" if rows is not None else ""), (n, self.spec.size))
         ops.add_rmsnorm(residual, delta, self.weight, self.spec.eps, out, rows=rows)
         return out
+
+
+def accumulate_and_prepare(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, next_norm) -> bool:
+    """residual += a @ w.T inside the product (a few tokens, bfloat16), and, where the norm that follows is an
+    RMSNorm, that norm prepared by the same kernel and left in ``ctx.prepared_norms`` for whoever applies it
+    (``ops.linear_accumulate`` / ``ops.linear_prenormed``).  False, having done nothing, when the product declines."""
+    n, width = residual.shape
+    if isinstance(next_norm, RMSNorm) and next_norm.spec.size == width and width % 16 == 0:
+        tag = next_norm.tag
+        prepared = ctx.scratch(tag + ".prepared", (n, width), torch.bfloat16)
+        parts = ctx.scratch(tag + ".parts", ((width // 16) * n,), torch.float32)
+        if ops.linear_accumulate(a, w, residual, next_norm.weight, prepared, parts):
+            ctx.prepared_norms[id(next_norm)] = (prepared, parts)
+            return True
+        return False
+    return ops.linear_accumulate(a, w, residual)

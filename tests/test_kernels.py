@@ -195,6 +195,69 @@ def test_gemm_skinny(m, n, k):
     close(act, gate * torch.sigmoid(gate) * up, 1e-2, "swiglu")
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(96, 192), (4096, 4096), (1024, 12288), (64, 2048), (192, 832), (640, 5120)])
+def test_gemm_skinny_adds_into_the_residual_and_prepares_the_norm_that_follows(m, n, k):
+    """The product that adds its result to the float32 residual stream in place and prepares the RMSNorm behind it
+    (residual * norm weight in bfloat16, the blocks' parts of the rows' sums of squares), and the product that
+    takes tokens prepared so and scales each token's sums, plain and with the SwiGLU epilogue, against float64.
+    One residual row is all zero (only eps keeps it finite), one is large, so that the per-token factor shows."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(17)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).bfloat16()
+    w[n // 3, (5 * k) // 7] = 3.0
+    res = torch.randn(m, n, generator=g) * 2.0
+    res[m // 2] *= 40.0
+    delta = a.double() @ w.double().T
+    if m > 2:
+        res[1] = 0.0
+        a[1] = 0.0
+        delta[1] = 0.0
+    want_res = res.double() + delta
+    res_dev = dev(res.clone())
+    assert ops.fused_projection_supported(m, dev(w))
+    assert ops.linear_accumulate(dev(a), dev(w), res_dev)
+    close(res_dev, want_res, 2e-5, "accumulate")
+    # once more, now preparing the norm that follows: it adds, it does not overwrite
+    nw = 1.0 + 0.1 * torch.randn(n, generator=g)
+    eps = 3e-6
+    prepared = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    parts = torch.full(((n // 16) * m,), float("nan"), dtype=torch.float32, device="cuda")
+    assert ops.linear_accumulate(dev(a), dev(w), res_dev, dev(nw), prepared, parts)
+    x = res.double() + 2 * delta
+    close(res_dev, x, 2e-5, "accumulate twice")
+    close(prepared, x * nw.double(), 1e-2, "prepared operand")
+    close(parts.view(n // 16, m).sum(0), (x ** 2).sum(-1), 2e-5, "sums of squares")
+    # the product behind the norm: rows of W2 [n2, n]
+    n2 = 256
+    w2 = (torch.randn(n2, n, generator=g) / n ** 0.5).bfloat16()
+    exact = (x * torch.rsqrt((x ** 2).mean(-1, keepdim=True) + eps) * nw.double()) @ w2.double().T
+    out = torch.full((m, n2), float("nan"), dtype=torch.bfloat16, device="cuda")
+    if n % 64 == 0:
+        assert ops.linear_prenormed(prepared, parts, eps, dev(w2), out)
+        close(out, exact, 1.6e-2, "product behind the prepared norm")
+        if m > 2:
+            assert float(out[1].float().abs().max()) == 0.0
+        act = torch.full((m, n2 // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+        assert ops.linear_prenormed(prepared, parts, eps, dev(w2), act, swiglu=True)
+        gate, up = exact[:, :n2 // 2], exact[:, n2 // 2:]
+        close(act, gate * torch.sigmoid(gate) * up, 2e-2, "the same with the SwiGLU epilogue")
+    else:
+        assert not ops.linear_prenormed(prepared, parts, eps, dev(w2), out)
+
+
+def test_fused_projections_decline_other_sizes():
+    from pulsar_b200 import ops
+    w = torch.zeros(32, 96, dtype=torch.bfloat16, device="cuda")                  # K no multiple of 64
+    assert not ops.fused_projection_supported(4, w)
+    assert not ops.linear_accumulate(torch.zeros(4, 96, dtype=torch.bfloat16, device="cuda"), w, torch.zeros(4, 32, device="cuda"))
+    w = torch.zeros(32, 128, dtype=torch.bfloat16, device="cuda")
+    assert not ops.fused_projection_supported(17, w)                              # too many tokens
+    assert not ops.linear_accumulate(torch.zeros(17, 128, dtype=torch.bfloat16, device="cuda"), w, torch.zeros(17, 32, device="cuda"))
+    assert ops.fused_projection_supported(16, w)
+
+
 def test_gemm_skinny_declines_other_sizes():
     from pulsar_b200 import ops
     a = torch.zeros(17, 64, dtype=torch.bfloat16, device="cuda")

@@ -168,6 +168,25 @@ def test_steps_of_many_single_tokens(folders, name, n, dtype):
     _compare(got, ref, dtype)
 
 
+@pytest.mark.parametrize("norms", ["all_inside", "none_inside"])
+@pytest.mark.parametrize("name", ["D", "F"])
+def test_decoding_with_the_norms_inside_the_products_or_in_kernels_of_their_own(folders, name, norms, monkeypatch):
+    """Steps of a few tokens in bfloat16 take the residual addition, and the norm in front of q/k/v, into the weight-
+    streaming products.  The same replay with the norm in front of gate/up inside its product too, and with
+    everything in kernels of its own: all against the plain implementation."""
+    from pulsar_b200 import ops
+    monkeypatch.setattr(ops, "FUSED_NORM_MLP", norms == "all_inside")
+    monkeypatch.setattr(ops, "FUSED_NORM", norms == "all_inside")
+    raw, seed, page = TINY[name]
+    rng = random.Random(seed + 90)
+    requests = {f"r{i}": helpers.random_tokens(rng, n, raw["vocab_size"]) for i, n in enumerate([44, 71, 23, 50, 37])}
+    ref = _reference(folders[name], "bfloat16", requests)
+    trace = helpers.trace_mixed(requests, rng, max_live=3, portion=(2, 9), decode_tail=20)
+    got = _replay(folders[name], "bfloat16", trace, 3 * 128, page, max_running=3)
+    assert len(got) == sum(len(t) for t in requests.values())
+    _compare(got, ref, "bfloat16")
+
+
 @pytest.mark.parametrize("name", ["B", "D"])
 def test_portions_with_the_tcgen05_products(folders, name, monkeypatch):
     """The same replay with every projection of more than 16 rows on the tcgen05 / TMA kernel
