@@ -34,7 +34,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;                 // the usual case costs no clock read
     const long long t0 = clock64();
-    const long long limit = *(volatile long long*)&g_wait_limit;
+    // read through the read-only path: after an SM's first wait the limit comes from L1, not from L2 (a wait that
+    // blocks must not cost a round trip to L2 before it looks at its barrier again)
+    const long long limit = __ldg(&g_wait_limit);
     while (!mbar_try_wait(bar, parity)) {
         if (*abort_flag) return false;
         if (clock64() - t0 > limit) return false;

@@ -104,8 +104,8 @@ class Engine:
         self._inflight: Optional[_Inflight] = None          # the pass whose tokens have not been read yet
         self._unclaimed: List[Tuple[int, int, bool]] = []   # events booked outside ``step``
         self._host_ids: List[Optional[torch.Tensor]] = [None, None, None]
-        self._host_status = [torch.zeros(4, dtype=torch.int32, pin_memory=True) for _ in self._host_ids]
-        self._status_dev = torch.zeros(4, dtype=torch.int32, device=cfg.device)
+        self._host_status = [torch.zeros(8, dtype=torch.int32, pin_memory=True) for _ in self._host_ids]
+        self._status_dev = torch.zeros(8, dtype=torch.int32, device=cfg.device)
         self._host_next = 0
         self._failed: Optional[BaseException] = None
 
@@ -271,7 +271,7 @@ class Engine:
         """Wait for a pass's sampled ids and book them: events ``(seq_id, token, finished)``."""
         flight.event.synchronize()
         if flight.status is not None:
-            what = ops.describe_wait_words(flight.status[:3].tolist())
+            what = ops.describe_wait_words(flight.status[:ops.N_WAIT_WORDS].tolist())
             if what is not None:
                 # the pass's tokens come from a kernel that gave up: none of them is booked, and nothing runs after it
                 self._failed = ops.DeviceWaitError(what)

@@ -65,6 +65,9 @@ _SIGNATURES = {
     "pb_gemm_tcgen05": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_gemm_tcgen05_supported": [_I, _I, _I, _I],
     "pb_gemm_tcgen05_error": [],
+    "pb_gemm_tcgen05_stream": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
+    "pb_gemm_tcgen05_stream_supported": [_I, _I, _I, _I],
+    "pb_gemm_tcgen05_stream_wait_control": [ctypes.c_longlong, _I, _P],
     "pb_gemm_tcgen05_wait_control": [ctypes.c_longlong, _I, _P],
     "pb_gemm_tcgen05_wait_selftest": [_P],
     "pb_prefill_tcgen05_wait_control": [ctypes.c_longlong, _I, _P],
@@ -362,6 +365,40 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bo
     return True
 
 
+# Which products of 17 to 128 tokens take this library's weight-streaming tcgen05 kernel instead of the library
+# product: "auto" those whose weights have tiles for four rounds of all SMs or more (the head: there the kernel's
+# persistent form is ahead of the library, 6.1 against 6.0 TB/s at 64 tokens); "1" all of them (measured behind the
+# library for the projections of a layer at the 8B sizes: see profiles/); "0" none.
+STREAM_GEMM = os.environ.get("PULSAR_GEMM_STREAM", "auto")
+_STREAM_MIN_ROWS = 4 * 148 * 128
+
+
+def _stream_wanted(m: int, n: int) -> bool:
+    if m > 128 or STREAM_GEMM == "0" or GEMM_BACKEND == "library":
+        return False
+    return STREAM_GEMM == "1" or n >= _STREAM_MIN_ROWS
+
+
+def gemm_tcgen05_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> bool:
+    """The weight-streaming tcgen05 / TMA product for up to 128 tokens (bfloat16 operands, float32 accumulation
+    in tensor memory, K split over the blocks of a cluster).  ``swiglu`` as in ``gemm_skinny``.  Returns False,
+    having done nothing, when the sizes are not the kernel's."""
+    m, k = a.shape
+    n = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k:
+        return False
+    mode = 1 if swiglu else 0
+    if not fn("pb_gemm_tcgen05_stream_supported")(mode, m, n, k):
+        return False
+    _cuda(a, w, out)
+    assert out.shape == (m, n // 2 if swiglu else n)
+    status = fn("pb_gemm_tcgen05_stream")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream())
+    if status == -3:
+        return False                 # sizes that leave no room for its ring of stages
+    check(status, "gemm_tcgen05_stream")
+    return True
+
+
 def gemm_tcgen05_error() -> int:
     """0 unless a block of the tcgen05 product ever gave up a bounded wait (synchronises)."""
     return int(fn("pb_gemm_tcgen05_error")())
@@ -373,9 +410,12 @@ def gemm_tcgen05_error() -> int:
 # memory and returns, and what the kernel wrote is then not to be trusted.  The reference's engine turns a step
 # that cannot go on into an exception (pulsar-core/src/runtime/engine.cpp:809-814) and its Python layer
 # poisons the engine (pulsar/src/pulsar/rt/sync.py:21-34); the words below are how this engine learns of it.
-WAIT_WORD_NAMES = ("tcgen05 product", "tcgen05 attention, one head per block", "tcgen05 attention, two heads per block")
+WAIT_WORD_NAMES = ("tcgen05 product", "tcgen05 attention, one head per block", "tcgen05 attention, two heads per block",
+                   "tcgen05 product for up to 128 tokens")
+N_WAIT_WORDS = len(WAIT_WORD_NAMES)
 WAIT_ROLES = {2: "the TMA producer", 3: "the MMA issuer", 4: "the epilogue or softmax warps", 9: "the wait self-test"}
 _wait_words = {}
+_check_buf = {}
 
 
 class DeviceWaitError(KernelError):
@@ -383,25 +423,27 @@ class DeviceWaitError(KernelError):
 
 
 def wait_word_addresses() -> "ctypes.Array":
-    """Device addresses of the three error words of the current device (looked up once per device)."""
+    """Device addresses of the error words of the current device (looked up once per device)."""
     dev = torch.cuda.current_device()
     got = _wait_words.get(dev)
     if got is None:
-        got = (ctypes.c_void_p * 3)()
+        got = (ctypes.c_void_p * N_WAIT_WORDS)()
         one = (ctypes.c_void_p * 1)()
         two = (ctypes.c_void_p * 2)()
-        if fn("pb_gemm_tcgen05_wait_control")(0, -1, one) != 0 or fn("pb_prefill_tcgen05_wait_control")(0, -1, two) != 0:
+        three = (ctypes.c_void_p * 1)()
+        if (fn("pb_gemm_tcgen05_wait_control")(0, -1, one) != 0 or fn("pb_prefill_tcgen05_wait_control")(0, -1, two) != 0
+                or fn("pb_gemm_tcgen05_stream_wait_control")(0, -1, three) != 0):
             raise KernelError("the addresses of the wait error words could not be had")
-        got[0], got[1], got[2] = one[0], two[0], two[1]
+        got[0], got[1], got[2], got[3] = one[0], two[0], two[1], three[0]
         _wait_words[dev] = got
     return got
 
 
 def gather_wait_words(out: torch.Tensor) -> None:
-    """out[:3] (int32, device) = the three error words, read in the stream behind whatever was launched before."""
+    """out[:N_WAIT_WORDS] (int32, device) = the error words, read in the stream behind whatever was launched before."""
     _cuda(out)
-    assert out.dtype == torch.int32 and out.numel() >= 3
-    check(fn("pb_gather_words")(wait_word_addresses(), 3, _p(out), stream()), "gather_words")
+    assert out.dtype == torch.int32 and out.numel() >= N_WAIT_WORDS
+    check(fn("pb_gather_words")(wait_word_addresses(), N_WAIT_WORDS, _p(out), stream()), "gather_words")
 
 
 def set_wait_limit(cycles: int) -> None:
@@ -409,14 +451,16 @@ def set_wait_limit(cycles: int) -> None:
     if cycles <= 0:
         raise ValueError("the wait limit must be positive")
     if fn("pb_gemm_tcgen05_wait_control")(int(cycles), -1, None) != 0 or \
-            fn("pb_prefill_tcgen05_wait_control")(int(cycles), -1, None) != 0:
+            fn("pb_prefill_tcgen05_wait_control")(int(cycles), -1, None) != 0 or \
+            fn("pb_gemm_tcgen05_stream_wait_control")(int(cycles), -1, None) != 0:
         raise KernelError("the wait limit could not be set")
 
 
 def set_wait_words(value: int) -> None:
     """Write all three error words (0 clears them once a failure has been dealt with)."""
     if fn("pb_gemm_tcgen05_wait_control")(0, int(value), None) != 0 or \
-            fn("pb_prefill_tcgen05_wait_control")(0, int(value), None) != 0:
+            fn("pb_prefill_tcgen05_wait_control")(0, int(value), None) != 0 or \
+            fn("pb_gemm_tcgen05_stream_wait_control")(0, int(value), None) != 0:
         raise KernelError("the wait error words could not be written")
 
 
@@ -434,12 +478,14 @@ def describe_wait_words(words) -> Optional[str]:
 
 
 def check_wait_words() -> None:
-    """Read the three words now (synchronises) and raise DeviceWaitError if one is set."""
-    words = (gemm_tcgen05_error(), prefill_tcgen05_error())
-    if any(words):
-        buf = torch.zeros(4, dtype=torch.int32, device="cuda")
-        gather_wait_words(buf)
-        raise DeviceWaitError(describe_wait_words(buf[:3].tolist()))
+    """Read the words now (synchronises) and raise DeviceWaitError if one is set."""
+    buf = _check_buf.get(torch.cuda.current_device())
+    if buf is None:
+        buf = _check_buf[torch.cuda.current_device()] = torch.zeros(8, dtype=torch.int32, device="cuda")
+    gather_wait_words(buf)
+    what = describe_wait_words(buf[:N_WAIT_WORDS].tolist())
+    if what is not None:
+        raise DeviceWaitError(what)
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -456,6 +502,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError(f"linear: operand dtypes {a.dtype} / {w.dtype} must both be float32 or both bfloat16")
     if gemm_skinny(a, w, out):
         return
+    if _stream_wanted(a.shape[0], w.shape[0]) and gemm_tcgen05_stream(a, w, out):
+        return
     if GEMM_BACKEND == "tcgen05" and gemm_tcgen05(a, w, out):
         return
     if out.dtype == torch.bfloat16:
@@ -470,6 +518,8 @@ def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tenso
     take one kernel that never writes the [M, 2I] intermediate; otherwise the product followed by the
     gating kernel."""
     if gemm_skinny(a, w_gate_up, out, swiglu=True):
+        return
+    if _stream_wanted(a.shape[0], w_gate_up.shape[0]) and gemm_tcgen05_stream(a, w_gate_up, out, swiglu=True):
         return
     # Between 17 and 128 rows the product is still bound by streaming the weights, which the library's small
     # tiles do faster (4.5 against 3.2 TB/s at the 8B sizes) than the tcgen05 kernel's 128 x 256 tiles.

@@ -270,6 +270,34 @@ def test_gemm_skinny_declines_other_sizes():
     assert float(out.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("m", [17, 33, 64, 100, 128])
+@pytest.mark.parametrize("n,k", [(256, 64), (4096, 4096), (1024, 12288), (6144, 4096), (264, 200), (24576, 512), (1000, 1536),
+                                 (48, 8192)])
+def test_gemm_tcgen05_stream(m, n, k):
+    """The weight-streaming tcgen05 product for 17 to 128 tokens against float64: tiles that hang over the rows of W
+    and the tail of K, one to eight slices of K per cluster (few tiles) and none (many tiles, two blocks per SM),
+    float32 and bfloat16 outputs, the SwiGLU epilogue; weights made large in places so that a wrong swizzle,
+    descriptor or owner of a column would show."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(15)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).bfloat16()
+    w[n // 3, (5 * k) // 7] = 3.0
+    w[n - 1, k - 1] = -2.0
+    a[m - 1, k - 1] = 4.0
+    ref = a.double() @ w.double().T
+    for dt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 1e-2)):
+        out = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
+        assert ops.gemm_tcgen05_stream(dev(a), dev(w), out)
+        close(out, ref, tol, f"plain {dt}")
+    inter = n // 2
+    gate, up = ref[:, :inter], ref[:, inter:]
+    act = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops.gemm_tcgen05_stream(dev(a), dev(w), act, swiglu=True)
+    close(act, gate * torch.sigmoid(gate) * up, 1e-2, "swiglu")
+    ops.check_wait_words()
+
+
 @pytest.mark.parametrize("m,n,k", [(17, 256, 64), (128, 512, 128), (100, 320, 72), (300, 1000, 4096), (2048, 1024, 512),
                                    (129, 264, 200)])
 def test_gemm_tcgen05(m, n, k):

@@ -168,6 +168,25 @@ def test_steps_of_many_single_tokens(folders, name, n, dtype):
     _compare(got, ref, dtype)
 
 
+@pytest.mark.parametrize("name,n", [("D", 40), ("F", 72)])
+def test_steps_of_many_single_tokens_on_the_weight_streaming_tcgen05_product(folders, name, n, monkeypatch):
+    """The same large decode steps with every projection of 17 to 128 tokens on this library's weight-streaming
+    tcgen05 kernel (slices of K over the blocks of a cluster, SwiGLU in its epilogue) instead of the library product."""
+    from pulsar_b200 import ops
+    monkeypatch.setattr(ops, "STREAM_GEMM", "1")
+    raw, seed, page = TINY[name]
+    rng = random.Random(seed + 170 + n)
+    tail = 5
+    lens = [RAGGED[i % len(RAGGED)] % 70 + tail + 1 + (i % 5) for i in range(n)]
+    reqs = {f"r{i}": helpers.random_tokens(rng, ln, raw["vocab_size"]) for i, ln in enumerate(lens)}
+    ref = _reference(folders[name], "bfloat16", reqs)
+    trace = trace_many_decoding(reqs, tail, 9, list(reqs))
+    got = _replay(folders[name], "bfloat16", trace, sum(-(-len(t) // 64) * 64 for t in reqs.values()), page, max_running=n)
+    assert len(got) == n * (tail + 1)
+    _compare(got, ref, "bfloat16")
+    ops.check_wait_words()
+
+
 @pytest.mark.parametrize("norms", ["all_inside", "none_inside"])
 @pytest.mark.parametrize("name", ["D", "F"])
 def test_decoding_with_the_norms_inside_the_products_or_in_kernels_of_their_own(folders, name, norms, monkeypatch):
