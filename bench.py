@@ -63,14 +63,40 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clocks and throttle reasons while a timed region runs: NVML every 5 ms from a thread of this
+    process (dozens of samples for a region of a few hundred ms), nvidia-smi every 100 ms where NVML cannot be had.
+    It only reads."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self):
-        self.rows, self.proc = [], None
+        self.rows, self.proc, self.thread, self.stop_flag = [], None, None, threading.Event()
+
+    def _nvml_loop(self, nvml, handle):
+        bits = [getattr(nvml, n, 0) for n in ("nvmlClocksThrottleReasonHwSlowdown", "nvmlClocksThrottleReasonHwThermalSlowdown",
+                                              "nvmlClocksThrottleReasonSwThermalSlowdown", "nvmlClocksThrottleReasonSwPowerCap")]
+        mx = nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM)
+        while not self.stop_flag.is_set():
+            try:
+                sm = nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)
+                reasons = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.rows.append([str(sm), str(mx)] + ["Active" if reasons & b else "Not Active" for b in bits])
+            except Exception:
+                break
+            time.sleep(0.005)
 
     def start(self):
+        self.rows, self.stop_flag = [], threading.Event()
+        try:
+            import pynvml as nvml
+            nvml.nvmlInit()
+            handle = nvml.nvmlDeviceGetHandleByIndex(0)
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nvml, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                           "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -83,12 +109,14 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        self.stop_flag.set()
+        if self.thread is not None:
+            self.thread.join(timeout=1.0)
         if self.proc is not None:
             self.proc.terminate()
         sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
         mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in self.rows)]
+        reasons = [n for i, n in enumerate(self.NAMES) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in self.rows)]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
                 "samples": len(sm)}
 
@@ -111,6 +139,9 @@ def build_engine(shape: dict, n_layers: int, batch: int, context: int, max_chunk
         for pool in g.pools.values():
             pool.normal_(0.0, 1.0)
     return engine
+
+
+LAST = {}        # what the last time_decode saw beside its total: median step, index bytes per step
 
 
 def decode_bytes_of_shape(raw: dict, batch: int, context: float) -> float:
@@ -156,21 +187,40 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int, sampl
     if sampler is not None:
         sampler.start()
     launches0 = ops.LAUNCHES
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
+    h2d0 = runner.h2d_bytes
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]      # one after every step: no waits added
+    marks[0].record()
     for i in range(warmup, warmup + steps):
         one(i)
-    t1.record()
+        marks[i - warmup + 1].record()
     torch.cuda.synchronize()
-    seconds = t0.elapsed_time(t1) / 1e3
+    seconds = marks[0].elapsed_time(marks[-1]) / 1e3
     clocks = sampler.stop() if sampler is not None else None
     launches = ops.LAUNCHES - launches0
+    per_step = sorted(a.elapsed_time(b) for a, b in zip(marks, marks[1:]))
+    LAST["median_ms"] = per_step[len(per_step) // 2]
+    LAST["h2d_bytes_per_step"] = (runner.h2d_bytes - h2d0) / steps
+    LAST["table_width"] = int(max(cache.n_logical_pages(rid) for rid in rids))
     for rid in rids:
         runner.finish(rid)
     return seconds, launches, clocks
 
 
-def time_prefill(engine, tokens: int, reps: int = 7):
+def time_prefill(engine, tokens: int, reps: int = 7, backend: str = None):
+    """One step of ``tokens`` prompt tokens.  ``backend`` "tcgen05": every product on this library's own kernel."""
+    import torch
+    from pulsar_b200 import ops
+    from pulsar_b200.engine.runner import StepEntry
+    saved = ops.GEMM_BACKEND
+    if backend is not None:
+        ops.GEMM_BACKEND = backend
+    try:
+        return _time_prefill(engine, tokens, reps)
+    finally:
+        ops.GEMM_BACKEND = saved
+
+
+def _time_prefill(engine, tokens: int, reps: int):
     import torch
     from pulsar_b200.engine.runner import StepEntry
     gen = torch.Generator().manual_seed(2)
@@ -286,16 +336,28 @@ def main() -> int:
     mid_context = args.context - args.steps / 2.0
     achieved = decode_bytes(engine, args.batch, mid_context) / (seconds / args.steps) / 1e9
 
+    median_ms = LAST.get("median_ms")
     p_seconds = time_prefill(engine, 2048)
     p_flops = prefill_flops(raw, 2048)
     prefill = {"value": 2048 / p_seconds, "tokens": 2048, "ms": p_seconds * 1e3,
                "frac": p_flops / p_seconds / (pk["bf16_tflops"] * 1e12)}
+    own_seconds = time_prefill(engine, 2048, backend="tcgen05")
+    prefill_own = {"value": 2048 / own_seconds, "tokens": 2048, "ms": own_seconds * 1e3,
+                   "frac": p_flops / own_seconds / (pk["bf16_tflops"] * 1e12), "what": "every product on gemm_tcgen05"}
 
-    points = {}
+    points, index_bytes = {}, {}
     if not args.no_points:
-        for b in (1, 64):
+        for b in (1, 16, 32, 64):
             s, _, _ = time_decode(engine, b, args.context, args.steps, warmup)
             points[f"decode_b{b}"] = b * args.steps / s
+            points[f"decode_b{b}_hbm_frac"] = decode_bytes(engine, b, mid_context) / (s / args.steps) / 1e9 / pk["hbm_gbs"]
+            if b == 64:            # index arrays of a step: what travels with resident block tables, and what whole tables would be
+                index_bytes = {"batch": 64, "h2d_bytes_per_step": LAST["h2d_bytes_per_step"],
+                               "with_whole_tables": LAST["h2d_bytes_per_step"] + 4.0 * 64 * (-(-LAST["table_width"] // 64) * 64)}
+        for ctx in (2048, 3072):
+            if ctx < args.context:
+                s, _, _ = time_decode(engine, args.batch, ctx, args.steps, warmup)
+                points[f"decode_b{args.batch}_ctx{ctx}"] = args.batch * args.steps / s
     e2e = None
     if not args.no_e2e:
         e_seconds, h2d, d2h = time_e2e(engine, args.batch, args.context, args.steps, warmup)
@@ -314,8 +376,8 @@ def main() -> int:
                    "head_dim": shape["head_dim"], "intermediate": shape["intermediate_size"], "vocab": shape["vocab_size"],
                    "page_size": PAGE, "prompt_tokens": 2048,
                    "l2": f"inputs larger than L2 (weights {engine.model.weight_bytes(1) / 1e9:.0f} GB)", "peaks": pk["source"]},
-        "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-        "prefill": prefill,
+        "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "ms_per_step_median": median_ms,
+        "prefill": prefill, "prefill_own": prefill_own, "index_bytes": index_bytes,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"]},
         "points": points,

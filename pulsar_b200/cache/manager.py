@@ -192,6 +192,9 @@ class CacheManager:
             if need.kind == "state" and device is not None:
                 self.state[e] = torch.zeros((self.max_requests, *need.state_shape),
                                             dtype=need.state_dtype or dtype, device=device)
+        # Resident block tables (device): one row per state slot and group; a step sends only the page ids that its
+        # requests gained (the step function turns this on and asks for the tensors).
+        self.resident: Dict[int, torch.Tensor] = {}
         self._ids: Dict[Hashable, int] = {}         # request name -> the runtime's number for it
         self._names: Dict[int, Hashable] = {}
         self._pinned: set = set()                   # names that keep their number while they hold nothing
@@ -368,6 +371,27 @@ class CacheManager:
 
     def n_free_slots(self) -> int:
         return self._lib.ph_n_free_slots(self._h)
+
+    def set_resident_tables(self, on: bool) -> None:
+        """Whether the step packer sends whole block tables (off) or only the page ids that requests gained since
+        they were last sent, for tables that stay on the device (on).  Switching forgets what was sent."""
+        self._lib.ph_set_resident_tables(self._h, 1 if on else 0)
+        self.resident.clear()
+
+    def resident_table(self, group: int, width: int) -> Tuple[torch.Tensor, bool]:
+        """The device's resident table of a group, ``[max_requests, stride]`` with stride >= ``width``; grown (its
+        contents kept) when a request needs a wider row.  Second value: whether the tensor was (re)allocated."""
+        t = self.resident.get(group)
+        if t is not None and t.shape[1] >= width:
+            return t, False
+        stride = max(64, width)
+        if t is not None:
+            stride = max(stride, 2 * t.shape[1])
+        new = torch.full((self.max_requests, stride), -1, dtype=torch.int32, device=self.device)
+        if t is not None:
+            new[:, :t.shape[1]] = t
+        self.resident[group] = new
+        return new, True
 
     def check_consistency(self) -> None:
         """Every page is free or held by exactly one request, every slot likewise; used by tests."""

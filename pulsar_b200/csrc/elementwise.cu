@@ -419,6 +419,36 @@ PB_EXPORT int pb_scale_cap(float* x, long long n, float scale, float cap, cudaSt
 }
 
 // out[t] = table[ids[t]] * scale (float32 out; scale 1 for most architectures).
+namespace {
+// Block i serves sequence i of the step: it writes the page ids that the step brings for that sequence's row of the
+// resident table, then copies the row's first `width` entries into the step's table.
+__global__ void table_update_kernel(int* __restrict__ resident, int row_stride, const int* __restrict__ updates,
+                                    const int* __restrict__ rows, int width, int* __restrict__ out) {
+    const int i = blockIdx.x;
+    const int row = rows[i];
+    int* mine = resident + (size_t)row * row_stride;
+    const int n = updates[0];
+    for (int u = threadIdx.x; u < n; u += blockDim.x) {
+        const int* t = updates + 1 + 3 * u;
+        if (t[0] == row && t[1] >= 0 && t[1] < row_stride) mine[t[1]] = t[2];
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < width; j += blockDim.x) out[(size_t)i * width + j] = mine[j];
+}
+}  // namespace
+
+// The device's resident block tables (one row of `row_stride` page ids per state slot): `updates` = the count, then
+// (row, logical page, page id) triples that the step's requests gained; `rows` [n_seqs] = each sequence's row.
+// out [n_seqs, width] receives the rows' first `width` entries: the block table the step's kernels read.
+// width <= row_stride.  Entries beyond a request's pages hold whatever an earlier holder of the row left there.
+PB_EXPORT int pb_table_update(int* resident, int row_stride, const int* updates, const int* rows, int n_seqs, int width, int* out,
+                              cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (width <= 0 || width > row_stride) return PB_ERR_BAD_SIZE;
+    table_update_kernel<<<n_seqs, 128, 0, stream>>>(resident, row_stride, updates, rows, width, out);
+    return launch_status();
+}
+
 PB_EXPORT int pb_embed(int dtype, const void* table, const int* ids, float* out, int n, int width, int vocab, float scale,
                        cudaStream_t stream) {
     if (n <= 0) return 0;

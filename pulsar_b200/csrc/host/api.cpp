@@ -126,7 +126,30 @@ PH_EXPORT int ph_slots(void* h, int64_t rid, int group, int start, int n, int* o
 //   token_ids, positions, seq_of_token [N]; cu_q [S+1]; kv_len, state_slots [S]; logit_rows [R];
 //   per group: slots [N], block table [S, width] (-1 where a request has no page);
 //   if any entry takes its token from the device: move_dst, move_src [number of such entries].
+// With resident tables (ph_set_resident_tables) the device keeps a block-table row per state slot, and the per-group
+// table array is replaced by the page ids the step's requests gained since they were last sent:
+//   updates [1 + 3 * capacity]: the count, then (state slot, logical page, page id) triples; the capacity is the
+//   number of entries for a step of single tokens (a token adds one page at most; the array's length then does not
+//   change from step to step), else the exact count.  Packing marks those pages as sent.
 // offsets/lengths receive where each array starts and how long it is (7 + 2 * groups (+ 2) entries).
+namespace {
+// Page ids of group g that the entries' requests hold and the device's resident table does not yet.
+int unsynced_pages(const Cache& c, int g, int n_entries, const int64_t* rids) {
+    int n = 0;
+    for (int i = 0; i < n_entries; ++i) {
+        const Request* r = c.find(rids[i]);
+        n += std::max(0, (int)r->tables[g].size() - r->synced[g]);
+    }
+    return n;
+}
+int update_capacity(const Cache& c, int g, int n_entries, const int64_t* rids, bool all_single) {
+    const int exact = unsynced_pages(c, g, n_entries, rids);
+    return all_single ? std::max(exact, n_entries) : exact;
+}
+}  // namespace
+
+PH_EXPORT void ph_set_resident_tables(void* h, int on) { static_cast<Cache*>(h)->set_resident_tables(on != 0); }
+
 PH_EXPORT int ph_step_plan(void* h, int n_entries, const int64_t* rids, const int* n_tok, const int* tokens, const int* want_n,
                            const int* wants, const int* token_src, int n_sampled, int vocab, int table_bucket, int* starts,
                            int* slots, int* widths, int* bad_entry) {
@@ -188,7 +211,8 @@ PH_EXPORT int ph_step_plan(void* h, int n_entries, const int64_t* rids, const in
         for (int i = 0; i < n_entries; ++i) w = std::max(w, (int)c->find(rids[i])->tables[g].size());
         if (all_single && table_bucket > 0) w = (w + table_bucket - 1) / table_bucket * table_bucket;
         widths[g] = w;
-        total += align4(std::max(n, 1)) + align4(n_entries * w);
+        const int table_words = c->resident_tables() ? 1 + 3 * update_capacity(*c, g, n_entries, rids, all_single) : n_entries * w;
+        total += align4(std::max(n, 1)) + align4(table_words);
     }
     if (moved) total += 2 * align4(moved);
     return total;
@@ -197,14 +221,17 @@ PH_EXPORT int ph_step_plan(void* h, int n_entries, const int64_t* rids, const in
 PH_EXPORT int ph_step_pack(void* h, int n_entries, const int64_t* rids, const int* n_tok, const int* tokens, const int* want_n,
                            const int* wants, const int* token_src, const int* starts, const int* slots, const int* widths,
                            int* buf, int capacity, int* offsets, int* lengths) {
-    const Cache* c = static_cast<Cache*>(h);
+    Cache* c = static_cast<Cache*>(h);
     const int G = c->n_groups(), ps = c->page_size(), S = n_entries;
     int n = 0, rows = 0, moved = 0;
+    bool all_single = true;
     for (int i = 0; i < S; ++i) {
         n += n_tok[i];
         rows += want_n[i];
         if (token_src[i] >= 0) ++moved;
+        if (n_tok[i] != 1) all_single = false;
     }
+    const bool resident = c->resident_tables();
     int k = 0, total = 0;
     auto place = [&](int len) {
         offsets[k] = total;
@@ -213,7 +240,10 @@ PH_EXPORT int ph_step_pack(void* h, int n_entries, const int64_t* rids, const in
         total += align4(std::max(len, 1));
     };
     place(n); place(n); place(n); place(S + 1); place(S); place(S); place(rows);
-    for (int g = 0; g < G; ++g) { place(n); place(S * widths[g]); }
+    for (int g = 0; g < G; ++g) {
+        place(n);
+        place(resident ? 1 + 3 * update_capacity(*c, g, S, rids, all_single) : S * widths[g]);
+    }
     if (moved) { place(moved); place(moved); }
     if (total > capacity) return kTooSmall;
     int* tok = buf + offsets[0];
@@ -249,20 +279,39 @@ PH_EXPORT int ph_step_pack(void* h, int n_entries, const int64_t* rids, const in
         int* sl = buf + offsets[7 + 2 * g];
         int* table = buf + offsets[8 + 2 * g];
         const int w = widths[g];
-        std::fill(table, table + (size_t)S * w, -1);
+        if (resident) std::fill(table, table + lengths[8 + 2 * g], 0);
+        else std::fill(table, table + (size_t)S * w, -1);
         at = 0;
+        int n_upd = 0;
         for (int i = 0; i < S; ++i) {
-            const std::vector<int>& t = c->find(rids[i])->tables[g];
+            Request* r = c->find(rids[i]);
+            const std::vector<int>& t = r->tables[g];
             for (int j = 0; j < n_tok[i]; ++j) {
                 const int p = starts[i] + j;
                 const int page = t[p / ps];
                 if (page < 0) return kReleasedPage;
                 sl[at + j] = page * ps + p % ps;
             }
-            std::memcpy(table + (size_t)i * w, t.data(), sizeof(int) * t.size());
+            if (resident) {
+                for (int lp = r->synced[g]; lp < (int)t.size(); ++lp) {
+                    int* triple = table + 1 + 3 * n_upd++;
+                    triple[0] = r->slot;
+                    triple[1] = lp;
+                    triple[2] = t[lp];
+                }
+            } else {
+                std::memcpy(table + (size_t)i * w, t.data(), sizeof(int) * t.size());
+            }
             at += n_tok[i];
         }
+        if (resident) table[0] = n_upd;
     }
+    if (resident)           // only now, with every array written: these pages count as sent
+        for (int g = 0; g < G; ++g)
+            for (int i = 0; i < S; ++i) {
+                Request* r = c->find(rids[i]);
+                r->synced[g] = (int)r->tables[g].size();
+            }
     return total;
 }
 

@@ -50,8 +50,14 @@ int Cache::open(int64_t rid) {
     r.slot = slot;
     r.tables.resize(groups_.size());
     r.released.assign(groups_.size(), 0);
+    r.synced.assign(groups_.size(), 0);
     reqs_.emplace(rid, std::move(r));
     return slot;
+}
+
+void Cache::set_resident_tables(bool on) {
+    resident_tables_ = on;
+    for (auto& kv : reqs_) kv.second.synced.assign(groups_.size(), 0);      // nothing is known to be on the device
 }
 
 // Logical pages below this hold only keys that no query at position >= length sees.

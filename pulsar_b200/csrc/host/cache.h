@@ -53,6 +53,7 @@ struct Request {
     int slot = -1;
     std::vector<std::vector<int>> tables;     // per group: logical page -> page id, or -1 once released
     std::vector<int> released;                // per group: logical pages [0, released) were given back
+    std::vector<int> synced;                  // per group: logical pages [0, synced) are in the device's resident table
 };
 
 class Cache {
@@ -78,6 +79,10 @@ public:
     const FreeList& slots() const { return slots_; }
     const std::unordered_map<int64_t, Request>& requests() const { return reqs_; }
     bool windowed() const { return windowed_; }
+    // Resident tables: the device keeps one block-table row per state slot, and a step sends only the page ids that
+    // its requests gained since they were last sent (see ph_step_pack).
+    bool resident_tables() const { return resident_tables_; }
+    void set_resident_tables(bool on);
 
 private:
     int first_needed_page(const Group& g, int length) const;
@@ -87,6 +92,7 @@ private:
     FreeList slots_;
     std::unordered_map<int64_t, Request> reqs_;
     bool windowed_ = false;
+    bool resident_tables_ = false;
 };
 
 }  // namespace ph

@@ -13,7 +13,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 
-from .. import ops
+from .. import ops, profiling
 from ..cache.manager import CacheManager
 from ..config.engine_config import EngineConfig
 from ..sampling.sampler import GenerationParams, Sampler, make_generator
@@ -249,7 +249,8 @@ class Engine:
         sampled = [e.rid for e in plan if e.sample]
         sessions = [self._sessions[r] for r in sampled]
         states = {r: s.generator.get_state() for r, s in zip(sampled, sessions) if not s.params.greedy}
-        ids = self.sampler.sample_on_device(logits, [s.params for s in sessions], [s.generator for s in sessions])
+        with profiling.scope("launch (sampling)"):
+            ids = self.sampler.sample_on_device(logits, [s.params for s in sessions], [s.generator for s in sessions])
         slot = self._host_ids[self._host_next]
         if slot is None or slot.numel() < len(sampled):
             slot = self._host_ids[self._host_next] = torch.empty(max(64, len(sampled)), dtype=torch.int32, pin_memory=True)
@@ -269,7 +270,8 @@ class Engine:
 
     def _collect(self, flight: "_Inflight") -> List[Tuple[int, int, bool]]:
         """Wait for a pass's sampled ids and book them: events ``(seq_id, token, finished)``."""
-        flight.event.synchronize()
+        with profiling.scope("read (wait for the sampled ids)"):
+            flight.event.synchronize()
         if flight.status is not None:
             what = ops.describe_wait_words(flight.status[:ops.N_WAIT_WORDS].tolist())
             if what is not None:
@@ -312,7 +314,8 @@ class Engine:
         if self._unclaimed:
             events, self._unclaimed = self._unclaimed, []
             return events
-        plan = self.scheduler.schedule()
+        with profiling.scope("plan (the scheduler's decision)"):
+            plan = self.scheduler.schedule()
         if not plan:
             return []
         return self._collect(self._launch(plan))
@@ -332,7 +335,8 @@ class Engine:
         self._unclaimed = []
         while len(events) < n:
             if self._inflight is None:
-                plan = self.scheduler.schedule()
+                with profiling.scope("plan (the scheduler's decision)"):
+                    plan = self.scheduler.schedule()
                 if not plan:
                     if self.scheduler.has_work():
                         raise RuntimeError("the scheduler has work but nothing can run: the pool is held by parked "
@@ -342,7 +346,8 @@ class Engine:
             flight = self._inflight
             nxt = None
             if lookahead:
-                plan = self.scheduler.schedule(allow_preempt=False)
+                with profiling.scope("plan (the scheduler's decision)"):
+                    plan = self.scheduler.schedule(allow_preempt=False)
                 if plan:
                     nxt = self._launch(plan)
             self._inflight = nxt

@@ -15,10 +15,11 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import ctypes
 import gc
+import os
 
 import torch
 
-from .. import host, ops
+from .. import host, ops, profiling
 from ..cache.manager import CacheManager, OutOfPages
 from ..parts.base import CacheView, HostBatch, StepContext
 
@@ -71,13 +72,18 @@ class ModelRunner:
         self.steps_run = 0
         # Decode steps (one token per request) are launch-bound: their kernel sequence is
         # captured once per (batch size, block-table width) and replayed.
-        self.cuda_graphs = bool(cuda_graphs) and bool(getattr(model, "graph_safe", True))
+        self.cuda_graphs = bool(cuda_graphs) and bool(getattr(model, "graph_safe", True)) and not profiling.ENABLED
         self._graphs: Dict[tuple, Tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._graph_seen: Dict[tuple, int] = {}
         self._graph_epoch = -1
         self.graph_replays = 0
         self._capturing = False
         self.h2d_bytes = 0          # bytes of index arrays copied to the device so far
+        # The block tables stay on the device, one row per state slot; a step brings only the page ids its requests
+        # gained (a few hundred bytes for a decode step instead of the whole [sequences, width] table).
+        # PULSAR_RESIDENT_TABLES=0: every step brings whole tables.
+        self.resident_tables = os.environ.get("PULSAR_RESIDENT_TABLES", "1") != "0"
+        cache.set_resident_tables(self.resident_tables)
 
     # ------------------------------------------------------------------ memory
     def scratch(self, tag: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
@@ -217,13 +223,22 @@ class ModelRunner:
             if len(self._views) > 64:
                 self._views.clear()
             views = [dev[o:o + ln] for o, ln in zip(offsets, lengths)]
-            for g in range(n_groups):
-                views[8 + 2 * g] = views[8 + 2 * g].view(s, widths[g])
+            if not self.resident_tables:
+                for g in range(n_groups):
+                    views[8 + 2 * g] = views[8 + 2 * g].view(s, widths[g])
             self._views[key] = views
         (ctx.token_ids, ctx.positions, ctx.seq_of_token, ctx.cu_q, ctx.kv_len, ctx.state_slots, ctx.logit_rows) = views[:7]
         for g in range(n_groups):
             ctx.group_slots.append(views[7 + 2 * g])
-            ctx.group_tables.append(views[8 + 2 * g])
+            if self.resident_tables:
+                resident, fresh = cache.resident_table(g, widths[g])
+                if fresh:
+                    self.scratch_epoch += 1
+                table = self.scratch(f"table.{g}", (s, widths[g]), torch.int32)
+                ops.table_update(resident, views[8 + 2 * g], ctx.state_slots, table)
+                ctx.group_tables.append(table)
+            else:
+                ctx.group_tables.append(views[8 + 2 * g])
         if moved:
             ops.move_ids(ctx.token_ids, views[-2], views[-1], sampled_ids)
         if self.position_axes > 1:
@@ -243,8 +258,9 @@ class ModelRunner:
         """Run the given tokens as one batch from the cache that earlier steps left and
         return float32 logits ``[wanted, vocab]`` in the order of the entries and of their
         ``want`` lists.  The tensor is scratch memory: it is valid until the next step."""
-        ctx = self.prepare(entries, sampled_ids)
-        with torch.cuda.device(self.device):
+        with profiling.scope("pack (index arrays, pages, one copy)"):
+            ctx = self.prepare(entries, sampled_ids)
+        with profiling.scope("launch (the model's kernels)"), torch.cuda.device(self.device):
             logits = self._forward(ctx)
         self.steps_run += 1
         return logits

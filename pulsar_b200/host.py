@@ -25,6 +25,7 @@ _SIGNATURES = {
     "ph_n_free_pages": (_I, [_P, _I]), "ph_n_pages": (_I, [_P, _I]), "ph_page_held": (_I, [_P, _I, _I]),
     "ph_n_free_slots": (_I, [_P]), "ph_slot_held": (_I, [_P, _I]),
     "ph_table": (_I, [_P, _L, _I, _IP, _I]), "ph_slots": (_I, [_P, _L, _I, _I, _I, _IP]),
+    "ph_set_resident_tables": (None, [_P, _I]),
     "ph_step_plan": (_I, [_P, _I, _LP, _IP, _IP, _IP, _IP, _IP, _I, _I, _I, _IP, _IP, _IP, _IP]),
     "ph_step_pack": (_I, [_P, _I, _LP, _IP, _IP, _IP, _IP, _IP, _IP, _IP, _IP, _P, _I, _IP, _IP]),
 }

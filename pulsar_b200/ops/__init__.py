@@ -16,6 +16,7 @@ from typing import Optional
 
 import torch
 
+from .. import profiling
 from ..csrc.build import library
 
 F32, BF16 = 0, 1
@@ -41,6 +42,7 @@ _SIGNATURES = {
     "pb_embed": [_I, _P, _P, _P, _I, _I, _I, _F, _P],
     "pb_scale_cap": [_P, ctypes.c_longlong, _F, _F, _P],
     "pb_move_ids": [_P, _P, _P, _P, _I, _P],
+    "pb_table_update": [_P, _I, _P, _P, _I, _I, _P, _P],
     "pb_add_rmsnorm": [_I, _P, _P, _P, _P, _P, _I, _I, _F, _I, _P],
     "pb_rope_table": [_P, _P, _P, _P, _I, _I, _P],
     "pb_qk_norm_rope_write": [_I, _P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P],
@@ -78,6 +80,11 @@ _SIGNATURES = {
     "pb_argmax": [_P, _I, _I, _P, _P, _P],
 }
 _fns = {}
+# the entry points that launch kernels (the others answer questions on the host): what PULSAR_PROF=1 times
+_LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk_norm_rope_write", "silu_mul", "gather_words",
+              "paged_attention_generic", "paged_attention_decode", "paged_attention_decode_tc", "paged_attention_decode_tc_fused",
+              "paged_attention_prefill_tc", "paged_attention_prefill_tcgen05", "gemm_skinny", "gemm_skinny_accumulate",
+              "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update"}
 
 
 class KernelError(RuntimeError):
@@ -90,6 +97,8 @@ def fn(name: str):
         f = getattr(library(), name)
         f.argtypes = _SIGNATURES[name]
         f.restype = ctypes.c_int
+        if profiling.ENABLED and name[3:] in _LAUNCHERS:
+            f = profiling.timed_launcher(name, f)
         _fns[name] = f
     return f
 
@@ -152,6 +161,16 @@ def move_ids(ids: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, src_ids: t
     _cuda(ids, dst, src, src_ids)
     assert ids.dtype == dst.dtype == src.dtype == src_ids.dtype == torch.int32 and dst.numel() == src.numel()
     check(fn("pb_move_ids")(_p(ids), _p(dst), _p(src), _p(src_ids), dst.numel(), stream()), "move_ids")
+
+
+def table_update(resident: torch.Tensor, updates: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    """Apply a step's (row, logical page, page id) triples to the resident block tables [rows, stride] and copy the
+    step's rows (``rows`` [S]) into ``out`` [S, width]; ``updates`` = the count, then the triples (all int32)."""
+    _cuda(resident, updates, rows, out)
+    assert resident.dtype == updates.dtype == rows.dtype == out.dtype == torch.int32
+    s, width = out.shape
+    assert rows.numel() == s and resident.dim() == 2 and width <= resident.shape[1]
+    check(fn("pb_table_update")(_p(resident), resident.shape[1], _p(updates), _p(rows), s, width, _p(out), stream()), "table_update")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -506,10 +525,11 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         return
     if GEMM_BACKEND == "tcgen05" and gemm_tcgen05(a, w, out):
         return
-    if out.dtype == torch.bfloat16:
-        torch.mm(a, w.t(), out=out)
-    else:
-        out.copy_(torch.mm(a, w.t(), out_dtype=torch.float32))
+    with profiling.kernel("library product (torch.mm)"):
+        if out.dtype == torch.bfloat16:
+            torch.mm(a, w.t(), out=out)
+        else:
+            out.copy_(torch.mm(a, w.t(), out_dtype=torch.float32))
 
 
 def gated_linear(ctx, a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:

@@ -474,6 +474,23 @@ def test_command_line(folders, tmp_path):
     assert got == [plain.greedy_generate(cfg, weights, p, 5) for p in ([1, 2, 3, 4], [9, 8, 7])]
 
 
+def test_profile_of_a_run_names_kernel_classes_and_host_phases(folders):
+    """PULSAR_PROF=1: the same generation, and at exit a table of device time per kernel class (CUDA events) and of
+    host time per phase on standard error; the tokens are those of the run without it."""
+    raw, seed, page = TINY["D"]
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "pulsar-generate"), "--model", folders["D"], "--dtype", "bfloat16",
+           "--prompt_ids", "1,2,3,4,5,6,7", "--gen_tokens", "6", "--max_pages", "32", "--eos_id", "-1", "--json"]
+    plain_run = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    prof_run = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, PULSAR_PROF="1"))
+    assert plain_run.returncode == 0 and prof_run.returncode == 0, prof_run.stderr
+    assert json.loads(prof_run.stdout.strip().splitlines()[-1])["outputs"] == json.loads(plain_run.stdout.strip().splitlines()[-1])["outputs"]
+    err = prof_run.stderr
+    assert "device time per kernel class" in err and "host time per phase" in err
+    for name in ("gemm_skinny", "paged_attention_decode", "qk_norm_rope_write", "argmax", "plan (", "pack (", "launch (", "read ("):
+        assert name in err, (name, err)
+    assert "device time per kernel class" not in plain_run.stderr
+
+
 LAYER_SIZES = {      # hidden, intermediate, query heads (8 kv heads of 128 each): the dense sizes of the family
     "8b": (4096, 12288, 32), "14b": (5120, 17408, 40), "32b": (5120, 25600, 64)}
 

@@ -225,3 +225,67 @@ def test_step_packer_refuses_without_changing_anything():
     assert (cache.n_free_pages(), cache.length("a"), cache.table("a", 0)) == before and not cache.has("b")
     assert plan([("a", [1]), ("b", [2] * 4)]) > 0 and cache.has("b") and cache.length("a") == 8
     cache.check_consistency()
+
+
+def test_resident_tables_hold_what_the_host_tables_say():
+    """With resident tables a step brings only the page ids that its requests gained since they were last sent.
+    A stand-in for the device applies them to one row per state slot; after every step each request's row equals
+    its table on the host wherever a kernel may read it (pages that a window released are never read), also for
+    requests that were closed and opened again on a used row, and the packed array of a step of single tokens
+    keeps its length."""
+    rng = random.Random(9)
+    needs = [CacheNeed.paged_kv(2, 16), CacheNeed.paged_kv(2, 16, 6)]
+    cache = CacheManager(needs, 4, 96, 4)
+    lib = host.lib()
+    lib.ph_set_resident_tables(cache._h, 1)
+    resident = [[[-7] * 64 for _ in range(4)] for _ in range(2)]           # [group][row][logical page]
+    live, sent_words, table_words = {}, 0, 0
+    for step in range(60):
+        for rid in list(live):                                             # some requests end, their rows are used again
+            if rng.random() < 0.08:
+                cache.close(rid)
+                del live[rid]
+        names = [f"r{i}" for i in range(4)]
+        entries = []
+        for rid in names:
+            if rng.random() < 0.7 and (rid in live or len(live) + len([e for e in entries if e[0] not in live]) < 4):
+                n = 1 if rid in live and rng.random() < 0.7 else rng.randint(1, 9)
+                entries.append((rid, [rng.randrange(50) for _ in range(n)]))
+        if not entries:
+            continue
+        s = len(entries)
+        rids = host.longs([cache.native_id(e[0], create=True) for e in entries])
+        n_tok = host.ints([len(e[1]) for e in entries])
+        tokens = host.ints([t for e in entries for t in e[1]])
+        zeros, minus = host.ints([0] * s), host.ints([-1] * s)
+        starts, slots, widths, bad = (ctypes.c_int * s)(), (ctypes.c_int * s)(), (ctypes.c_int * 2)(), ctypes.c_int()
+        total = lib.ph_step_plan(cache._h, s, rids, n_tok, tokens, zeros, host.ints([0]), minus, 0, 50, 64, starts, slots,
+                                 widths, ctypes.byref(bad))
+        assert total > 0, total
+        for e in entries:
+            live[e[0]] = live.get(e[0], 0) + len(e[1])
+        buf = (ctypes.c_int * total)()
+        off, ln = (ctypes.c_int * 11)(), (ctypes.c_int * 11)()
+        assert lib.ph_step_pack(cache._h, s, rids, n_tok, tokens, zeros, host.ints([0]), minus, starts, slots, widths,
+                                ctypes.cast(buf, ctypes.c_void_p), total, off, ln) == total
+        single = all(len(e[1]) == 1 for e in entries)
+        for g in range(2):
+            upd = list(buf[off[8 + 2 * g]:off[8 + 2 * g] + ln[8 + 2 * g]])
+            if single:
+                assert len(upd) == 1 + 3 * s                               # the same length every such step
+            assert upd[0] * 3 + 1 <= len(upd)
+            for u in range(upd[0]):
+                row, lp, page = upd[1 + 3 * u:4 + 3 * u]
+                assert row in list(slots) and page >= 0
+                resident[g][row][lp] = page
+            sent_words += len(upd)
+            table_words += s * widths[g]
+            window = needs[g].window
+            for i, e in enumerate(entries):
+                table = cache.table(e[0], g)
+                length = cache.length(e[0])
+                first_read = 0 if window is None else max(0, starts[i] - window + 1) // 4     # pages a query of this step reads
+                for lp in range(first_read, -(-length // 4)):
+                    assert resident[g][slots[i]][lp] == table[lp], (step, g, e[0], lp)
+        cache.check_consistency()
+    assert sent_words * 4 < table_words                                    # far fewer words travel
