@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                     float* __restrict__ partial, const int* __restrict__ block_table, int table_stride,
                     const int* __restrict__ kv_len, int Hq, int Hkv, int D, int page_size, float scale, int window,
-                    int n_splits) {
+                    int n_splits, const PoolBounds bounds) {
     extern __shared__ float smem[];
     const int G = Hq / Hkv;
     float* q_s = smem;                                  // [kGP][D]
@@ -91,7 +91,8 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
 #pragma unroll
             for (int g = 0; g < kGP; ++g) sc[g] = 0.0f;
             if (valid) {
-                const int page = table[j / page_size];
+                int page = table[j / page_size];
+                if (!page_ok(page, bounds)) page = 0;
                 const T* kr = k_pool + (((size_t)page * Hkv + kvh) * page_size + j % page_size) * D;
                 for (int d = 0; d < D; d += 8) {
                     float kf[8];
@@ -127,7 +128,8 @@ decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, const
             const int n_here = min(32, end - j0);
             for (int kk = 0; kk < n_here; ++kk) {
                 const int jj = j0 + kk;
-                const int page = table[jj / page_size];
+                int page = table[jj / page_size];
+                if (!page_ok(page, bounds)) page = 0;
                 const T* vr = v_pool + (((size_t)page * Hkv + kvh) * page_size + jj % page_size) * D;
                 float vf[kAcc];
 #pragma unroll
@@ -242,12 +244,13 @@ PB_EXPORT int pb_paged_attention_decode(int dtype, const void* q, const void* k_
     dim3 grid(n_splits, Hkv, n_seqs);
     if (dtype == PB_F32) {
         decode_split_kernel<float><<<grid, kWarps * 32, smem, stream>>>((const float*)q, (const float*)k_pool,
-            (const float*)v_pool, partial, block_table, table_stride, kv_len, Hq, Hkv, D, page_size, scale, window, n_splits);
+            (const float*)v_pool, partial, block_table, table_stride, kv_len, Hq, Hkv, D, page_size, scale, window, n_splits,
+            pb::pool_bounds_now());
         decode_combine_kernel<float><<<n_seqs * Hq, 128, 0, stream>>>(partial, (float*)out, D, n_splits);
     } else if (dtype == PB_BF16) {
         decode_split_kernel<__nv_bfloat16><<<grid, kWarps * 32, smem, stream>>>((const __nv_bfloat16*)q,
             (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, partial, block_table, table_stride, kv_len, Hq, Hkv, D,
-            page_size, scale, window, n_splits);
+            page_size, scale, window, n_splits, pb::pool_bounds_now());
         decode_combine_kernel<__nv_bfloat16><<<n_seqs * Hq, 128, 0, stream>>>(partial, (__nv_bfloat16*)out, D, n_splits);
     } else {
         return PB_ERR_BAD_DTYPE;

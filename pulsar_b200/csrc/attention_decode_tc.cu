@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2)
 decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                  float* __restrict__ partial, const int* __restrict__ block_table, int table_stride,
                  const int* __restrict__ kv_len, int Hq, int Hkv, int page_shift, float scale, int window, int n_splits,
-                 bf16* __restrict__ out, unsigned int* __restrict__ tickets, int evict_first) {
+                 bf16* __restrict__ out, unsigned int* __restrict__ tickets, int evict_first, const PoolBounds bounds) {
     constexpr int kTileBytes = kTile * D * 2;
     constexpr int kKSteps = D / 16;                   // k-steps of Q K^T
     constexpr int kNTiles = D / 8;                    // n-tiles of P V
@@ -59,7 +59,7 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
     auto issue_tile = [&](int tile_index, int stage) {
         const uint32_t k_dst = smem_base + stage * 2 * kTileBytes;
         load_kv_tile<D, kWarps * 32>(k_dst, k_dst + kTileBytes, k_pool, v_pool, table, (tile0 + tile_index) * kTile, begin,
-                                     end - 1, kvh, Hkv, page_shift, tid, policy);
+                                     end - 1, kvh, Hkv, page_shift, tid, policy, bounds);
     };
 
     // The kernel before this one writes only the newest key and value (position p).  Tiles that lie wholly
@@ -289,7 +289,8 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, float* part
     static const int evict_first = [] { const char* v = getenv("PULSAR_DECODE_EVICT_FIRST"); return (v && v[0] == '0' && v[1] == 0) ? 0 : 1; }();
     dim3 grid(n_splits, Hkv, n_seqs);
     return launch_pdl(decode_tc_kernel<D>, grid, kWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
-                      partial, block_table, table_stride, kv_len, Hq, Hkv, page_shift, scale, window, n_splits, (bf16*)out, tickets, evict_first);
+                      partial, block_table, table_stride, kv_len, Hq, Hkv, page_shift, scale, window, n_splits, (bf16*)out, tickets, evict_first,
+                      pool_bounds_now());
 }
 
 }  // namespace

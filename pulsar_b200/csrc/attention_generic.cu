@@ -55,7 +55,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                T* __restrict__ out, const int* __restrict__ block_table, int table_stride,
                                const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                const int* __restrict__ seq_of_token, int Hq, int Hkv, int D, int page_size,
-                               float scale, int window) {
+                               float scale, int window, const PoolBounds bounds) {
     extern __shared__ float smem[];
     float* q_s = smem;                         // [D] query, pre-multiplied by scale
     float* p_s = q_s + D;                      // [kWarps][32]
@@ -87,7 +87,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
         const bool valid = j >= lo && j <= p;
         float sc = -INFINITY;
         if (valid) {
-            const int page = table[j / page_size];
+            int page = table[j / page_size];
+            if (!page_ok(page, bounds)) page = 0;
             const T* kr = k_pool + (((size_t)page * Hkv + g) * page_size + j % page_size) * D;
             float dot = 0.0f;
             for (int d = 0; d < D; d += Vec<T>::n) {
@@ -113,7 +114,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
         const int k_end = (p - j0 < 31) ? p - j0 : 31;
         for (int kk = k_begin; kk <= k_end; ++kk) {
             const int jj = j0 + kk;
-            const int page = table[jj / page_size];
+            int page = table[jj / page_size];
+            if (!page_ok(page, bounds)) page = 0;
             const T* vr = v_pool + (((size_t)page * Hkv + g) * page_size + jj % page_size) * D;
             const float pk = p_s[warp * 32 + kk];
 #pragma unroll
@@ -161,11 +163,11 @@ PB_EXPORT int pb_paged_attention_generic(int dtype, const void* q, const void* k
     if (dtype == PB_F32)
         paged_attention_generic_kernel<float><<<grid, kWarps * 32, smem, stream>>>((const float*)q, (const float*)k_pool,
             (const float*)v_pool, (float*)out, block_table, table_stride, cu_q, kv_len, seq_of_token, Hq, Hkv, D, page_size,
-            scale, window);
+            scale, window, pb::pool_bounds_now());
     else if (dtype == PB_BF16)
         paged_attention_generic_kernel<__nv_bfloat16><<<grid, kWarps * 32, smem, stream>>>((const __nv_bfloat16*)q,
             (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, block_table, table_stride, cu_q,
-            kv_len, seq_of_token, Hq, Hkv, D, page_size, scale, window);
+            kv_len, seq_of_token, Hq, Hkv, D, page_size, scale, window, pb::pool_bounds_now());
     else return PB_ERR_BAD_DTYPE;
     return launch_status();
 }

@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2)
 prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                   bf16* __restrict__ out, const int* __restrict__ block_table, int table_stride,
                   const int* __restrict__ cu_q, const int* __restrict__ kv_len, int n_seqs, int Hq, int Hkv,
-                  int page_shift, float scale, int window) {
+                  int page_shift, float scale, int window, const PoolBounds bounds) {
     constexpr int kChunks = D / 8;
     constexpr int kTileBytes = kBN * D * 2;
     constexpr int kKSteps = D / 16;
@@ -77,7 +77,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, c
     auto issue_kv = [&](int tile_index, int stage) {
         const uint32_t k_dst = smem_base + stage * 2 * kTileBytes;
         load_kv_tile<D, kWarps * 32>(k_dst, k_dst + kTileBytes, k_pool, v_pool, table, (kt0 + tile_index) * kBN, lo, pos_last,
-                                     kvh, Hkv, page_shift, tid);
+                                     kvh, Hkv, page_shift, tid, 0, bounds);
     };
 
     // Q tile through the second stage's K buffer into registers, while the first K/V tile loads.
@@ -255,7 +255,7 @@ int launch_prefill(const void* q, const void* k_pool, const void* v_pool, void* 
     dim3 grid(n_q_tiles, Hq);
     prefill_tc_kernel<D><<<grid, kWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
                                                               (bf16*)out, block_table, table_stride, cu_q, kv_len, n_seqs,
-                                                              Hq, Hkv, page_shift, scale, window);
+                                                              Hq, Hkv, page_shift, scale, window, pool_bounds_now());
     return launch_status();
 }
 

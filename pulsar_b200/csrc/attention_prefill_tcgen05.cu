@@ -67,6 +67,7 @@ struct Args {
     const int* kv_len;
     int table_stride, n_seqs, n_items, Hq, Hkv, page_shift, rows_per_load, window;
     float scale;
+    PoolBounds bounds;
 };
 
 // One work item: a tile of 128 query rows of one sequence and one query head.  Every role of a block
@@ -188,7 +189,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const bool want = slot < loads && key + a.rows_per_load > w.lo && key <= w.pos_last;
                 int row = 0;
                 if (want) {
-                    const int page = w.table[key >> a.page_shift];
+                    int page = w.table[key >> a.page_shift];
+                    if (!page_ok(page, a.bounds)) page = 0;
                     row = ((page * a.Hkv + w.kvh) << a.page_shift) + (key & ((1 << a.page_shift) - 1));
                 }
                 const uint32_t n_want = __popc(__ballot_sync(0xffffffffu, want));
@@ -498,6 +500,7 @@ PB_EXPORT int pb_paged_attention_prefill_tcgen05(int dtype, const void* q, const
     a.rows_per_load = rows_per_load;
     a.window = window;
     a.scale = scale;
+    a.bounds = pool_bounds_now();
     const int grid = (int)(items < sm_count() ? items : sm_count());       // persistent: one block per SM
     prefill_tcgen05_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, a);
     return launch_status();

@@ -101,6 +101,7 @@ struct Args {
     int table_stride, n_seqs, n_items, Hq, Hkv, page_shift, rows_per_load, window;
     int pairs, n_q_tiles, group;      // Hq / 2, n_items / pairs, Hq / Hkv
     float scale;
+    PoolBounds bounds;
 };
 
 // One work item: a tile of 128 query rows of one sequence and a pair of query heads (2p, 2p+1) of one group.  Items are
@@ -224,7 +225,8 @@ prefill_tcgen05_dual_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     const bool want = slot < loads && key + a.rows_per_load > w.lo && key <= w.pos_last;
                     int row = 0;
                     if (want) {
-                        const int page = w.table[key >> a.page_shift];
+                        int page = w.table[key >> a.page_shift];
+                        if (!page_ok(page, a.bounds)) page = 0;
                         row = ((page * a.Hkv + w.kvh) << a.page_shift) + (key & ((1 << a.page_shift) - 1));
                     }
                     const uint32_t n_want = __popc(__ballot_sync(0xffffffffu, want));
@@ -567,6 +569,7 @@ int launch_dual(const void* q, const void* k_pool, const void* v_pool, void* out
     a.rows_per_load = rows_per_load;
     a.window = window;
     a.scale = scale;
+    a.bounds = pool_bounds_now();
     const int grid = (int)(items < sm_count() ? items : sm_count());       // persistent: one block per SM
     prefill_tcgen05_dual_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, a);
     return launch_status();

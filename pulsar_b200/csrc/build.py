@@ -24,11 +24,15 @@ import time
 from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_NAME = "libpulsar_b200.so"
+# PULSAR_CHECK_BOUNDS=1: the debug build, in a library of its own beside the ordinary one.  Its kernels check every
+# page id and slot they take from an index array against the pool's size, record a bad one in an error word and skip
+# the access (common.cuh: PoolBounds).
+CHECK_BOUNDS = os.environ.get("PULSAR_CHECK_BOUNDS", "0") not in ("", "0")
+LIB_NAME = "libpulsar_b200_checked.so" if CHECK_BOUNDS else "libpulsar_b200.so"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-]   # precise math: never -use_fast_math
+] + (["-DPB_CHECK_BOUNDS"] if CHECK_BOUNDS else [])   # precise math: never -use_fast_math
 
 _lib: Optional[ctypes.CDLL] = None
 _lock = threading.Lock()
@@ -87,7 +91,7 @@ def build(verbose: bool = True, force: bool = False, extra_flags: Optional[List[
     """Compile what is stale and return the library's path."""
     out_dir = _build_dir()
     lib_path = os.path.join(out_dir, LIB_NAME)
-    stamp_path = os.path.join(out_dir, "stamp.txt")
+    stamp_path = os.path.join(out_dir, "stamp_checked.txt" if CHECK_BOUNDS else "stamp.txt")
     digest = _digest()
     if not force and os.path.isfile(lib_path) and os.path.isfile(stamp_path):
         with open(stamp_path) as f:
@@ -99,18 +103,24 @@ def build(verbose: bool = True, force: bool = False, extra_flags: Optional[List[
     if verbose:
         _say(f"compiling {len(srcs)} CUDA sources for sm_100a into {out_dir} (first call only)")
     t0 = time.time()
-    procs = []
+    procs, logs = [], {}
     for name in srcs:
-        obj = os.path.join(out_dir, name[:-3] + ".o")
+        obj = os.path.join(out_dir, name[:-3] + (".checked.o" if CHECK_BOUNDS else ".o"))
         cmd = [nvcc, *flags, "-I", HERE, "-c", os.path.join(HERE, name), "-o", obj]
-        procs.append((name, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        # the compiler's messages go to a file: a pipe that nobody reads until the process ends blocks a compiler
+        # that has more to say than the pipe holds
+        log = open(obj + ".log", "w+")
+        logs[name] = log
+        procs.append((name, obj, subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT, stdin=subprocess.DEVNULL)))
     pending = {name for name, _, _ in procs}
     last = time.time()
     outputs = {}
     while pending:
         for name, _, p in procs:
             if name in pending and p.poll() is not None:
-                outputs[name] = p.stdout.read()
+                logs[name].seek(0)
+                outputs[name] = logs[name].read()
+                logs[name].close()
                 pending.discard(name)
                 if verbose:
                     _say(f"  {name} done ({time.time() - t0:.0f}s, {len(pending)} left)")

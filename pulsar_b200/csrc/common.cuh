@@ -57,6 +57,38 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 inline int launch_status() { return (int)cudaPeekAtLastError(); }
 
+// Bounds checks of the debug build (-DPB_CHECK_BOUNDS; PULSAR_CHECK_BOUNDS=1 when the library is built): every page
+// id and slot that a kernel takes from a block table or a slot array is checked against the pool's size before it
+// becomes an address.  A bad one is recorded in the caller's error word (the largest code seen: 2 = a page id in a
+// block table, 3 = a slot) and the access is skipped: a read takes page 0 instead, a write is dropped.  The host sets
+// what the next launches check against (pb_set_pool_bounds); without the flag the checks compile to nothing.
+// (The reference checks its arguments on the host, pulsar-core/src/kernels/paged_common.cu:172-272, and has one device
+// assertion, pulsar-core/inc/pulsar/kernels/attn_params.cuh:130.)
+struct PoolBounds {
+    int n_pages;             // pages of the pool the next launches read and write; <= 0: unchecked
+    unsigned int* error;     // device word; null: unchecked
+};
+PoolBounds pool_bounds_now();            // host side: what pb_set_pool_bounds set last (zeros in a build without the flag)
+
+__device__ __forceinline__ bool page_ok(int page, const PoolBounds& b) {
+#ifdef PB_CHECK_BOUNDS
+    if (b.error != nullptr && b.n_pages > 0 && (page < 0 || page >= b.n_pages)) {
+        atomicMax(b.error, 2u);
+        return false;
+    }
+#endif
+    return true;
+}
+__device__ __forceinline__ bool slot_ok(int slot, int page_size, const PoolBounds& b) {
+#ifdef PB_CHECK_BOUNDS
+    if (b.error != nullptr && b.n_pages > 0 && slot >= b.n_pages * page_size) {        // negative: "no slot", skipped anyway
+        atomicMax(b.error, 3u);
+        return false;
+    }
+#endif
+    return true;
+}
+
 // Programmatic dependent launch.  A kernel launched through launch_pdl may be brought onto the
 // SMs while the kernel before it on the stream is finishing: as soon as every block of that
 // kernel has called pdl_trigger (or exited).  It must call pdl_wait before it touches anything

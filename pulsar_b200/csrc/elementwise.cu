@@ -186,7 +186,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
                                           const int* __restrict__ slots,
                                           const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                           const float* __restrict__ q_weight, const float* __restrict__ k_weight,
-                                          float eps, int Hq, int Hkv, int D, int rotary, int page_size) {
+                                          float eps, int Hq, int Hkv, int D, int rotary, int page_size, const PoolBounds bounds) {
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -199,7 +199,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
         dst = q_out + ((size_t)t * Hq + head) * D;
     } else {
         const int slot = slots[t];
-        if (slot < 0) return;
+        if (slot < 0 || !slot_ok(slot, page_size, bounds)) return;
         const int kvh = is_k ? head - Hq : head - Hq - Hkv;
         const size_t at = (((size_t)(slot / page_size) * Hkv + kvh) * page_size + slot % page_size) * D;
         dst = (is_k ? k_pool : v_pool) + at;
@@ -281,7 +281,7 @@ qk_norm_rope_write_bf16_d128_kernel(const uint32_t* __restrict__ qkv, uint32_t* 
                                     uint32_t* __restrict__ k_pool, uint32_t* __restrict__ v_pool,
                                     const int* __restrict__ slots, const float2* __restrict__ cos_t,
                                     const float2* __restrict__ sin_t, const float2* __restrict__ q_weight,
-                                    const float2* __restrict__ k_weight, float eps, int Hq, int Hkv, int page_size) {
+                                    const float2* __restrict__ k_weight, float eps, int Hq, int Hkv, int page_size, const PoolBounds bounds) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31;
@@ -299,7 +299,8 @@ qk_norm_rope_write_bf16_d128_kernel(const uint32_t* __restrict__ qkv, uint32_t* 
         }
     }
     const float2 c = cos_t[(size_t)t * 32 + lane], sn = sin_t[(size_t)t * 32 + lane];
-    const int slot = Hkv ? slots[t] : -1;
+    int slot = Hkv ? slots[t] : -1;
+    if (slot >= 0 && !slot_ok(slot, page_size, bounds)) slot = -1;
 #pragma unroll
     for (int h = 0; h < kRopeHeadsPerWarp; ++h) {
         const int head = head0 + h;
@@ -389,6 +390,32 @@ PB_EXPORT int pb_move_ids(int* ids, const int* dst, const int* src, const int* s
     if (n <= 0) return 0;
     move_ids_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, dst, src, src_ids, n);
     return launch_status();
+}
+
+namespace pb {
+static PoolBounds g_pool_bounds = {0, nullptr};
+PoolBounds pool_bounds_now() { return g_pool_bounds; }
+}  // namespace pb
+
+// 1 in a build with the bounds checks (see common.cuh), else 0.
+PB_EXPORT int pb_bounds_checked(void) {
+#ifdef PB_CHECK_BOUNDS
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+// What the kernels launched from now on check page ids and slots against: a pool of n_pages pages, violations
+// recorded in *error (a device word).  n_pages <= 0 or error null: unchecked.  Does nothing without the build flag.
+PB_EXPORT void pb_set_pool_bounds(int n_pages, unsigned int* error) {
+#ifdef PB_CHECK_BOUNDS
+    pb::g_pool_bounds.n_pages = n_pages;
+    pb::g_pool_bounds.error = error;
+#else
+    (void)n_pages;
+    (void)error;
+#endif
 }
 
 namespace {
@@ -505,15 +532,16 @@ PB_EXPORT int pb_qk_norm_rope_write(int dtype, const void* qkv, void* q_out, voi
         dim3 fast_grid(n, (heads + warps * kRopeHeadsPerWarp - 1) / (warps * kRopeHeadsPerWarp));
         return launch_pdl(qk_norm_rope_write_bf16_d128_kernel, fast_grid, warps * 32, 0, stream, (const uint32_t*)qkv, (uint32_t*)q_out,
             (uint32_t*)k_pool, (uint32_t*)v_pool, slots, (const float2*)cos_t, (const float2*)sin_t, (const float2*)q_weight,
-            (const float2*)k_weight, eps, Hq, Hkv, page_size);
+            (const float2*)k_weight, eps, Hq, Hkv, page_size, pb::pool_bounds_now());
     }
     dim3 grid(n, (heads + warps - 1) / warps);
     if (dtype == PB_F32)
         qk_norm_rope_write_kernel<float><<<grid, warps * 32, 0, stream>>>((const float*)qkv, (float*)q_out, (float*)k_pool, (float*)v_pool,
-            slots, cos_t, sin_t, q_weight, k_weight, eps, Hq, Hkv, D, rotary, page_size);
+            slots, cos_t, sin_t, q_weight, k_weight, eps, Hq, Hkv, D, rotary, page_size, pb::pool_bounds_now());
     else if (dtype == PB_BF16)
         qk_norm_rope_write_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out,
-            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, slots, cos_t, sin_t, q_weight, k_weight, eps, Hq, Hkv, D, rotary, page_size);
+            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, slots, cos_t, sin_t, q_weight, k_weight, eps, Hq, Hkv, D, rotary, page_size,
+            pb::pool_bounds_now());
     else return PB_ERR_BAD_DTYPE;
     return launch_status();
 }

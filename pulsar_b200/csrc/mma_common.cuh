@@ -75,7 +75,7 @@ template <int D, int THREADS>
 __device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, const bf16* __restrict__ k_pool,
                                              const bf16* __restrict__ v_pool, const int* __restrict__ table, int key0,
                                              int first_key, int last_key, int kvh, int Hkv, int page_shift, int tid,
-                                             uint64_t policy = 0) {
+                                             uint64_t policy = 0, const PoolBounds bounds = PoolBounds{0, nullptr}) {
     constexpr int kChunks = D / 8;
     constexpr int kRowsPerPass = THREADS / kChunks;       // a multiple of 8: (row & 7) does not change
     constexpr int kPasses = 64 / kRowsPerPass;
@@ -89,7 +89,8 @@ __device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, con
 #pragma unroll
         for (int i = 0; i < kPasses; ++i) {
             const int key = key0 + r0 + i * kRowsPerPass;
-            const int page = table[key >> page_shift];
+            int page = table[key >> page_shift];
+            if (!page_ok(page, bounds)) page = 0;
             const size_t at = (size_t)(page * Hkv + kvh) * page_elems + (size_t)((key & page_mask) * D + col);
             const uint32_t off = off0 + (uint32_t)(i * kRowsPerPass * kChunks * 16);
             if (policy) {
@@ -107,7 +108,8 @@ __device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, con
             const bool ok = key >= first_key && key <= last_key;
             size_t at = 0;
             if (ok) {
-                const int page = table[key >> page_shift];
+                int page = table[key >> page_shift];
+                if (!page_ok(page, bounds)) page = 0;
                 at = (size_t)(page * Hkv + kvh) * page_elems + (size_t)((key & page_mask) * D + col);
             }
             const uint32_t off = off0 + (uint32_t)(i * kRowsPerPass * kChunks * 16);

@@ -74,6 +74,8 @@ _SIGNATURES = {
     "pb_gemm_tcgen05_wait_selftest": [_P],
     "pb_prefill_tcgen05_wait_control": [ctypes.c_longlong, _I, _P],
     "pb_gather_words": [_P, _I, _P, _P],
+    "pb_bounds_checked": [],
+    "pb_set_pool_bounds": [_I, _P],
     "pb_gemm_simt": [_I, _I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_sample": [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P],
     "pb_sample_workspace": [_I],
@@ -207,6 +209,7 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[
     """Per-head RMSNorm (when weights are given) and rotation of q and k, q to ``q_out``,
     k and v into their pages.  ``n_kv_heads`` 0: the row holds q only."""
     _cuda(qkv, q_out, k_pool, v_pool, slots, cos, sin, q_weight, k_weight)
+    _check_against(k_pool)
     n = qkv.shape[0]
     assert qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim and q_out.dtype == qkv.dtype
     assert cos.shape == (n, rotary // 2) and sin.shape == cos.shape and cos.dtype == torch.float32
@@ -231,6 +234,7 @@ def paged_attention_generic(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
                             block_table: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                             seq_of_token: torch.Tensor, scale: float, window: Optional[int]) -> None:
     _cuda(q, k_pool, v_pool, out, block_table, cu_q, kv_len, seq_of_token)
+    _check_against(k_pool)
     n, hq, d = q.shape
     pages, hkv, page_size, d2 = k_pool.shape
     assert d2 == d and v_pool.shape == k_pool.shape and out.shape == q.shape
@@ -430,8 +434,41 @@ def gemm_tcgen05_error() -> int:
 # that cannot go on into an exception (pulsar-core/src/runtime/engine.cpp:809-814) and its Python layer
 # poisons the engine (pulsar/src/pulsar/rt/sync.py:21-34); the words below are how this engine learns of it.
 WAIT_WORD_NAMES = ("tcgen05 product", "tcgen05 attention, one head per block", "tcgen05 attention, two heads per block",
-                   "tcgen05 product for up to 128 tokens")
-N_WAIT_WORDS = len(WAIT_WORD_NAMES)
+                   "tcgen05 product for up to 128 tokens", "bounds check of the debug build")
+N_WAIT_WORDS = len(WAIT_WORD_NAMES)          # the last one is 0 in a build without the checks
+BOUNDS_CODES = {2: "a block table named a page outside its pool (the access was skipped)",
+                3: "a slot outside its pool (the write was dropped)"}
+_bounds_words = {}
+
+
+def bounds_checked() -> bool:
+    """Whether the loaded library is the debug build whose kernels check page ids and slots
+    (built with PULSAR_CHECK_BOUNDS=1)."""
+    return bool(fn("pb_bounds_checked")())
+
+
+def _bounds_word() -> torch.Tensor:
+    dev = torch.cuda.current_device()
+    word = _bounds_words.get(dev)
+    if word is None:
+        word = _bounds_words[dev] = torch.zeros(1, dtype=torch.int32, device="cuda")
+    return word
+
+
+def _check_against(pool: Optional[torch.Tensor]) -> None:
+    """Debug build: the kernels launched next check page ids and slots against this pool's size."""
+    if pool is not None and bounds_checked():
+        fn("pb_set_pool_bounds")(int(pool.shape[0]), _p(_bounds_word()))
+
+
+def bounds_error() -> int:
+    """0, or the largest code a bounds check recorded (synchronises); always 0 without the debug build."""
+    return int(_bounds_word().item()) if bounds_checked() else 0
+
+
+def clear_bounds_error() -> None:
+    if bounds_checked():
+        _bounds_word().zero_()
 WAIT_ROLES = {2: "the TMA producer", 3: "the MMA issuer", 4: "the epilogue or softmax warps", 9: "the wait self-test"}
 _wait_words = {}
 _check_buf = {}
@@ -454,6 +491,7 @@ def wait_word_addresses() -> "ctypes.Array":
                 or fn("pb_gemm_tcgen05_stream_wait_control")(0, -1, three) != 0):
             raise KernelError("the addresses of the wait error words could not be had")
         got[0], got[1], got[2], got[3] = one[0], two[0], two[1], three[0]
+        got[4] = _bounds_word().data_ptr()
         _wait_words[dev] = got
     return got
 
@@ -490,10 +528,11 @@ def wait_selftest() -> None:
 
 def describe_wait_words(words) -> Optional[str]:
     """None when all words are 0, else which kernel gave up and in which role."""
-    bad = [(WAIT_WORD_NAMES[i], int(w)) for i, w in enumerate(words) if int(w) != 0]
+    bad = [(i, WAIT_WORD_NAMES[i], int(w)) for i, w in enumerate(words) if int(w) != 0]
     if not bad:
         return None
-    return "; ".join(f"{name}: {WAIT_ROLES.get(w, 'role ' + str(w))} gave up a bounded wait" for name, w in bad)
+    return "; ".join(f"{name}: {BOUNDS_CODES.get(w, 'code ' + str(w))}" if i == N_WAIT_WORDS - 1 else
+                     f"{name}: {WAIT_ROLES.get(w, 'role ' + str(w))} gave up a bounded wait" for i, name, w in bad)
 
 
 def check_wait_words() -> None:
@@ -605,6 +644,7 @@ def paged_attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     it saves a launch; with several splits the ticket and fences cost what the combine kernel costs
     (measured: 5.04 vs 4.99 ms per step at batch 8)."""
     _cuda(q, k_pool, v_pool, out, partial, block_table, kv_len)
+    _check_against(k_pool)
     s, hq, d = q.shape
     pages, hkv, page_size, d2 = k_pool.shape
     assert d2 == d and v_pool.shape == k_pool.shape and out.shape == q.shape and kv_len.numel() == s
@@ -647,6 +687,7 @@ def paged_attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: to
                                scale: float, window: Optional[int]) -> None:
     """Tensor-core attention for a ragged batch of portions (bfloat16, head size 64 or 128)."""
     _cuda(q, k_pool, v_pool, out, block_table, cu_q, kv_len)
+    _check_against(k_pool)
     n, hq, d = q.shape
     pages, hkv, page_size, d2 = k_pool.shape
     assert d2 == d and v_pool.shape == k_pool.shape and out.shape == q.shape
@@ -683,6 +724,7 @@ def paged_attention_prefill_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_poo
     """tcgen05 attention for a ragged batch of portions (bfloat16, head size 128, pages of 8 or more
     tokens).  Pool rows that were never written must hold finite values."""
     _cuda(q, k_pool, v_pool, out, block_table, cu_q, kv_len)
+    _check_against(k_pool)
     n, hq, d = q.shape
     pages, hkv, page_size, d2 = k_pool.shape
     assert d2 == d and v_pool.shape == k_pool.shape and out.shape == q.shape

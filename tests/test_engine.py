@@ -275,7 +275,7 @@ def test_a_wait_that_runs_out_sets_its_error_word():
         assert ops.gemm_tcgen05_error() == 9
         words = torch.zeros(8, dtype=torch.int32, device="cuda")
         ops.gather_wait_words(words)
-        assert words.tolist()[:ops.N_WAIT_WORDS] == [9, 0, 0, 0]
+        assert words.tolist()[:ops.N_WAIT_WORDS] == [9, 0, 0, 0, 0]
         assert "wait self-test" in ops.describe_wait_words(words.tolist()[:ops.N_WAIT_WORDS])
         with pytest.raises(ops.DeviceWaitError):
             ops.check_wait_words()
