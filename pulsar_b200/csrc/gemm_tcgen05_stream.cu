@@ -3,22 +3,24 @@
 // but there are too many tokens for the kernel that keeps them in MMA fragments (gemm_skinny.cu).
 //
 // The operands change places against gemm_tcgen05.cu: 128 rows of W are the 128-row operand of tcgen05.mma
-// (the lanes of the accumulator in tensor memory), the tokens are its narrow one (16 to 128 columns).  A block
-// owns one tile of 128 weight rows and a slice of K; the S blocks of a cluster own the S slices of one tile,
-// so that a product with few tiles (4096 output features are 32 tiles) still has a block on nearly every SM
-// and each block streams its part of W through a ring of TMA stages without a pause.  The partial sums meet
-// in shared memory: every block of the cluster sends, for each token, its 128 partial sums to the block that
-// owns that token's column slice (st.shared::cluster), one cluster barrier, and every block adds up and
-// stores its own columns.  No partial sum goes through global memory, no atomics, a fixed order of addition.
+// (the lanes of the accumulator in tensor memory), the tokens are its narrow one (16 to 128 columns).  The work
+// is cut into units of (a tile of 128 weight rows, a slice of K), as many slices as make the units fill whole
+// rounds of the SMs: 4096 output features are only 32 tiles, and 192 tiles on 148 SMs are 1.3 rounds.  A
+// persistent grid of one block per SM walks over the units (unit u to block u mod grid) and streams its part of
+// W through one ring of TMA stages without a pause: two accumulators in tensor memory take turns, so that a
+// finished unit is read out while the next one's bytes arrive.  With one slice the accumulator is stored straight
+// from registers.  With more, every unit writes its float32 partial sums to a workspace (they stay in L2) and
+// takes a ticket of its tile; the unit that draws the tile's last ticket adds the slices in their order and stores
+// the tile (no block waits for another, the order of addition is fixed).
 //
 // Roles in a block (192 threads): warp 0 / one thread issues the TMA loads (W with an evict-first L2 hint:
 // weights are read once per step and are far larger than L2; W of the first stages is asked for before the
 // kernel waits for its predecessor, x after), warp 1 / one thread issues the MMAs, warps 2-5 read the
-// accumulator.  SwiGLU: a tile is 64 gate rows and the 64 up rows that belong to them (two TMA boxes), and
-// silu(gate) * up is applied after the sums are complete, so the [M, 2I] intermediate never exists.
+// accumulators.  SwiGLU: a tile is 64 gate rows and the 64 up rows that belong to them (two TMA boxes), and
+// silu(gate) * up is applied where the sums are complete, so the [M, 2I] intermediate never exists.
 //
-// Every wait on a barrier is bounded by a clock limit; a role that gives up sets the error word and every
-// role still reaches the cluster barrier and frees the tensor memory.  No TMA load uses cluster multicast.
+// Every wait on a barrier is bounded by a clock limit; a role that gives up sets the error word, lets its copies
+// land, and the block frees its tensor memory and returns.  No TMA load uses cluster multicast.
 //
 // The reference calls at::linear (cuBLAS) for all of these (pulsar-core/src/model/qwen3.cpp:82-84, 114, 117-119).
 #include "tcgen05_common.cuh"
@@ -34,9 +36,9 @@ constexpr int kRows = 128;            // weight rows per tile (MMA M, lanes of t
 constexpr int kBK = 64;               // k per stage: one 128-byte swizzle atom of bfloat16
 constexpr int kThreads = 192;
 constexpr int kWBytes = kRows * kBK * 2;      // 16 KB
-constexpr int kTmemColumns = 128;
+constexpr int kTmemColumns = 256;      // two accumulators of up to 128 columns
 constexpr int kMaxStages = 8;
-constexpr int kMaxCluster = 8;
+constexpr int kMaxSlices = 16;
 
 enum { kPlain = 0, kSwiGLU = 1 };
 
@@ -66,219 +68,129 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
     return policy;
 }
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t remote_addr(uint32_t local, uint32_t rank) {      // the same offset in block `rank`'s shared memory
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void store_remote(uint32_t addr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
 
 struct StreamArgs {
     int M, N, K, inter;
-    int n_pad;          // tokens rounded up to a multiple of 16: columns of the accumulator, rows of an x box
+    int n_pad;          // tokens rounded up to a multiple of 16: columns of an accumulator, rows of an x box
     int stages;         // TMA stages of the ring
-    int splits;         // blocks per cluster = slices of K
-    int cols_per;       // token columns that a block of the cluster adds up and stores: ceil(M / splits)
-    int recv_offset;    // bytes from the ring's start to the receive buffer (0: it takes the ring's place, splits == 1)
+    int slices;         // slices of K per tile
+    int n_tiles;        // tiles of 128 weight rows (SwiGLU: 64 gate rows and their 64 up rows)
+    int up_offset;      // bytes from the ring's start to the SwiGLU staging buffer
     int bar_offset;     // bytes from the ring's start to the barriers
+    float* workspace;   // slices > 1: [n_tiles * slices][M][128] float32 partial sums
+    unsigned int* tickets;   // slices > 1: one per tile, zero before the launch and after it
 };
 
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Barrier of `threads` threads that returns whether `ok` held for all of them: the epilogue warps decide together
+// whether a wait ran out, so that none of them goes on to a barrier that the others have left.
+__device__ __forceinline__ bool named_barrier_all(int id, int threads, bool ok) {
+    uint32_t all;
+    asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 q, %3, 0;\nbar.red.and.pred p, %1, %2, q;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(all) : "r"(id), "r"(threads), "r"((uint32_t)ok) : "memory");
+    return all != 0;
+}
+
+constexpr int kReduceCols = 16;
+
+// Four values to consecutive addresses: one vector store where the address allows it and all four are inside.
+template <typename OutT>
+__device__ __forceinline__ void store4(OutT* dst, const float v[4], int valid, bool vector_ok) {
+    if (valid >= 4 && vector_ok) {
+        if constexpr (sizeof(OutT) == 2) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(dst) = packed;
+        } else {
+            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    } else {
+        for (int i = 0; i < 4 && i < valid; ++i) dst[i] = from_float<OutT>(v[i]);
+    }
+}
+
+// Sum of `slices` partial tiles [M][128 rows] float32 (slice_stride floats apart) into rows n0.. of out[M][width],
+// added in the order of the slices.  128 threads.  Plain: thread = (32 row quads, 4 column groups).  SwiGLU: rows
+// 0-63 are gate rows and 64-127 their up rows, thread = (16 row quads, 8 column groups), out = silu(gate) * up.
 template <int MODE, typename OutT>
-__global__ void __launch_bounds__(kThreads)
+__device__ __forceinline__ void reduce_tile(const float* __restrict__ base, size_t slice_stride, int slices, int M, int width,
+                                            int n0, int etid, OutT* __restrict__ out) {
+    constexpr int kQuads = (MODE == kSwiGLU) ? 16 : 32;
+    constexpr int kGroups = 128 / kQuads;
+    constexpr int kVec = (MODE == kSwiGLU) ? 2 : 1;                 // float4 loads per column and slice
+    constexpr int kCols = kReduceCols / kVec;
+    const int quad = etid % kQuads, group = etid / kQuads;
+    const int row = quad * 4;
+    const int valid = width - (n0 + row);
+    if (valid <= 0) return;
+    const bool vector_ok = (width % 4 == 0) && (n0 % 4 == 0) &&
+                           ((reinterpret_cast<uintptr_t>(out) % (4 * sizeof(OutT))) == 0);
+    for (int c0 = group; c0 < M; c0 += kGroups * kCols) {
+        float4 acc[kCols][kVec];
+#pragma unroll
+        for (int i = 0; i < kCols; ++i)
+#pragma unroll
+            for (int h = 0; h < kVec; ++h) acc[i][h] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < slices; ++s) {
+            float4 v[kCols][kVec];
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) {
+                const int c = c0 + i * kGroups;
+#pragma unroll
+                for (int h = 0; h < kVec; ++h)
+                    v[i][h] = c < M ? __ldcg(reinterpret_cast<const float4*>(base + s * slice_stride + (size_t)c * kRows + row + h * (kRows / 2)))
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < kCols; ++i)
+#pragma unroll
+                for (int h = 0; h < kVec; ++h) {
+                    acc[i][h].x += v[i][h].x; acc[i][h].y += v[i][h].y; acc[i][h].z += v[i][h].z; acc[i][h].w += v[i][h].w;
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < kCols; ++i) {
+            const int c = c0 + i * kGroups;
+            if (c >= M) break;
+            float r[4] = {acc[i][0].x, acc[i][0].y, acc[i][0].z, acc[i][0].w};
+            if (MODE == kSwiGLU) {
+                const float u[4] = {acc[i][kVec - 1].x, acc[i][kVec - 1].y, acc[i][kVec - 1].z, acc[i][kVec - 1].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) r[e] = r[e] / (1.0f + expf(-r[e])) * u[e];
+            }
+            store4<OutT>(out + (size_t)c * width + n0 + row, r, valid, vector_ok);
+        }
+    }
+}
+
+template <int MODE, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_stream_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                            OutT* __restrict__ out, const StreamArgs a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int x_bytes = a.n_pad * kBK * 2;
     const int stage_bytes = kWBytes + x_bytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + a.bar_offset);            // full[stages], empty[stages], acc_full
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 1);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* recv = reinterpret_cast<float*>(smem + a.recv_offset);                 // [splits][cols_per][128]
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t rank = cluster_rank();
-    const int tile = blockIdx.x / a.splits;
-    const int k_tiles = (a.K + kBK - 1) / kBK;
-    const int kt_begin = (int)((long long)k_tiles * rank / a.splits), kt_end = (int)((long long)k_tiles * (rank + 1) / a.splits);
-    const int n_kt = kt_end - kt_begin;
-    constexpr int kTileCols = (MODE == kSwiGLU) ? kRows / 2 : kRows;              // output features of a tile
-    const int n0 = tile * kTileCols;
-    const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + kMaxStages), acc_full = smem_addr(bars + 2 * kMaxStages);
-
-    if (tid == 0) {
-        for (int s = 0; s < a.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(acc_full, 1);
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemColumns));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_base = *tmem_slot;
-
-    if (warp == 0) {
-        // ---------------- TMA producer
-        if (lane == 0) {
-            const uint64_t policy = policy_evict_first();
-            auto load_w = [&](int s, int kt) {
-                const uint32_t w_dst = smem_addr(smem + s * stage_bytes);
-                mbar_expect_tx(full0 + 8 * s, stage_bytes);
-                if (MODE == kSwiGLU) {
-                    tma_load_2d_hint(w_dst, &map_w, full0 + 8 * s, kt * kBK, n0, policy);
-                    tma_load_2d_hint(w_dst + kWBytes / 2, &map_w, full0 + 8 * s, kt * kBK, a.inter + n0, policy);
-                } else {
-                    tma_load_2d_hint(w_dst, &map_w, full0 + 8 * s, kt * kBK, n0, policy);
-                }
-            };
-            auto load_x = [&](int s, int kt) {
-                tma_load_2d(smem_addr(smem + s * stage_bytes + kWBytes), &map_x, full0 + 8 * s, kt * kBK, 0);
-            };
-            // the weights depend on no earlier kernel: the first stages' W is on its way before this kernel may read x
-            const int first = n_kt < a.stages ? n_kt : a.stages;
-            for (int i = 0; i < first; ++i) load_w(i, kt_begin + i);
-            pdl_wait();
-            for (int i = 0; i < first; ++i) load_x(i, kt_begin + i);
-            bool ok = true;
-            for (int i = first; i < n_kt; ++i) {
-                const int s = i % a.stages;
-                if (!mbar_wait(empty0 + 8 * s, ((i / a.stages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                load_w(s, kt_begin + i);
-                load_x(s, kt_begin + i);
-            }
-            if (!ok) { *abort_flag = 1; atomicMax(&g_stream_error, 2u); }
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer: the warp walks the loop uniformly, one elected lane issues
-        const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
-        const uint64_t desc0 = umma_desc(smem_addr(smem));
-        // float32 accumulator, bfloat16 A and B, both K-major, N >> 3, M >> 4
-        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.n_pad >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
-        bool ok = true;
-        for (int i = 0; i < n_kt; ++i) {
-            const int s = i % a.stages;
-            if (!mbar_wait(full0 + 8 * s, (i / a.stages) & 1, abort_flag)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t w_desc = desc0 + (uint64_t)((uint32_t)(s * stage_bytes) >> 4);
-            const uint64_t x_desc = w_desc + (uint64_t)(kWBytes >> 4);
-            if (elect_one()) {
-#pragma unroll
-                for (int k = 0; k < kBK / 16; ++k)
-                    umma_bf16(tmem_u, w_desc + (uint64_t)(k * 2), x_desc + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
-                umma_commit(empty0 + 8 * s);
-                if (i == n_kt - 1) umma_commit(acc_full);
-            }
-            __syncwarp();
-        }
-        if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_stream_error, 3u); }
-    } else {
-        // ---------------- accumulator -> the blocks that own the token columns.  This thread holds weight row `row`.
-        const int quarter = warp & 3;
-        const int row = quarter * 32 + lane;
-        bool ok = n_kt == 0 || mbar_wait(acc_full, 0, abort_flag);
-        if (!ok && lane == 0) { *abort_flag = 1; atomicMax(&g_stream_error, 4u); }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        pdl_trigger();
-        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t recv_local = smem_addr(recv);
-        for (int c0 = 0; c0 < a.M; c0 += 32) {
-            uint32_t v[32];
-            if (ok && n_kt > 0) {
-                tmem_ld32(lane_base + c0, v);
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0u;
-            }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const int c = c0 + i;
-                if (c < a.M) {
-                    const uint32_t owner = (uint32_t)(c / a.cols_per);
-                    const uint32_t local = recv_local + (uint32_t)((((int)rank * a.cols_per + (c - (int)owner * a.cols_per)) * kRows + row) * 4);
-                    if (a.splits == 1) *reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(recv) + (local - recv_local)) = __uint_as_float(v[i]);
-                    else store_remote(remote_addr(local, owner), __uint_as_float(v[i]));
-                }
-            }
-        }
-    }
-    __syncwarp();
-    if (*abort_flag) {
-        for (int i = 0; i < 2000; ++i) __nanosleep(1000);      // copies that are still in flight may land
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    cluster_sync_all();          // every block's partial sums have arrived; nobody writes into a peer's memory after this
-    if (warp >= 2) {
-        // ---------------- add up the slices of K for this block's token columns and store them
-        const int r = (warp - 2) * 32 + lane;                  // weight row within the tile
-        const int c_begin = (int)rank * a.cols_per;
-        const int c_end = min(a.M, c_begin + a.cols_per);
-        for (int c = c_begin; c < c_end; ++c) {
-            const float* col = recv + (size_t)(c - c_begin) * kRows;
-            if (MODE == kSwiGLU) {
-                if (r < kRows / 2) {
-                    float gate = 0.0f, up = 0.0f;
-                    for (int s = 0; s < a.splits; ++s) {
-                        gate += col[(size_t)s * a.cols_per * kRows + r];
-                        up += col[(size_t)s * a.cols_per * kRows + r + kRows / 2];
-                    }
-                    if (n0 + r < a.inter) out[(size_t)c * a.inter + n0 + r] = from_float<OutT>(gate / (1.0f + expf(-gate)) * up);
-                }
-            } else {
-                float sum = 0.0f;
-                for (int s = 0; s < a.splits; ++s) sum += col[(size_t)s * a.cols_per * kRows + r];
-                if (n0 + r < a.N) out[(size_t)c * a.N + n0 + r] = from_float<OutT>(sum);
-            }
-        }
-    }
-    __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
-}
-
-// ---------------------------------------------------------------------------------------------
-// The same product without slices of K, for weights with more tiles than SMs (gate/up, the head): a persistent
-// grid of one block per SM walks over the tiles; two accumulators in tensor memory take turns, so that the ring of
-// TMA stages never pauses while a finished tile is read out and stored.  Plain tiles are stored straight from
-// registers (a warp's 32 lanes are 32 consecutive output features of one token); SwiGLU tiles pass the up half
-// through shared memory to the warps that hold the gate half.
-constexpr int kPersistTmem = 256;          // two accumulators of up to 128 columns
-
-__device__ __forceinline__ void named_barrier(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-template <int MODE, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tcgen05_stream_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                                      OutT* __restrict__ out, const StreamArgs a, int n_tiles) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int x_bytes = a.n_pad * kBK * 2;
-    const int stage_bytes = kWBytes + x_bytes;
-    float* stage_up = reinterpret_cast<float*>(smem + a.recv_offset);             // SwiGLU: [32 columns][64 rows]
+    float* stage_up = reinterpret_cast<float*>(smem + a.up_offset);               // SwiGLU, one slice: [32 columns][64 rows]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + a.bar_offset);            // full[8], empty[8], acc_full[2], acc_empty[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* last_flag = const_cast<int*>(abort_flag) + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int k_tiles = (a.K + kBK - 1) / kBK;
+    const int n_units = a.n_tiles * a.slices;
     constexpr int kTileCols = (MODE == kSwiGLU) ? kRows / 2 : kRows;
     const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + kMaxStages);
     const uint32_t acc_full0 = smem_addr(bars + 2 * kMaxStages), acc_empty0 = smem_addr(bars + 2 * kMaxStages + 2);
+    // unit u = tile * slices + slice covers k-tiles [k_tiles * slice / slices, k_tiles * (slice + 1) / slices)
+    auto kt_first = [&](int unit) { return (int)((long long)k_tiles * (unit % a.slices) / a.slices); };
+    auto kt_last = [&](int unit) { return (int)((long long)k_tiles * (unit % a.slices + 1) / a.slices); };
 
     if (tid == 0) {
         for (int s = 0; s < a.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -287,7 +199,7 @@ gemm_tcgen05_stream_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kPersistTmem));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(kTmemColumns));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -309,39 +221,44 @@ gemm_tcgen05_stream_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
                 tma_load_2d(smem_addr(smem + s * stage_bytes + kWBytes), &map_x, full0 + 8 * s, kt * kBK, 0);
             };
             // the weights depend on no earlier kernel: the first stages' W is on its way before this kernel may read x
-            const int first = k_tiles < a.stages ? k_tiles : a.stages;
-            const int tile0 = blockIdx.x;
-            if (tile0 < n_tiles)
-                for (int i = 0; i < first; ++i) load_w(i, i, tile0 * kTileCols);
+            const int unit0 = blockIdx.x;
+            int first = 0;
+            if (unit0 < n_units) {
+                const int n_kt0 = kt_last(unit0) - kt_first(unit0);
+                first = n_kt0 < a.stages ? n_kt0 : a.stages;
+                for (int i = 0; i < first; ++i) load_w(i, kt_first(unit0) + i, (unit0 / a.slices) * kTileCols);
+            }
             pdl_wait();
-            if (tile0 < n_tiles)
-                for (int i = 0; i < first; ++i) load_x(i, i);
+            for (int i = 0; i < first; ++i) load_x(i, kt_first(unit0) + i);
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = tile0; tile < n_tiles && ok; tile += gridDim.x) {
-                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
-                    if (tile == tile0 && kt < first) continue;           // asked for above
+            for (int unit = unit0; unit < n_units && ok; unit += gridDim.x) {
+                const int n0 = (unit / a.slices) * kTileCols;
+                for (int kt = kt_first(unit); kt < kt_last(unit); ++kt, ++it) {
+                    if (unit == unit0 && (int)it < first) continue;      // asked for above
                     const int s = it % a.stages;
                     if (!mbar_wait(empty0 + 8 * s, ((it / a.stages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                    load_w(s, kt, tile * kTileCols);
+                    load_w(s, kt, n0);
                     load_x(s, kt);
                 }
             }
             if (!ok) { *abort_flag = 1; atomicMax(&g_stream_error, 2u); }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer
+        // ---------------- MMA issuer: the warp walks the loop uniformly, one elected lane issues
         const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);
         const uint64_t desc0 = umma_desc(smem_addr(smem));
+        // float32 accumulator, bfloat16 A and B, both K-major, N >> 3, M >> 4
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.n_pad >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
         uint32_t it = 0;
         int j = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
+        for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ++j) {
             const int acc = j & 1;
             ok = mbar_wait(acc_empty0 + 8 * acc, ((j >> 1) & 1) ^ 1, abort_flag);
             const uint32_t tmem_d = tmem_u + acc * 128;
-            for (int kt = 0; kt < k_tiles && ok; ++kt, ++it) {
+            const int kt0 = kt_first(unit), kt1 = kt_last(unit);
+            for (int kt = kt0; kt < kt1 && ok; ++kt, ++it) {
                 const int s = it % a.stages;
                 if (!mbar_wait(full0 + 8 * s, (it / a.stages) & 1, abort_flag)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -350,9 +267,9 @@ gemm_tcgen05_stream_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
                 if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)
-                        umma_bf16(tmem_d, w_desc + (uint64_t)(k * 2), x_desc + (uint64_t)(k * 2), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16(tmem_d, w_desc + (uint64_t)(k * 2), x_desc + (uint64_t)(k * 2), idesc, (kt > kt0 || k > 0) ? 1u : 0u);
                     umma_commit(empty0 + 8 * s);
-                    if (kt == k_tiles - 1) umma_commit(acc_full0 + 8 * acc);
+                    if (kt == kt1 - 1) umma_commit(acc_full0 + 8 * acc);
                 }
                 __syncwarp();
             }
@@ -362,17 +279,51 @@ gemm_tcgen05_stream_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
         // ---------------- epilogue: this thread holds weight row `row` of the tile, one token per column
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
+        const int etid = tid - 64;                                              // 0 .. 127 among the epilogue threads
         int j = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
+        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++j) {
             const int acc = j & 1;
+            const int tile = unit / a.slices;
             const int n0 = tile * kTileCols;
-            if (!mbar_wait(acc_full0 + 8 * acc, (j >> 1) & 1, abort_flag)) {
+            if (!named_barrier_all(4, 128, mbar_wait(acc_full0 + 8 * acc, (j >> 1) & 1, abort_flag))) {
                 if (lane == 0) { *abort_flag = 1; atomicMax(&g_stream_error, 4u); }
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (tile + (int)gridDim.x >= n_tiles) pdl_trigger();                 // this block's last tile
+            if (unit + (int)gridDim.x >= n_units) pdl_trigger();                  // this block's last unit
             const uint32_t lane_base = tmem_base + acc * 128 + ((uint32_t)(quarter * 32) << 16);
+            if (a.slices > 1) {
+                // partial sums of this slice -> workspace [unit][token][128 rows] (a warp's lanes are consecutive rows)
+                float* part = a.workspace + (size_t)unit * a.M * kRows;
+                for (int c0 = 0; c0 < a.M; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_base + c0, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c0 + i < a.M) __stcg(part + (size_t)(c0 + i) * kRows + row, __uint_as_float(v[i]));
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);                // the accumulator is free again
+                named_barrier(1, 128);                                           // all partial sums are written ...
+                if (etid == 0) {
+                    __threadfence();                                             // ... and visible before the ticket is
+                    *last_flag = atomicAdd(a.tickets + tile, 1u) == (unsigned int)(a.slices - 1) ? 1 : 0;
+                }
+                named_barrier(2, 128);
+                if (*last_flag) {
+                    // the tile's last slice to finish: add the slices in their order and store the tile.  A thread
+                    // owns four consecutive rows in kReduceCols columns and has all their loads in flight at once:
+                    // the loads of one slice cost one trip to L2 together, not one each.
+                    __threadfence();
+                    const float* base = a.workspace + (size_t)tile * a.slices * a.M * kRows;
+                    const size_t slice_stride = (size_t)a.M * kRows;
+                    reduce_tile<MODE, OutT>(base, slice_stride, a.slices, a.M, MODE == kSwiGLU ? a.inter : a.N, n0, etid, out);
+                    if (etid == 0) a.tickets[tile] = 0;                          // ready for the next launch
+                }
+                named_barrier(3, 128);                                           // last_flag is read by all before it is set again
+                continue;
+            }
             for (int c0 = 0; c0 < a.M; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(lane_base + c0, v);
@@ -405,11 +356,11 @@ gemm_tcgen05_stream_persistent_kernel(const __grid_constant__ CUtensorMap map_x,
     }
     __syncwarp();
     if (*abort_flag) {
-        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);      // copies that are still in flight may land
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kPersistTmem));
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
 }
 
 // Row-major [rows, K] bfloat16 matrix, boxes of box_rows x 64 columns, 128-byte swizzle, zero fill outside.
@@ -440,77 +391,56 @@ int forced(const char* name) {
     return v ? atoi(v) : 0;
 }
 
-template <int MODE, typename OutT>
-int launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, StreamArgs a, int tiles, cudaStream_t stream) {
-    const int k_tiles = (a.K + kBK - 1) / kBK;
-    // Slices of K: as many as give every SM a block (one block per SM then, with a deep ring); with more tiles than
-    // SMs no slices and two blocks per SM (rings half as deep, the receive buffer in the ring's place).
-    int splits = sm_count() / tiles;
-    if (splits > kMaxCluster) splits = kMaxCluster;
-    if (splits > k_tiles) splits = k_tiles;
-    if (splits < 1) splits = 1;
-    if (forced("PULSAR_STREAM_SPLITS") > 0) splits = forced("PULSAR_STREAM_SPLITS") < k_tiles ? forced("PULSAR_STREAM_SPLITS") : k_tiles;
-    if (splits > kMaxCluster) splits = kMaxCluster;
-    if (splits == 1 && forced("PULSAR_STREAM_PERSISTENT") >= 0) {
-        // persistent: one block per SM, a deep ring, two accumulators
-        a.splits = 1;
-        a.cols_per = a.M;
-        const int stage_bytes1 = kWBytes + a.n_pad * kBK * 2;
-        const int up_bytes = MODE == kSwiGLU ? 32 * (kRows / 2) * 4 : 0;
-        int stages1 = (220 * 1024 - 1024 - 256 - up_bytes) / stage_bytes1;
-        if (stages1 > kMaxStages) stages1 = kMaxStages;
-        if (forced("PULSAR_STREAM_STAGES") > 0 && forced("PULSAR_STREAM_STAGES") < stages1) stages1 = forced("PULSAR_STREAM_STAGES");
-        if (stages1 < 2) return PB_ERR_BAD_SIZE;
-        a.stages = stages1;
-        a.recv_offset = stages1 * stage_bytes1;
-        a.bar_offset = (a.recv_offset + up_bytes + 15) / 16 * 16;
-        const int smem1 = a.bar_offset + 256 + 1024;
-        static bool configured1 = false;
-        if (!configured1) {
-            cudaError_t rc = cudaFuncSetAttribute(gemm_tcgen05_stream_persistent_kernel<MODE, OutT>,
-                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            if (rc != cudaSuccess) return (int)rc;
-            configured1 = true;
-        }
-        const int grid = tiles < sm_count() ? tiles : sm_count();
-        return launch_pdl(gemm_tcgen05_stream_persistent_kernel<MODE, OutT>, grid, kThreads, smem1, stream, mx, mw, (OutT*)out, a, tiles);
+// Slices of K for `tiles` tiles: the fewest that make the units fill their rounds of the SMs to 0.9 or better,
+// never more than the k-tiles or kMaxSlices; one slice where the tiles alone make four rounds or more (the last,
+// partly filled round then costs less than the partial sums would).
+int choose_slices(int tiles, int k_tiles) {
+    const int sms = sm_count();
+    if (tiles >= 4 * sms) return 1;
+    int best = 1;
+    double best_fill = 0.0;
+    for (int s = 1; s <= kMaxSlices && s <= k_tiles; ++s) {
+        const long long units = (long long)tiles * s;
+        const long long rounds = (units + sms - 1) / sms;
+        const double fill = (double)units / (double)(rounds * sms);
+        if (fill > best_fill + 1e-9) { best = s; best_fill = fill; }
+        if (fill >= 0.9) break;
     }
-    a.splits = splits;
-    a.cols_per = (a.M + splits - 1) / splits;
+    return best;
+}
+
+template <int MODE, typename OutT>
+int launch(const CUtensorMap& mx, const CUtensorMap& mw, void* out, StreamArgs a, float* workspace, long long workspace_floats,
+           unsigned int* tickets, int n_tickets, cudaStream_t stream) {
+    const int k_tiles = (a.K + kBK - 1) / kBK;
+    int slices = choose_slices(a.n_tiles, k_tiles);
+    if (forced("PULSAR_STREAM_SLICES") > 0) slices = forced("PULSAR_STREAM_SLICES") < k_tiles ? forced("PULSAR_STREAM_SLICES") : k_tiles;
+    if (slices > kMaxSlices) slices = kMaxSlices;
+    if (slices > 1 && (workspace == nullptr || tickets == nullptr ||
+                       (long long)a.n_tiles * slices * a.M * kRows > workspace_floats || a.n_tiles > n_tickets))
+        slices = 1;                                                // no room for partial sums: whole tiles only
+    a.slices = slices;
+    a.workspace = workspace;
+    a.tickets = tickets;
     const int stage_bytes = kWBytes + a.n_pad * kBK * 2;
-    const int recv_bytes = splits * a.cols_per * kRows * 4;
-    const int budget = splits > 1 ? 220 * 1024 : 110 * 1024;         // one block per SM, or two
-    int stages = (budget - 1024 - 256 - (splits > 1 ? recv_bytes : 0)) / stage_bytes;
+    const int up_bytes = MODE == kSwiGLU ? 32 * (kRows / 2) * 4 : 0;
+    int stages = (220 * 1024 - 1024 - 256 - up_bytes) / stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     if (forced("PULSAR_STREAM_STAGES") > 0 && forced("PULSAR_STREAM_STAGES") < stages) stages = forced("PULSAR_STREAM_STAGES");
-    if (stages < 2 || (splits == 1 && stages * stage_bytes < recv_bytes)) return PB_ERR_BAD_SIZE;
+    if (stages < 2) return PB_ERR_BAD_SIZE;
     a.stages = stages;
-    const int ring = stages * stage_bytes;
-    a.recv_offset = splits > 1 ? ring : 0;
-    a.bar_offset = (splits > 1 ? ring + recv_bytes : ring);
-    a.bar_offset = (a.bar_offset + 15) / 16 * 16;
+    a.up_offset = stages * stage_bytes;
+    a.bar_offset = (a.up_offset + up_bytes + 15) / 16 * 16;
     const int smem_bytes = a.bar_offset + 256 + 1024;
-    static int configured = 0;
-    if (configured < smem_bytes) {
+    static bool configured = false;
+    if (!configured) {
         cudaError_t rc = cudaFuncSetAttribute(gemm_tcgen05_stream_kernel<MODE, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (rc != cudaSuccess) return (int)rc;
-        configured = 227 * 1024;
+        configured = true;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(tiles * splits);
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem_bytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = splits;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    return (int)cudaLaunchKernelEx(&cfg, gemm_tcgen05_stream_kernel<MODE, OutT>, mx, mw, (OutT*)out, a);
+    const long long units = (long long)a.n_tiles * slices;
+    const int grid = (int)(units < sm_count() ? units : sm_count());
+    return launch_pdl(gemm_tcgen05_stream_kernel<MODE, OutT>, grid, kThreads, smem_bytes, stream, mx, mw, (OutT*)out, a);
 }
 
 }  // namespace
@@ -523,6 +453,18 @@ PB_EXPORT int pb_gemm_tcgen05_stream_supported(int mode, int M, int N, int K) {
     return mode == kPlain ? 1 : 0;
 }
 
+// What the kernel wants for this problem in order to cut K into slices: `floats` of float32 workspace and
+// `tickets` ticket words; both 0 when it works on whole tiles.
+PB_EXPORT int pb_gemm_tcgen05_stream_workspace(int mode, int M, int N, int K, long long* floats, int* tickets) {
+    const int tiles = mode == kSwiGLU ? (N / 2 + kRows / 2 - 1) / (kRows / 2) : (N + kRows - 1) / kRows;
+    int slices = choose_slices(tiles, (K + kBK - 1) / kBK);
+    if (forced("PULSAR_STREAM_SLICES") > 0) slices = forced("PULSAR_STREAM_SLICES");
+    if (slices > kMaxSlices) slices = kMaxSlices;
+    *tickets = slices > 1 ? tiles : 0;
+    *floats = slices > 1 ? (long long)tiles * slices * M * kRows : 0;
+    return 0;
+}
+
 // limit > 0: the new limit of the kernel's bounded waits in clock cycles; error >= 0: the new value of the error
 // word; address: receives the word's device address.  Returns 0, or -1 when a CUDA call failed.
 PB_EXPORT int pb_gemm_tcgen05_stream_wait_control(long long limit, int error, void** address) {
@@ -531,7 +473,10 @@ PB_EXPORT int pb_gemm_tcgen05_stream_wait_control(long long limit, int error, vo
 
 // mode 0: out[M, N] = x W^T (out_dtype bfloat16 or float32).  mode 1: W = [gate rows; up rows], N = 2 * inter,
 // out[M, inter] = silu(x Wg^T) * (x Wu^T).  x [M, K] and W [N, K] bfloat16, 16-byte aligned, M <= 128.
+// workspace (workspace_floats float32) and tickets (n_tickets words, zero; the kernel leaves them zero) let the
+// kernel cut K into slices; without them, or where they are too small, it works on whole tiles.
 PB_EXPORT int pb_gemm_tcgen05_stream(int mode, int out_dtype, const void* x, const void* w, void* out, int M, int N, int K,
+                                     float* workspace, long long workspace_floats, unsigned int* tickets, int n_tickets,
                                      cudaStream_t stream) {
     if (!pb_gemm_tcgen05_stream_supported(mode, M, N, K)) return PB_ERR_BAD_SIZE;
     if ((((uintptr_t)x | (uintptr_t)w) & 15) != 0) return PB_ERR_BAD_SIZE;
@@ -548,11 +493,11 @@ PB_EXPORT int pb_gemm_tcgen05_stream(int mode, int out_dtype, const void* x, con
     rc = make_map(&mw, w, N, K, mode == kSwiGLU ? kRows / 2 : kRows);
     if (rc != 0) return rc;
     if (mode == kSwiGLU) {
-        const int tiles = (a.inter + kRows / 2 - 1) / (kRows / 2);
-        if (out_dtype == PB_BF16) return launch<kSwiGLU, bf16>(mx, mw, out, a, tiles, stream);
-        return launch<kSwiGLU, float>(mx, mw, out, a, tiles, stream);
+        a.n_tiles = (a.inter + kRows / 2 - 1) / (kRows / 2);
+        if (out_dtype == PB_BF16) return launch<kSwiGLU, bf16>(mx, mw, out, a, workspace, workspace_floats, tickets, n_tickets, stream);
+        return launch<kSwiGLU, float>(mx, mw, out, a, workspace, workspace_floats, tickets, n_tickets, stream);
     }
-    const int tiles = (N + kRows - 1) / kRows;
-    if (out_dtype == PB_BF16) return launch<kPlain, bf16>(mx, mw, out, a, tiles, stream);
-    return launch<kPlain, float>(mx, mw, out, a, tiles, stream);
+    a.n_tiles = (N + kRows - 1) / kRows;
+    if (out_dtype == PB_BF16) return launch<kPlain, bf16>(mx, mw, out, a, workspace, workspace_floats, tickets, n_tickets, stream);
+    return launch<kPlain, float>(mx, mw, out, a, workspace, workspace_floats, tickets, n_tickets, stream);
 }

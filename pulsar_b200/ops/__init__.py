@@ -67,7 +67,8 @@ _SIGNATURES = {
     "pb_gemm_tcgen05": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_gemm_tcgen05_supported": [_I, _I, _I, _I],
     "pb_gemm_tcgen05_error": [],
-    "pb_gemm_tcgen05_stream": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
+    "pb_gemm_tcgen05_stream": [_I, _I, _P, _P, _P, _I, _I, _I, _P, ctypes.c_longlong, _P, _I, _P],
+    "pb_gemm_tcgen05_stream_workspace": [_I, _I, _I, _I, _P, _P],
     "pb_gemm_tcgen05_stream_supported": [_I, _I, _I, _I],
     "pb_gemm_tcgen05_stream_wait_control": [ctypes.c_longlong, _I, _P],
     "pb_gemm_tcgen05_wait_control": [ctypes.c_longlong, _I, _P],
@@ -402,10 +403,34 @@ def _stream_wanted(m: int, n: int) -> bool:
     return STREAM_GEMM == "1" or n >= _STREAM_MIN_ROWS
 
 
+# Float32 partial sums and tile tickets of the product below, one pair per device, grown on demand.  A buffer
+# that was outgrown stays alive: a captured graph may still name it.  Kernels of one stream share the pair (each
+# finishes with it before the next one starts, and leaves the tickets zero).
+_stream_scratch = {}
+_stream_scratch_old = []
+
+
+def _stream_workspace(device: torch.device, mode: int, m: int, n: int, k: int):
+    floats, tickets = ctypes.c_longlong(0), ctypes.c_int(0)
+    fn("pb_gemm_tcgen05_stream_workspace")(mode, m, n, k, ctypes.byref(floats), ctypes.byref(tickets))
+    if floats.value == 0:
+        return None, None
+    have = _stream_scratch.get(device)
+    if have is None or have[0].numel() < floats.value or have[1].numel() < tickets.value:
+        if torch.cuda.is_current_stream_capturing():
+            return None, None                 # no allocation inside a capture: whole tiles this once
+        if have is not None:
+            _stream_scratch_old.append(have)
+        have = (torch.empty(max(floats.value, have[0].numel() if have else 0), dtype=torch.float32, device=device),
+                torch.zeros(max(tickets.value, have[1].numel() if have else 0, 2048), dtype=torch.int32, device=device))
+        _stream_scratch[device] = have
+    return have
+
+
 def gemm_tcgen05_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> bool:
     """The weight-streaming tcgen05 / TMA product for up to 128 tokens (bfloat16 operands, float32 accumulation
-    in tensor memory, K split over the blocks of a cluster).  ``swiglu`` as in ``gemm_skinny``.  Returns False,
-    having done nothing, when the sizes are not the kernel's."""
+    in tensor memory, K cut into slices whose partial sums meet in a float32 workspace).  ``swiglu`` as in
+    ``gemm_skinny``.  Returns False, having done nothing, when the sizes are not the kernel's."""
     m, k = a.shape
     n = w.shape[0]
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != k:
@@ -415,7 +440,11 @@ def gemm_tcgen05_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swi
         return False
     _cuda(a, w, out)
     assert out.shape == (m, n // 2 if swiglu else n)
-    status = fn("pb_gemm_tcgen05_stream")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k, stream())
+    work, tickets = _stream_workspace(a.device, mode, m, n, k)
+    status = fn("pb_gemm_tcgen05_stream")(mode, code(out.dtype), _p(a), _p(w), _p(out), m, n, k,
+                                          _p(work) if work is not None else None, work.numel() if work is not None else 0,
+                                          _p(tickets) if tickets is not None else None,
+                                          tickets.numel() if tickets is not None else 0, stream())
     if status == -3:
         return False                 # sizes that leave no room for its ring of stages
     check(status, "gemm_tcgen05_stream")

@@ -275,7 +275,7 @@ def test_gemm_skinny_declines_other_sizes():
                                  (48, 8192)])
 def test_gemm_tcgen05_stream(m, n, k):
     """The weight-streaming tcgen05 product for 17 to 128 tokens against float64: tiles that hang over the rows of W
-    and the tail of K, one to eight slices of K per cluster (few tiles) and none (many tiles, two blocks per SM),
+    and the tail of K, several slices of K whose partial sums meet in the workspace (few tiles) and whole tiles (many),
     float32 and bfloat16 outputs, the SwiGLU epilogue; weights made large in places so that a wrong swizzle,
     descriptor or owner of a column would show."""
     from pulsar_b200 import ops
