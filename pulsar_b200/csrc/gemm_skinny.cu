@@ -170,6 +170,7 @@ __device__ __forceinline__ Wide load_stream32(const void* p) {
 __device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
     Wide v;
     if (ok) {
+        // (one 32-byte load per lane instead of two of 16 was no faster: 4.86 against 4.83 ms per step of 16 sequences)
         v.lo = __ldg(reinterpret_cast<const uint4*>(p));
         v.hi = __ldg(reinterpret_cast<const uint4*>(p) + 1);
     } else {
@@ -178,7 +179,9 @@ __device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
     return v;
 }
 
-// kPre > 0: besides the first batch of register loads, every warp asks for its next kPre k-blocks by cp.async into
+// kPre > 0 (up to 8 tokens only: with 9 to 16 the buffer takes from the L1 cache what the tokens, which every block
+// of an SM reads whole, need there; measured 5.08 against 4.83 ms per step of 16 sequences): besides the first batch
+// of register loads, every warp asks for its next kPre k-blocks by cp.async into
 // shared memory before the kernel waits for its predecessor, so that twice the bytes are on their way while the
 // kernel before this one ends; a warp copies and reads only its own part (no block barrier), rows padded by 16
 // bytes against bank conflicts.  The sums keep their order.
@@ -212,7 +215,9 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
     __shared__ float scale_s[kScaled ? 8 * NT : 1];                 // kScaled: rsqrt(mean(x^2) + eps) per token
     // kScaled: a copy of fuse.part_in.  Where part of the weights is prefetched through shared memory, the copy
     // takes that buffer's place once a warp has read its part of it (1,024 floats in each warp's region).
-    __shared__ __align__(16) float parts_s[(kScaled && kPre == 0) ? kMaxParts * 8 * NT : 4];
+    // Without a prefetch buffer the copy lies in dynamic shared memory of n_parts * M floats: no more than this
+    // product needs, since what shared memory takes the L1 cache loses, which holds the tokens for all blocks of an SM.
+    extern __shared__ __align__(16) float parts_s[];
     __shared__ float square_s[kAcc ? 8 * NT : 1][kAcc ? kRows : 1]; // kAcc: x_new^2 of the block's columns
     __shared__ __align__(16) unsigned char pre[kPre > 0 ? kWarps : 1][kPre > 0 ? kRows : 1][kPre > 0 ? kPreRow : 16];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -332,6 +337,8 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
         for (int i = warp * 256 + lane; i < end; i += 32) cp_async16(smem_u32(part_slot(4 * i)), fuse.part_in + 4 * i, true);
         cp_async_commit();
     }
+    // (Asking for a register pair again as soon as its k-block is multiplied, so that the next batch is on its way
+    // while this one is used, was slower: 5.05 against 4.83 ms per step of 16 sequences, 3.72 against 3.66 of 8.)
     for (; kb + kUnroll <= kb_end; kb += kUnroll, loaded = false) {
         if (!loaded) {
 #pragma unroll
@@ -412,7 +419,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
 }
 
 template <int NT, int MODE, typename OutT, int kUnroll, bool kEvictFirst>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, kUnroll <= 2 ? 3 : 2)
 gemm_skinny_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* __restrict__ out, int M, int N, int K,
                         int inter) {
     skinny_wide_body<NT, MODE, OutT, kUnroll, kEvictFirst, 0>(x, w, out, M, N, K, inter);
@@ -483,16 +490,16 @@ int launch_wide(int mode, int out_dtype, const bf16* xp, const bf16* wp, void* o
     return launch_pdl(gemm_skinny_wide_kernel<NT, kPlain, float, kU, kEvictFirst>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
 }
 
-template <int kU>
+template <int NT, int kU>
 int launch_prefetch(int mode, int out_dtype, const bf16* xp, const bf16* wp, void* out, int M, int N, int K, cudaStream_t stream) {
     if (mode == kSwiGLU) {
         const int inter = N / 2;
         if (out_dtype != PB_BF16) return PB_ERR_BAD_DTYPE;
-        return launch_pdl(gemm_skinny_wide_prefetch_kernel<1, kSwiGLU, bf16, kU>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
+        return launch_pdl(gemm_skinny_wide_prefetch_kernel<NT, kSwiGLU, bf16, kU>, inter / 8, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, inter);
     }
     if (out_dtype == PB_BF16)
-        return launch_pdl(gemm_skinny_wide_prefetch_kernel<1, kPlain, bf16, kU>, N / kRows, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, 0);
-    return launch_pdl(gemm_skinny_wide_prefetch_kernel<1, kPlain, float, kU>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
+        return launch_pdl(gemm_skinny_wide_prefetch_kernel<NT, kPlain, bf16, kU>, N / kRows, kWarps * 32, 0, stream, xp, wp, (bf16*)out, M, N, K, 0);
+    return launch_pdl(gemm_skinny_wide_prefetch_kernel<NT, kPlain, float, kU>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
 }
 
 template <int NT, int kUnroll>
@@ -502,7 +509,7 @@ int launch_u(int mode, int out_dtype, const void* x, const void* w, void* out, i
     if (K % 64 == 0 && (((uintptr_t)x | (uintptr_t)w) & 31) == 0 && wide_enabled()) {
         constexpr int kU = kUnroll / 2;                 // the same bytes in flight
         if (!evict_first_enabled()) return launch_wide<NT, kU, false>(mode, out_dtype, xp, wp, out, M, N, K, stream);
-        if (NT == 1 && prefetch_enabled()) return launch_prefetch<kU>(mode, out_dtype, xp, wp, out, M, N, K, stream);
+        if (NT == 1 && prefetch_enabled()) return launch_prefetch<1, kU>(mode, out_dtype, xp, wp, out, M, N, K, stream);
         return launch_wide<NT, kU, true>(mode, out_dtype, xp, wp, out, M, N, K, stream);
     }
     if (mode == kSwiGLU) {
@@ -587,8 +594,10 @@ PB_EXPORT int pb_gemm_skinny_scaled(int mode, const void* y, const void* w, void
     const int tiles = (mode == kSwiGLU) ? N / 2 / 8 : N / kRows;
     const int inter = mode == kSwiGLU ? N / 2 : 0;
     const bool many = tiles > 2 * sm_count();
+    const int parts_bytes = (n_parts * M * 4 + 15) / 16 * 16;
 #define PB_SCALED(NT, MODE, KU, PRE) \
-    return launch_pdl(gemm_skinny_scaled_kernel<NT, MODE, KU, PRE>, tiles, kWarps * 32, 0, stream, yp, wp, (bf16*)out, M, N, K, inter, fuse)
+    return launch_pdl(gemm_skinny_scaled_kernel<NT, MODE, KU, PRE>, tiles, kWarps * 32, (PRE) > 0 ? 0 : parts_bytes, stream, yp, wp, \
+                      (bf16*)out, M, N, K, inter, fuse)
     if (M <= 8) {
         if (mode == kSwiGLU) { if (many) PB_SCALED(1, kSwiGLU, 2, 2); PB_SCALED(1, kSwiGLU, 4, 2); }
         if (many) PB_SCALED(1, kPlain, 2, 2);
