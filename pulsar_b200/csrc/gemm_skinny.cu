@@ -190,18 +190,17 @@ __device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
 // projections themselves (a decode step then has no norm kernel between its products):
 //   kAcc     float32 output that is ADDED to what ``out`` holds (the residual stream; the projection's result never
 //            exists in bfloat16).  With ``fuse.next_w`` the block also prepares the norm that follows for its 16
-//            columns: y = bfloat16(x_new * next_w) and the block's part of sum_k x_new[token, k]^2.
-//   kScaled  the tokens come as such a prepared y; the sums of token m are scaled by rsqrt(sum / K + eps), the sum
-//            being the prepared parts added in block order (float32, fixed order: the same bits every time).
+//            columns: y = bfloat16(x_new * next_w) and the block's part of sum_k x_new[token, k]^2; the block
+//            that finishes last adds the parts (float32, fixed order: the same bits every time).
+//   kScaled  the tokens come as such a prepared y; the sums of token m are scaled by rsqrt(sum / K + eps).
 // rmsnorm(x) W^T = rsqrt(mean(x^2) + eps) * ((x * norm_w) W^T): the per-token factor commutes with the product.
-constexpr int kMaxParts = 512;      // blocks of the product that prepared a norm: widths up to 8192
 
 struct SkinnyFuse {
     const float* next_w;      // kAcc: weight of the norm that follows, or null
     bf16* y;                  // kAcc: [M, N] prepared operand
-    float* part_out;          // kAcc: [gridDim.x, M] parts of the sums of squares
-    const float* part_in;     // kScaled: [n_parts, M]
-    int n_parts;
+    float* part_out;          // kAcc: [gridDim.x, M] parts of the sums of squares, then [M] their sums
+    unsigned int* ticket;     // kAcc: zero before the launch and after it
+    const float* sums;        // kScaled: [M] sums of squares
     float eps;
 };
 
@@ -213,11 +212,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
     constexpr int kPreRow = kPre * 128 + 16;          // bytes of a row's prefetched part in shared memory
     __shared__ float red[kWarps][kRows][8 * NT + 1];
     __shared__ float scale_s[kScaled ? 8 * NT : 1];                 // kScaled: rsqrt(mean(x^2) + eps) per token
-    // kScaled: a copy of fuse.part_in.  Where part of the weights is prefetched through shared memory, the copy
-    // takes that buffer's place once a warp has read its part of it (1,024 floats in each warp's region).
-    // Without a prefetch buffer the copy lies in dynamic shared memory of n_parts * M floats: no more than this
-    // product needs, since what shared memory takes the L1 cache loses, which holds the tokens for all blocks of an SM.
-    extern __shared__ __align__(16) float parts_s[];
+    __shared__ int last_s;                                          // kAcc: this block drew the last ticket
     __shared__ float square_s[kAcc ? 8 * NT : 1][kAcc ? kRows : 1]; // kAcc: x_new^2 of the block's columns
     __shared__ __align__(16) unsigned char pre[kPre > 0 ? kWarps : 1][kPre > 0 ? kRows : 1][kPre > 0 ? kPreRow : 16];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -272,7 +267,10 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
     pdl_wait();
     // What the epilogue needs from the kernel before this one is asked for now and used at the end, so that no warp
     // waits for it: the parts of the sums of squares (copied to shared memory), the residual's old value.
-    float old_value = 0.0f, next_weight = 0.0f;
+    float old_value = 0.0f, next_weight = 0.0f, square_sum = 0.0f;
+    if constexpr (kScaled) {
+        if (tid < M) square_sum = __ldcg(fuse.sums + tid);
+    }
     if constexpr (kAcc) {
         if (tid < kRows * M) {
             const int col = blockIdx.x * kRows + tid % kRows;
@@ -323,20 +321,6 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
         }
         kb += kPre;
     }
-    auto part_slot = [&](int f) -> float* {
-        if constexpr (kPre > 0) return reinterpret_cast<float*>(&pre[f >> 10][0][0]) + (f & 1023);
-        else return parts_s + f;
-    };
-    if constexpr (kScaled) {
-        // asked for now, used at the very end: no warp waits for it.  Each warp copies 1,024 floats at most, into its
-        // own region (which it has finished reading).
-        static_assert(kPre == 0 || kRows * kPreRow >= 4096, "a warp's region holds 1,024 floats");
-        __syncwarp();
-        const int chunks = fuse.n_parts * M / 4;                    // 16-byte chunks (n_parts is a multiple of 4)
-        const int end = min(chunks, (warp + 1) * 256);
-        for (int i = warp * 256 + lane; i < end; i += 32) cp_async16(smem_u32(part_slot(4 * i)), fuse.part_in + 4 * i, true);
-        cp_async_commit();
-    }
     // (Asking for a register pair again as soon as its k-block is multiplied, so that the next batch is on its way
     // while this one is used, was slower: 5.05 against 4.83 ms per step of 16 sequences, 3.72 against 3.66 of 8.)
     for (; kb + kUnroll <= kb_end; kb += kUnroll, loaded = false) {
@@ -363,15 +347,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
         red[warp][g + 8][n * 8 + 2 * t + 1] = c[n][3];
     }
     if constexpr (kScaled) {
-        cp_async_wait<0>();
-        __syncthreads();
-        for (int token = warp; token < M; token += kWarps) {        // the parts in block order, then a fixed tree
-            float sum = 0.0f;
-            for (int b = lane; b < fuse.n_parts; b += 32) sum += *part_slot(b * M + token);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            if (lane == 0) scale_s[token] = rsqrtf(sum / (float)K + fuse.eps);
-        }
+        if (tid < M) scale_s[tid] = rsqrtf(square_sum / (float)K + fuse.eps);
     }
     __syncthreads();
     if (MODE == kSwiGLU) {
@@ -411,7 +387,27 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
                     float sum = 0.0f;
 #pragma unroll
                     for (int rr = 0; rr < kRows; ++rr) sum += square_s[tid][rr];
-                    fuse.part_out[(size_t)blockIdx.x * M + tid] = sum;
+                    __stcg(fuse.part_out + (size_t)blockIdx.x * M + tid, sum);
+                }
+                // The block that draws the last ticket adds the parts of all blocks (in block order within a lane,
+                // then a fixed tree: the same bits every time) and leaves each token's sum behind the parts, so
+                // that the product that applies the norm reads M numbers and not M per block of this one.
+                __syncthreads();
+                if (tid == 0) {
+                    __threadfence();
+                    last_s = atomicAdd(fuse.ticket, 1u) == gridDim.x - 1 ? 1 : 0;
+                }
+                __syncthreads();
+                if (last_s) {
+                    __threadfence();
+                    for (int token = warp; token < M; token += kWarps) {
+                        float sum = 0.0f;
+                        for (int b = lane; b < (int)gridDim.x; b += 32) sum += __ldcg(fuse.part_out + (size_t)b * M + token);
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                        if (lane == 0) fuse.part_out[(size_t)gridDim.x * M + token] = sum;
+                    }
+                    if (tid == 0) *fuse.ticket = 0;
                 }
             }
         }
@@ -554,19 +550,21 @@ PB_EXPORT int pb_gemm_skinny_fused_supported(int mode, int M, int N, int K) {
 }
 
 // residual[M, N] (float32) += x[M, K] W[N, K]^T.  With next_w (float32 [N], the weight of the RMSNorm that follows) also
-// y[M, N] = bfloat16(residual * next_w) and parts[N / 16, M] = each block's part of sum_n residual[m, n]^2, for
+// y[M, N] = bfloat16(residual * next_w), parts[N / 16, M] = each block's part of sum_n residual[m, n]^2 and, behind
+// them, parts[N / 16][m] = the sum of token m's parts; ticket: one word, zero (the kernel leaves it zero); for
 // pb_gemm_skinny_scaled.
 PB_EXPORT int pb_gemm_skinny_accumulate(const void* x, const void* w, float* residual, int M, int N, int K, const float* next_w,
-                                        void* y, float* parts, cudaStream_t stream) {
+                                        void* y, float* parts, unsigned int* ticket, cudaStream_t stream) {
     if (!pb_gemm_skinny_fused_supported(kPlain, M, N, K)) return PB_ERR_BAD_SIZE;
     if ((((uintptr_t)x | (uintptr_t)w) & 31) != 0) return PB_ERR_BAD_SIZE;
-    if (next_w != nullptr && (y == nullptr || parts == nullptr)) return PB_ERR_BAD_SIZE;
+    if (next_w != nullptr && (y == nullptr || parts == nullptr || ticket == nullptr)) return PB_ERR_BAD_SIZE;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)w;
     SkinnyFuse fuse{};
     fuse.next_w = next_w;
     fuse.y = (bf16*)y;
     fuse.part_out = parts;
+    fuse.ticket = ticket;
     const int tiles = N / kRows;
     const bool many = tiles > 2 * sm_count();
 #define PB_ACC(NT, KU, PRE) \
@@ -577,27 +575,23 @@ PB_EXPORT int pb_gemm_skinny_accumulate(const void* x, const void* w, float* res
 #undef PB_ACC
 }
 
-// out = (y W^T) * rsqrt(sum_m / K + eps) per token m, sum_m = the n_parts parts of parts[n_parts, M] added in order:
-// with y and parts from pb_gemm_skinny_accumulate this is rmsnorm(residual) W^T.  mode 0: bfloat16 [M, N]; mode 1: the
+// out = (y W^T) * rsqrt(sums[m] / K + eps) per token m: with y and the sums from pb_gemm_skinny_accumulate (which
+// leaves them behind its parts, at parts + (N / 16) * M) this is rmsnorm(residual) W^T.  mode 0: bfloat16 [M, N]; mode 1: the
 // SwiGLU form, bfloat16 [M, N / 2].
-PB_EXPORT int pb_gemm_skinny_scaled(int mode, const void* y, const void* w, void* out, int M, int N, int K, const float* parts,
-                                    int n_parts, float eps, cudaStream_t stream) {
-    if (!pb_gemm_skinny_fused_supported(mode, M, N, K) || parts == nullptr || n_parts <= 0) return PB_ERR_BAD_SIZE;
-    if (n_parts > kMaxParts || n_parts % 4 || (((uintptr_t)parts) & 15)) return PB_ERR_BAD_SIZE;
+PB_EXPORT int pb_gemm_skinny_scaled(int mode, const void* y, const void* w, void* out, int M, int N, int K, const float* sums,
+                                    float eps, cudaStream_t stream) {
+    if (!pb_gemm_skinny_fused_supported(mode, M, N, K) || sums == nullptr) return PB_ERR_BAD_SIZE;
     if ((((uintptr_t)y | (uintptr_t)w) & 31) != 0) return PB_ERR_BAD_SIZE;
     const bf16* yp = (const bf16*)y;
     const bf16* wp = (const bf16*)w;
     SkinnyFuse fuse{};
-    fuse.part_in = parts;
-    fuse.n_parts = n_parts;
+    fuse.sums = sums;
     fuse.eps = eps;
     const int tiles = (mode == kSwiGLU) ? N / 2 / 8 : N / kRows;
     const int inter = mode == kSwiGLU ? N / 2 : 0;
     const bool many = tiles > 2 * sm_count();
-    const int parts_bytes = (n_parts * M * 4 + 15) / 16 * 16;
 #define PB_SCALED(NT, MODE, KU, PRE) \
-    return launch_pdl(gemm_skinny_scaled_kernel<NT, MODE, KU, PRE>, tiles, kWarps * 32, (PRE) > 0 ? 0 : parts_bytes, stream, yp, wp, \
-                      (bf16*)out, M, N, K, inter, fuse)
+    return launch_pdl(gemm_skinny_scaled_kernel<NT, MODE, KU, PRE>, tiles, kWarps * 32, 0, stream, yp, wp, (bf16*)out, M, N, K, inter, fuse)
     if (M <= 8) {
         if (mode == kSwiGLU) { if (many) PB_SCALED(1, kSwiGLU, 2, 2); PB_SCALED(1, kSwiGLU, 4, 2); }
         if (many) PB_SCALED(1, kPlain, 2, 2);

@@ -223,12 +223,20 @@ def test_gemm_skinny_adds_into_the_residual_and_prepares_the_norm_that_follows(m
     nw = 1.0 + 0.1 * torch.randn(n, generator=g)
     eps = 3e-6
     prepared = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
-    parts = torch.full(((n // 16) * m,), float("nan"), dtype=torch.float32, device="cuda")
+    parts = torch.full(((n // 16 + 1) * m,), float("nan"), dtype=torch.float32, device="cuda")
     assert ops.linear_accumulate(dev(a), dev(w), res_dev, dev(nw), prepared, parts)
     x = res.double() + 2 * delta
     close(res_dev, x, 2e-5, "accumulate twice")
     close(prepared, x * nw.double(), 1e-2, "prepared operand")
-    close(parts.view(n // 16, m).sum(0), (x ** 2).sum(-1), 2e-5, "sums of squares")
+    close(parts.view(n // 16 + 1, m)[:-1].sum(0), (x ** 2).sum(-1), 2e-5, "parts of the sums of squares")
+    close(parts.view(n // 16 + 1, m)[-1], (x ** 2).sum(-1), 2e-5, "sums of squares")
+    # the ticket by which the last block is found is zero again; a second launch (adding nothing) finds its last
+    # block too and leaves the same sums, bit for bit
+    assert int(ops._norm_ticket(res_dev.device)) == 0
+    first = parts.clone()
+    parts.fill_(float("nan"))
+    assert ops.linear_accumulate(torch.zeros_like(dev(a)), dev(w), res_dev, dev(nw), prepared, parts)
+    assert torch.equal(parts, first) and int(ops._norm_ticket(res_dev.device)) == 0
     # the product behind the norm: rows of W2 [n2, n]
     n2 = 256
     w2 = (torch.randn(n2, n, generator=g) / n ** 0.5).bfloat16()
