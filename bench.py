@@ -10,12 +10,23 @@ configuration (36 layers, hidden 4096, 32/8 heads of 128, intermediate 12288, vo
 timed steps are the last K steps before the context reaches 4,096.  It prints one JSON
 line:
 
-  value      decoded tokens a second, device-timed over exactly K steps of the step function
-  e2e        the same through the Python entry point (Engine.step: host token ids in, host
-             token ids out, index arrays copied from pinned memory every step)
-  prefill    one step of 2,048 prompt tokens: tokens a second, ms, fraction of the bf16 peak
-  roofline   bytes a decode step must read (weights once + the live cache) / its time
-  points     decode tokens a second at batch 1 and 64
+  value        decoded tokens a second, device-timed over exactly K steps of the step function
+               (ms_per_step their mean, ms_per_step_median the median of the steps timed one by one)
+  e2e          the same through the Python entry point (Engine.step: host token ids in, host
+               token ids out, index arrays copied from pinned memory every step)
+  prefill      one step of 2,048 prompt tokens: tokens a second, ms, fraction of the bf16 peak
+  prefill_own  the same with every product on this library's tcgen05 kernel
+  roofline     bytes a decode step must read (weights once + the live cache) / its time
+  points       decode tokens a second at batch 1, 16, 32 and 64 (with their fraction of the copy
+               bandwidth) and at batch 8 with contexts 2,048 and 3,072
+  index_bytes  host-to-device bytes of a decode step of 64 sequences, with the block tables
+               resident on the device and with whole tables sent
+  clocks       SM clock (median, maximum) and throttle reasons sampled through NVML every 5 ms
+               during the timed steps
+
+--impl reference runs the unmodified reference (built by baseline/build_reference.py into
+baseline/_ref) through its own engine class on the same sizes, and prints the same line with
+"impl": "reference", or an "unavailable" line when it is not built.
 
 The cache of the decode measurements is filled with random keys and values instead of
 being computed by a prompt pass (the decode step does the same work either way); the
