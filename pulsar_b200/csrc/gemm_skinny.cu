@@ -190,17 +190,38 @@ __device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
 // projections themselves (a decode step then has no norm kernel between its products):
 //   kAcc     float32 output that is ADDED to what ``out`` holds (the residual stream; the projection's result never
 //            exists in bfloat16).  With ``fuse.next_w`` the block also prepares the norm that follows for its 16
-//            columns: y = bfloat16(x_new * next_w) and the block's part of sum_k x_new[token, k]^2; the block
-//            that finishes last adds the parts (float32, fixed order: the same bits every time).
-//   kScaled  the tokens come as such a prepared y; the sums of token m are scaled by rsqrt(sum / K + eps).
+//            columns: y = bfloat16(x_new * next_w) and the block's part of sum_k x_new[token, k]^2.
+//   kScaled  the tokens come as such a prepared y; the sums of token m are scaled by rsqrt(sum / K + eps), the sum
+//            being the parts added in block order within a lane, then a fixed tree (float32: the same bits every
+//            time).  Block 0 adds them when the kernel starts and leaves the sums behind the parts with a word
+//            that says so; the other blocks, which need them only at their end, read that word then and take the
+//            sums, or, if block 0 should not have come that far, add the parts themselves in the same order.  No
+//            block waits for another.
 // rmsnorm(x) W^T = rsqrt(mean(x^2) + eps) * ((x * norm_w) W^T): the per-token factor commutes with the product.
+
+// rsqrt(mean(x^2) + eps) of every token into scale_s from the parts of its sum of squares; the sums themselves to
+// sums_out where that is not null.  All warps of the block.
+__device__ __forceinline__ void add_parts(const float* parts, int n_parts, int M, int K, float eps, int warp, int lane,
+                                          float* scale_s, float* sums_out) {
+    for (int token = warp; token < M; token += kWarps) {
+        float sum = 0.0f;
+        for (int b = lane; b < n_parts; b += 32) sum += __ldcg(parts + (size_t)b * M + token);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) {
+            scale_s[token] = rsqrtf(sum / (float)K + eps);
+            if (sums_out != nullptr) __stcg(sums_out + token, sum);
+        }
+    }
+}
 
 struct SkinnyFuse {
     const float* next_w;      // kAcc: weight of the norm that follows, or null
     bf16* y;                  // kAcc: [M, N] prepared operand
-    float* part_out;          // kAcc: [gridDim.x, M] parts of the sums of squares, then [M] their sums
-    unsigned int* ticket;     // kAcc: zero before the launch and after it
-    const float* sums;        // kScaled: [M] sums of squares
+    float* parts;             // [n_parts, M] each producing block's part of the sums of squares, then [M] their sums,
+                              // then one word that says whether the sums are there
+    int n_parts;              // blocks of the producing product
+    int publish;              // kScaled: block 0 leaves the sums for the others (0: every block adds the parts itself)
     float eps;
 };
 
@@ -212,7 +233,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
     constexpr int kPreRow = kPre * 128 + 16;          // bytes of a row's prefetched part in shared memory
     __shared__ float red[kWarps][kRows][8 * NT + 1];
     __shared__ float scale_s[kScaled ? 8 * NT : 1];                 // kScaled: rsqrt(mean(x^2) + eps) per token
-    __shared__ int last_s;                                          // kAcc: this block drew the last ticket
+    __shared__ int ready_s;                                         // kScaled: the sums are there
     __shared__ float square_s[kAcc ? 8 * NT : 1][kAcc ? kRows : 1]; // kAcc: x_new^2 of the block's columns
     __shared__ __align__(16) unsigned char pre[kPre > 0 ? kWarps : 1][kPre > 0 ? kRows : 1][kPre > 0 ? kPreRow : 16];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -267,11 +288,22 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
     pdl_wait();
     // What the epilogue needs from the kernel before this one is asked for now and used at the end, so that no warp
     // waits for it: the parts of the sums of squares (copied to shared memory), the residual's old value.
-    float old_value = 0.0f, next_weight = 0.0f, square_sum = 0.0f;
+    float old_value = 0.0f, next_weight = 0.0f;
     if constexpr (kScaled) {
-        if (tid < M) square_sum = __ldcg(fuse.sums + tid);
+        if (blockIdx.x == 0) {
+            float* sums = fuse.parts + (size_t)fuse.n_parts * M;
+            add_parts(fuse.parts, fuse.n_parts, M, K, fuse.eps, warp, lane, scale_s, sums);
+            __syncthreads();
+            if (tid == 0 && fuse.publish) {
+                __threadfence();
+                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sums + M), "r"(1u) : "memory");
+            }
+        }
     }
     if constexpr (kAcc) {
+        // the word that says "the sums are there" is taken back before the product behind the norm can look at it
+        if (fuse.next_w != nullptr && blockIdx.x == 0 && tid == 0)
+            __stcg(reinterpret_cast<unsigned int*>(fuse.parts + (size_t)(gridDim.x + 1) * M), 0u);
         if (tid < kRows * M) {
             const int col = blockIdx.x * kRows + tid % kRows;
             old_value = to_float(out[(size_t)(tid / kRows) * N + col]);
@@ -347,7 +379,20 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
         red[warp][g + 8][n * 8 + 2 * t + 1] = c[n][3];
     }
     if constexpr (kScaled) {
-        if (tid < M) scale_s[tid] = rsqrtf(square_sum / (float)K + fuse.eps);
+        if (blockIdx.x != 0) {
+            const float* sums = fuse.parts + (size_t)fuse.n_parts * M;
+            if (tid == 0) {
+                unsigned int ready;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(ready) : "l"(sums + M) : "memory");
+                ready_s = (int)ready;
+            }
+            __syncthreads();
+            if (ready_s) {
+                if (tid < M) scale_s[tid] = rsqrtf(__ldcg(sums + tid) / (float)K + fuse.eps);
+            } else {
+                add_parts(fuse.parts, fuse.n_parts, M, K, fuse.eps, warp, lane, scale_s, nullptr);
+            }
+        }
     }
     __syncthreads();
     if (MODE == kSwiGLU) {
@@ -387,27 +432,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
                     float sum = 0.0f;
 #pragma unroll
                     for (int rr = 0; rr < kRows; ++rr) sum += square_s[tid][rr];
-                    __stcg(fuse.part_out + (size_t)blockIdx.x * M + tid, sum);
-                }
-                // The block that draws the last ticket adds the parts of all blocks (in block order within a lane,
-                // then a fixed tree: the same bits every time) and leaves each token's sum behind the parts, so
-                // that the product that applies the norm reads M numbers and not M per block of this one.
-                __syncthreads();
-                if (tid == 0) {
-                    __threadfence();
-                    last_s = atomicAdd(fuse.ticket, 1u) == gridDim.x - 1 ? 1 : 0;
-                }
-                __syncthreads();
-                if (last_s) {
-                    __threadfence();
-                    for (int token = warp; token < M; token += kWarps) {
-                        float sum = 0.0f;
-                        for (int b = lane; b < (int)gridDim.x; b += 32) sum += __ldcg(fuse.part_out + (size_t)b * M + token);
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                        if (lane == 0) fuse.part_out[(size_t)gridDim.x * M + token] = sum;
-                    }
-                    if (tid == 0) *fuse.ticket = 0;
+                    __stcg(fuse.parts + (size_t)blockIdx.x * M + tid, sum);
                 }
             }
         }
@@ -518,6 +543,8 @@ int launch_u(int mode, int out_dtype, const void* x, const void* w, void* out, i
     return launch_pdl(gemm_skinny_kernel<NT, kPlain, float, kUnroll>, N / kRows, kWarps * 32, 0, stream, xp, wp, (float*)out, M, N, K, 0);
 }
 
+int g_publish_sums = 1;
+
 int sm_count() {
     static int n = [] {
         int dev = 0, v = 0;
@@ -550,21 +577,22 @@ PB_EXPORT int pb_gemm_skinny_fused_supported(int mode, int M, int N, int K) {
 }
 
 // residual[M, N] (float32) += x[M, K] W[N, K]^T.  With next_w (float32 [N], the weight of the RMSNorm that follows) also
-// y[M, N] = bfloat16(residual * next_w), parts[N / 16, M] = each block's part of sum_n residual[m, n]^2 and, behind
-// them, parts[N / 16][m] = the sum of token m's parts; ticket: one word, zero (the kernel leaves it zero); for
+// y[M, N] = bfloat16(residual * next_w) and parts[N / 16, M] = each block's part of sum_n residual[m, n]^2; parts has
+// room for (N / 16 + 1) * M + 1 floats: behind the parts pb_gemm_skinny_scaled keeps the sums and a word, which this
+// kernel sets to zero; for
 // pb_gemm_skinny_scaled.
 PB_EXPORT int pb_gemm_skinny_accumulate(const void* x, const void* w, float* residual, int M, int N, int K, const float* next_w,
-                                        void* y, float* parts, unsigned int* ticket, cudaStream_t stream) {
+                                        void* y, float* parts, cudaStream_t stream) {
     if (!pb_gemm_skinny_fused_supported(kPlain, M, N, K)) return PB_ERR_BAD_SIZE;
     if ((((uintptr_t)x | (uintptr_t)w) & 31) != 0) return PB_ERR_BAD_SIZE;
-    if (next_w != nullptr && (y == nullptr || parts == nullptr || ticket == nullptr)) return PB_ERR_BAD_SIZE;
+    if (next_w != nullptr && (y == nullptr || parts == nullptr)) return PB_ERR_BAD_SIZE;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)w;
     SkinnyFuse fuse{};
     fuse.next_w = next_w;
     fuse.y = (bf16*)y;
-    fuse.part_out = parts;
-    fuse.ticket = ticket;
+    fuse.parts = parts;
+    fuse.n_parts = N / kRows;
     const int tiles = N / kRows;
     const bool many = tiles > 2 * sm_count();
 #define PB_ACC(NT, KU, PRE) \
@@ -575,17 +603,27 @@ PB_EXPORT int pb_gemm_skinny_accumulate(const void* x, const void* w, float* res
 #undef PB_ACC
 }
 
-// out = (y W^T) * rsqrt(sums[m] / K + eps) per token m: with y and the sums from pb_gemm_skinny_accumulate (which
-// leaves them behind its parts, at parts + (N / 16) * M) this is rmsnorm(residual) W^T.  mode 0: bfloat16 [M, N]; mode 1: the
+// on = 0: block 0 of pb_gemm_skinny_scaled keeps its sums to itself, so that every other block takes the path on
+// which it adds the parts itself (which otherwise only runs when block 0 is late).  For tests of that path.
+PB_EXPORT int pb_gemm_skinny_publish_sums(int on) {
+    g_publish_sums = on ? 1 : 0;
+    return 0;
+}
+
+// out = (y W^T) * rsqrt(sum_m / K + eps) per token m, sum_m = the K / 16 parts of parts[K / 16, M] added in order:
+// with y and parts from pb_gemm_skinny_accumulate this is rmsnorm(residual) W^T.  parts: (K / 16 + 1) * M + 1 floats,
+// the sums and one word behind the parts are written here.  mode 0: bfloat16 [M, N]; mode 1: the
 // SwiGLU form, bfloat16 [M, N / 2].
-PB_EXPORT int pb_gemm_skinny_scaled(int mode, const void* y, const void* w, void* out, int M, int N, int K, const float* sums,
+PB_EXPORT int pb_gemm_skinny_scaled(int mode, const void* y, const void* w, void* out, int M, int N, int K, float* parts,
                                     float eps, cudaStream_t stream) {
-    if (!pb_gemm_skinny_fused_supported(mode, M, N, K) || sums == nullptr) return PB_ERR_BAD_SIZE;
+    if (!pb_gemm_skinny_fused_supported(mode, M, N, K) || parts == nullptr) return PB_ERR_BAD_SIZE;
     if ((((uintptr_t)y | (uintptr_t)w) & 31) != 0) return PB_ERR_BAD_SIZE;
     const bf16* yp = (const bf16*)y;
     const bf16* wp = (const bf16*)w;
     SkinnyFuse fuse{};
-    fuse.sums = sums;
+    fuse.parts = parts;
+    fuse.n_parts = K / kRows;
+    fuse.publish = g_publish_sums;
     fuse.eps = eps;
     const int tiles = (mode == kSwiGLU) ? N / 2 / 8 : N / kRows;
     const int inter = mode == kSwiGLU ? N / 2 : 0;

@@ -62,7 +62,8 @@ _SIGNATURES = {
     "pb_gemm_skinny": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_gemm_skinny_supported": [_I, _I, _I, _I],
     "pb_gemm_skinny_fused_supported": [_I, _I, _I, _I],
-    "pb_gemm_skinny_accumulate": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P],
+    "pb_gemm_skinny_publish_sums": [_I],
+    "pb_gemm_skinny_accumulate": [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
     "pb_gemm_skinny_scaled": [_I, _P, _P, _P, _I, _I, _I, _P, _F, _P],
     "pb_gemm_tcgen05": [_I, _I, _P, _P, _P, _I, _I, _I, _P],
     "pb_gemm_tcgen05_supported": [_I, _I, _I, _I],
@@ -328,16 +329,10 @@ def fused_projection_supported(m: int, w: torch.Tensor, swiglu: bool = False) ->
                 and fn("pb_gemm_skinny_fused_supported")(1 if swiglu else 0, m, w.shape[0], w.shape[1]))
 
 
-_norm_tickets = {}
-
-
-def _norm_ticket(device: torch.device) -> torch.Tensor:
-    """The word by which the blocks of ``linear_accumulate`` find out which of them finishes last (zero between
-    kernels; the kernels of one stream share it)."""
-    t = _norm_tickets.get(device)
-    if t is None:
-        t = _norm_tickets[device] = torch.zeros(1, dtype=torch.int32, device=device)
-    return t
+def norm_parts_numel(m: int, width: int) -> int:
+    """Floats of the buffer in which ``linear_accumulate`` leaves the parts of the sums of squares of ``m`` rows
+    ``width`` wide: a part per 16 columns and row, the sums, one word."""
+    return (width // 16 + 1) * m + 1
 
 
 def linear_accumulate(a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, next_norm_weight: Optional[torch.Tensor] = None,
@@ -345,8 +340,8 @@ def linear_accumulate(a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, 
     """residual (float32) += a @ w.T for up to 16 tokens: the projection's result goes into the residual stream
     without a bfloat16 rounding and without a kernel for the addition.  With ``next_norm_weight`` (the weight of
     the RMSNorm that follows) the kernel also prepares that norm: ``prepared`` [M, N] bfloat16 = residual *
-    weight and ``parts`` [N / 16 + 1, M] float32 = each block's part of the rows' sums of squares and, in the last
-    row, their sums (added by the block that finishes last), which ``linear_prenormed`` takes.  Returns False, having done nothing, when the sizes or dtypes are not the kernel's."""
+    weight and ``parts`` (float32, ``norm_parts_numel(M, N)`` elements) = each block's part of the rows' sums of
+    squares [N / 16, M], which ``linear_prenormed`` takes (and behind which it keeps the sums).  Returns False, having done nothing, when the sizes or dtypes are not the kernel's."""
     m, k = a.shape
     n = w.shape[0]
     if (not FUSED_NORM or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or residual.dtype != torch.float32
@@ -358,9 +353,9 @@ def linear_accumulate(a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, 
     if next_norm_weight is not None:
         assert next_norm_weight.dtype == torch.float32 and next_norm_weight.numel() == n
         assert prepared.dtype == torch.bfloat16 and prepared.shape == (m, n)
-        assert parts.dtype == torch.float32 and parts.numel() >= (n // 16 + 1) * m
+        assert parts.dtype == torch.float32 and parts.numel() >= norm_parts_numel(m, n)
     check(fn("pb_gemm_skinny_accumulate")(_p(a), _p(w), _p(residual), m, n, k, _p(next_norm_weight), _p(prepared), _p(parts),
-                                          _p(_norm_ticket(a.device)), stream()), "gemm_skinny_accumulate")
+                                          stream()), "gemm_skinny_accumulate")
     return True
 
 
@@ -368,7 +363,7 @@ def linear_prenormed(prepared: torch.Tensor, parts: torch.Tensor, eps: float, w:
                      swiglu: bool = False) -> bool:
     """out = rmsnorm(residual) @ w.T (or its SwiGLU form) from what ``linear_accumulate`` prepared: the product of
     ``prepared`` (residual * norm weight, bfloat16) with each token's sums scaled by rsqrt(mean(residual^2) + eps),
-    the mean from the last row of ``parts``.  Returns False, having done nothing, when the sizes or dtypes are not the kernel's."""
+    the mean from ``parts``.  Returns False, having done nothing, when the sizes or dtypes are not the kernel's."""
     m, k = prepared.shape
     n = w.shape[0]
     if (not FUSED_NORM or prepared.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16
@@ -378,9 +373,8 @@ def linear_prenormed(prepared: torch.Tensor, parts: torch.Tensor, eps: float, w:
     if not fn("pb_gemm_skinny_fused_supported")(mode, m, n, k) or not _aligned32(prepared, w):
         return False
     _cuda(prepared, parts, w, out)
-    assert out.shape == (m, n // 2 if swiglu else n) and parts.numel() >= (k // 16 + 1) * m
-    sums = parts.view(-1)[(k // 16) * m:]
-    check(fn("pb_gemm_skinny_scaled")(mode, _p(prepared), _p(w), _p(out), m, n, k, _p(sums), float(eps), stream()),
+    assert out.shape == (m, n // 2 if swiglu else n) and parts.numel() >= norm_parts_numel(m, k)
+    check(fn("pb_gemm_skinny_scaled")(mode, _p(prepared), _p(w), _p(out), m, n, k, _p(parts), float(eps), stream()),
           "gemm_skinny_scaled")
     return True
 

@@ -45,7 +45,7 @@ def accumulate_and_prepare(ctx: StepContext, a: torch.Tensor, w: torch.Tensor, r
     if isinstance(next_norm, RMSNorm) and next_norm.spec.size == width and width % 16 == 0:
         tag = next_norm.tag
         prepared = ctx.scratch(tag + ".prepared", (n, width), torch.bfloat16)
-        parts = ctx.scratch(tag + ".parts", ((width // 16 + 1) * n,), torch.float32)
+        parts = ctx.scratch(tag + ".parts", (ops.norm_parts_numel(n, width),), torch.float32)
         if ops.linear_accumulate(a, w, residual, next_norm.weight, prepared, parts):
             ctx.prepared_norms[id(next_norm)] = (prepared, parts)
             return True

@@ -223,20 +223,14 @@ def test_gemm_skinny_adds_into_the_residual_and_prepares_the_norm_that_follows(m
     nw = 1.0 + 0.1 * torch.randn(n, generator=g)
     eps = 3e-6
     prepared = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
-    parts = torch.full(((n // 16 + 1) * m,), float("nan"), dtype=torch.float32, device="cuda")
+    parts = torch.full((ops.norm_parts_numel(m, n),), float("nan"), dtype=torch.float32, device="cuda")
     assert ops.linear_accumulate(dev(a), dev(w), res_dev, dev(nw), prepared, parts)
     x = res.double() + 2 * delta
     close(res_dev, x, 2e-5, "accumulate twice")
     close(prepared, x * nw.double(), 1e-2, "prepared operand")
-    close(parts.view(n // 16 + 1, m)[:-1].sum(0), (x ** 2).sum(-1), 2e-5, "parts of the sums of squares")
-    close(parts.view(n // 16 + 1, m)[-1], (x ** 2).sum(-1), 2e-5, "sums of squares")
-    # the ticket by which the last block is found is zero again; a second launch (adding nothing) finds its last
-    # block too and leaves the same sums, bit for bit
-    assert int(ops._norm_ticket(res_dev.device)) == 0
-    first = parts.clone()
-    parts.fill_(float("nan"))
-    assert ops.linear_accumulate(torch.zeros_like(dev(a)), dev(w), res_dev, dev(nw), prepared, parts)
-    assert torch.equal(parts, first) and int(ops._norm_ticket(res_dev.device)) == 0
+    close(parts[:(n // 16) * m].view(n // 16, m).sum(0), (x ** 2).sum(-1), 2e-5, "parts of the sums of squares")
+    word = parts[(n // 16 + 1) * m:].view(torch.int32)
+    assert int(word) == 0                                   # "the sums are not there yet"
     # the product behind the norm: rows of W2 [n2, n]
     n2 = 256
     w2 = (torch.randn(n2, n, generator=g) / n ** 0.5).bfloat16()
@@ -245,8 +239,20 @@ def test_gemm_skinny_adds_into_the_residual_and_prepares_the_norm_that_follows(m
     if n % 64 == 0:
         assert ops.linear_prenormed(prepared, parts, eps, dev(w2), out)
         close(out, exact, 1.6e-2, "product behind the prepared norm")
+        # its first block has left the sums behind the parts and said so; the producing product takes the word back
+        assert int(word) == 1
+        close(parts[(n // 16) * m:(n // 16 + 1) * m], (x ** 2).sum(-1), 2e-5, "sums of squares")
         if m > 2:
             assert float(out[1].float().abs().max()) == 0.0
+        # the same bits on the path on which every block adds the parts itself (block 0 keeps its sums to itself)
+        word.zero_()
+        ops.fn("pb_gemm_skinny_publish_sums")(0)
+        try:
+            again = torch.full((m, n2), float("nan"), dtype=torch.bfloat16, device="cuda")
+            assert ops.linear_prenormed(prepared, parts, eps, dev(w2), again)
+            assert int(word) == 0 and torch.equal(again, out)
+        finally:
+            ops.fn("pb_gemm_skinny_publish_sums")(1)
         act = torch.full((m, n2 // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
         assert ops.linear_prenormed(prepared, parts, eps, dev(w2), act, swiglu=True)
         gate, up = exact[:, :n2 // 2], exact[:, n2 // 2:]
