@@ -457,6 +457,54 @@ def test_random_arrivals_one_pass_ahead_and_one_pass_at_a_time(folders, seed):
     assert all(ev and ev[-1][1] for ev in a.values())
 
 
+@pytest.mark.parametrize("name,seed", [("A", 1), ("C", 5), ("E", 1), ("F", 1)])
+def test_random_arrivals_second_turns_and_preemption_give_the_plain_tokens(folders, name, seed):
+    """Requests of random lengths and budgets arrive while others run, in a pool so small that some are preempted
+    and recomputed; a stop token ends some early, and some get a second turn of new tokens behind what they
+    generated.  Every turn's tokens are the plain implementation's greedy tokens for that turn's whole prefix
+    (float32), in either stepping mode."""
+    from pulsar_b200.engine.engine import Engine
+    raw, model_seed, page = TINY[name]
+    cfg, weights = helpers.read_folder(folders[name])
+    rng = random.Random(7000 + seed)
+    arrivals = sorted(((rng.randint(0, 20), helpers.random_tokens(rng, rng.randint(1, 40), raw["vocab_size"]), rng.randint(1, 12),
+                        rng.random() < 0.5) for _ in range(7)), key=lambda a: a[0])
+    eos = rng.randrange(raw["vocab_size"])
+    n_preempted = 0
+    for lookahead in (False, True):
+        turn_rng = random.Random(seed)
+        eng = Engine(folders[name], dict(dtype="float32", page_size=page, num_pages=-(-72 // page) + 1, max_sessions=4, max_running=3,
+                                         max_chunk_size=13, eos_id=eos))
+        todo, live, tick = list(arrivals), {}, 0
+        while todo or live:
+            while todo and todo[0][0] <= tick and len(live) < 4:
+                _, prompt, budget, second = todo.pop(0)
+                sid = eng.create_session(prompt)
+                eng.feed(sid, [], budget)
+                live[sid] = dict(seq=list(prompt), got=[], budget=budget, second=second)
+            events = (eng.step(1) if lookahead else eng.step_once()) if eng.has_work() else []
+            for sid, tok, fin in events:
+                r = live[sid]
+                r["got"].append(tok)
+                if not fin:
+                    continue
+                assert r["got"] == plain.greedy_generate(cfg, weights, r["seq"], r["budget"], eos_id=eos), (lookahead, len(r["seq"]))
+                if r["second"]:
+                    extra = helpers.random_tokens(turn_rng, turn_rng.randint(1, 6), raw["vocab_size"])
+                    r["seq"] = r["seq"] + r["got"] + extra
+                    r["got"], r["second"], r["budget"] = [], False, turn_rng.randint(1, 8)
+                    eng.feed(sid, extra, r["budget"])
+                else:
+                    eng.release(sid)
+                    del live[sid]
+            tick += 1
+            assert tick < 5000
+        eng.cache.check_consistency()
+        assert eng.cache.live_requests() == []
+        n_preempted += eng.scheduler.n_preemptions
+    assert n_preempted > 0, "the pool was meant to be too small for all requests at once"
+
+
 def test_engine_refuses_a_cpu_device(folders):
     from pulsar_b200.engine.engine import Engine
     with pytest.raises(RuntimeError, match="no CPU path"):
