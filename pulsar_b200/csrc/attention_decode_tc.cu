@@ -12,6 +12,12 @@
 // O += P V.  The warps' partial results are merged through shared memory and written in
 // the layout of the split kernel (attention_decode.cu), whose combine kernel finishes.
 //
+// The kernel can also take over what otherwise runs as a kernel of its own before it: with a QkvFuse it reads the
+// step's raw q/k/v rows, applies the per-head RMSNorm and the rotation to its group's query heads as it loads them,
+// and the block whose keys include the newest position does the same for that position's key, writes key and value
+// into their page, and only then asks for the tile that holds them.  One launch less in a chain of dependent
+// launches, each of which costs more than a microsecond whatever it does.
+//
 // This kernel exists for memory bandwidth: a decode step reads every cached key and value
 // once, and what limits it is the number of bytes in flight per SM, not arithmetic.
 #include "mma_common.cuh"
@@ -26,12 +32,34 @@ constexpr int kTile = 64;        // keys per pipeline stage
 constexpr int kStages = 3;
 constexpr int kWarps = 4;
 
+// The step's projected rows, still without norm and rotation: [n_seqs][(Hq + 2 Hkv) * D] bfloat16, query heads first,
+// then key heads, then value heads.  The whole head rotates (pairs i, i + D / 2).  qkv null: q is ready and the newest
+// key and value are in their page.
+struct QkvFuse {
+    const bf16* qkv;
+    const float* q_weight;      // [D] or null (no norm)
+    const float* k_weight;
+    const float* cos_t;         // [n_seqs][D / 2]
+    const float* sin_t;
+    const int* slots;           // [n_seqs] slot of the newest position: page * page_size + offset; negative: not cached
+    bf16* k_out;                // the pools, writable
+    bf16* v_out;
+    float eps;
+    int page_size;
+};
+
+__device__ __forceinline__ void unpack_bf16(uint32_t v, float& lo, float& hi) {
+    lo = __uint_as_float(v << 16);
+    hi = __uint_as_float(v & 0xffff0000u);
+}
+
 template <int D>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                  float* __restrict__ partial, const int* __restrict__ block_table, int table_stride,
                  const int* __restrict__ kv_len, int Hq, int Hkv, int page_shift, float scale, int window, int n_splits,
-                 bf16* __restrict__ out, unsigned int* __restrict__ tickets, int evict_first, const PoolBounds bounds) {
+                 bf16* __restrict__ out, unsigned int* __restrict__ tickets, int evict_first, const PoolBounds bounds,
+                 const QkvFuse fuse) {
     constexpr int kTileBytes = kTile * D * 2;
     constexpr int kKSteps = D / 16;                   // k-steps of Q K^T
     constexpr int kNTiles = D / 8;                    // n-tiles of P V
@@ -75,7 +103,8 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
     // Q fragments: rows = query heads of the group (zero beyond G), straight from global memory.
     uint32_t qa[kKSteps][4];
     {
-        const bf16* q0 = q + ((size_t)s * Hq + (size_t)kvh * G) * D;
+        const bf16* q0 = fuse.qkv != nullptr ? fuse.qkv + (size_t)s * (Hq + 2 * Hkv) * D + (size_t)kvh * G * D
+                                             : q + ((size_t)s * Hq + (size_t)kvh * G) * D;
 #pragma unroll
         for (int ks = 0; ks < kKSteps; ++ks) {
             const int c0 = ks * 16 + 2 * t;
@@ -83,6 +112,91 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
             qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + c0) : 0u;
             qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)g * D + c0 + 8) : 0u;
             qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q0 + (size_t)(g + 8) * D + c0 + 8) : 0u;
+        }
+    }
+    if (fuse.qkv != nullptr) {
+        // Rows g (registers 0, 2) and g + 8 (registers 1, 3); the four threads of a row hold it whole.  RMSNorm in
+        // float32, then the rotation of the pairs (c, c + D / 2), which lie kKSteps / 2 k-steps apart in one thread.
+        float inv[2] = {1.0f, 1.0f};
+        if (fuse.q_weight != nullptr) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int ks = 0; ks < kKSteps; ++ks) {
+                    float a0, a1, b0, b1;
+                    unpack_bf16(qa[ks][r], a0, a1);
+                    unpack_bf16(qa[ks][r + 2], b0, b1);
+                    ss += a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1;
+                }
+                ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+                ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+                inv[r] = rsqrtf(ss / (float)D + fuse.eps);
+            }
+        }
+        const float* cos_row = fuse.cos_t + (size_t)s * (D / 2);
+        const float* sin_row = fuse.sin_t + (size_t)s * (D / 2);
+#pragma unroll
+        for (int ks = 0; ks < kKSteps / 2; ++ks) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int c = ks * 16 + 2 * t + 8 * half;
+                const float2 cs = *reinterpret_cast<const float2*>(cos_row + c), sn = *reinterpret_cast<const float2*>(sin_row + c);
+                float2 w_lo = make_float2(1.0f, 1.0f), w_hi = make_float2(1.0f, 1.0f);
+                if (fuse.q_weight != nullptr) {
+                    w_lo = *reinterpret_cast<const float2*>(fuse.q_weight + c);
+                    w_hi = *reinterpret_cast<const float2*>(fuse.q_weight + c + D / 2);
+                }
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int reg = half * 2 + r;
+                    float a0, a1, b0, b1;
+                    unpack_bf16(qa[ks][reg], a0, a1);
+                    unpack_bf16(qa[ks + kKSteps / 2][reg], b0, b1);
+                    if (fuse.q_weight != nullptr) {
+                        a0 *= inv[r] * w_lo.x; a1 *= inv[r] * w_lo.y; b0 *= inv[r] * w_hi.x; b1 *= inv[r] * w_hi.y;
+                    }
+                    qa[ks][reg] = pack_bf16(a0 * cs.x - b0 * sn.x, a1 * cs.y - b1 * sn.y);
+                    qa[ks + kKSteps / 2][reg] = pack_bf16(b0 * cs.x + a0 * sn.x, b1 * cs.y + a1 * sn.y);
+                }
+            }
+        }
+        // The newest key and value: the block whose keys include position p brings them into their page before it
+        // asks for the tile that holds them (what a block wrote before a barrier, its later copies read).
+        if (begin <= p && p < end) {
+            int slot = fuse.slots[s];
+            if (slot >= 0 && !slot_ok(slot, fuse.page_size, bounds)) slot = -1;
+            if (slot >= 0) {
+                constexpr int kHalf = D / 4;                      // 32-bit words in half a head
+                const size_t row = (((size_t)(slot / fuse.page_size) * Hkv + kvh) * fuse.page_size + slot % fuse.page_size) * (D / 2);
+                const uint32_t* src = reinterpret_cast<const uint32_t*>(fuse.qkv + (size_t)s * (Hq + 2 * Hkv) * D);
+                if (warp == 0) {
+                    const uint32_t* k_src = src + (size_t)(Hq + kvh) * (D / 2);
+                    const bool has = lane < kHalf;
+                    float a0, a1, b0, b1;
+                    unpack_bf16(has ? k_src[lane] : 0u, a0, a1);
+                    unpack_bf16(has ? k_src[lane + kHalf] : 0u, b0, b1);
+                    if (fuse.k_weight != nullptr) {
+                        const float k_inv = rsqrtf(warp_sum(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1) / (float)D + fuse.eps);
+                        if (has) {
+                            const float2 wa = reinterpret_cast<const float2*>(fuse.k_weight)[lane];
+                            const float2 wb = reinterpret_cast<const float2*>(fuse.k_weight)[lane + kHalf];
+                            a0 *= k_inv * wa.x; a1 *= k_inv * wa.y; b0 *= k_inv * wb.x; b1 *= k_inv * wb.y;
+                        }
+                    }
+                    if (has) {
+                        const float2 cs = reinterpret_cast<const float2*>(cos_row)[lane], sn = reinterpret_cast<const float2*>(sin_row)[lane];
+                        uint32_t* dst = reinterpret_cast<uint32_t*>(fuse.k_out) + row;
+                        dst[lane] = pack_bf16(a0 * cs.x - b0 * sn.x, a1 * cs.y - b1 * sn.y);
+                        dst[lane + kHalf] = pack_bf16(b0 * cs.x + a0 * sn.x, b1 * cs.y + a1 * sn.y);
+                    }
+                } else if (warp == 1) {
+                    const uint32_t* v_src = src + (size_t)(Hq + Hkv + kvh) * (D / 2);
+                    uint32_t* dst = reinterpret_cast<uint32_t*>(fuse.v_out) + row;
+                    for (int i = lane; i < D / 2; i += 32) dst[i] = v_src[i];
+                }
+            }
+            __syncthreads();
         }
     }
 
@@ -275,7 +389,7 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
 template <int D>
 int launch_tc(const void* q, const void* k_pool, const void* v_pool, float* partial, const int* block_table,
               int table_stride, const int* kv_len, int n_seqs, int Hq, int Hkv, int page_size, float scale, int window,
-              int n_splits, void* out, unsigned int* tickets, cudaStream_t stream) {
+              int n_splits, void* out, unsigned int* tickets, cudaStream_t stream, const QkvFuse fuse = QkvFuse{}) {
     const int page_shift = log2_exact(page_size);
     constexpr int pipeline = kStages * 2 * kTile * D * 2;
     constexpr int merge = (kWarps * 16 * D + 2 * kWarps * 16) * 4;
@@ -290,7 +404,7 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, float* part
     dim3 grid(n_splits, Hkv, n_seqs);
     return launch_pdl(decode_tc_kernel<D>, grid, kWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
                       partial, block_table, table_stride, kv_len, Hq, Hkv, page_shift, scale, window, n_splits, (bf16*)out, tickets, evict_first,
-                      pool_bounds_now());
+                      pool_bounds_now(), fuse);
 }
 
 }  // namespace
@@ -338,4 +452,43 @@ PB_EXPORT int pb_paged_attention_decode_tc_fused(int dtype, const void* q, const
                              window, n_splits, out, tickets, stream);
     return launch_tc<128>(q, k_pool, v_pool, partial, block_table, table_stride, kv_len, n_seqs, Hq, Hkv, page_size, scale,
                           window, n_splits, out, tickets, stream);
+}
+
+// The same attention for a step of single tokens whose rows come straight from the q/k/v product: qkv [n_seqs]
+// [(Hq + 2 Hkv) * D] bfloat16 (query, key, value heads in this order).  The kernel applies the per-head RMSNorm
+// (q_weight, k_weight float32 [D], or null for none; eps) and the rotation of the whole head (cos_t, sin_t float32
+// [n_seqs][D / 2]) to the queries and to the newest key, and writes that key and the value to slots[s] of their
+// pools before it reads them: what pb_qk_norm_rope_write does in a launch of its own.  tickets null: the splits are
+// merged by pb_decode_combine; else as pb_paged_attention_decode_tc_fused.
+PB_EXPORT int pb_paged_attention_decode_tc_qkv(int dtype, const void* qkv, const float* q_weight, const float* k_weight,
+                                               const float* cos_t, const float* sin_t, float eps, const int* slots,
+                                               void* k_pool, void* v_pool, void* out, float* partial, unsigned int* tickets,
+                                               const int* block_table, int table_stride, const int* kv_len, int n_seqs, int Hq,
+                                               int Hkv, int D, int page_size, float scale, int window, int n_splits,
+                                               cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (!pb_decode_tc_supported(dtype, Hq, Hkv, D, page_size) || n_splits <= 0) return PB_ERR_BAD_SIZE;
+    if (qkv == nullptr || cos_t == nullptr || sin_t == nullptr || slots == nullptr) return PB_ERR_BAD_SIZE;
+    if ((((uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)q_weight | (uintptr_t)k_weight) & 7) != 0) return PB_ERR_BAD_SIZE;
+    if (Hkv > 65535 || n_seqs > 65535 || (tickets != nullptr && n_splits > 64)) return PB_ERR_TOO_LARGE;
+    QkvFuse fuse{};
+    fuse.qkv = (const bf16*)qkv;
+    fuse.q_weight = q_weight;
+    fuse.k_weight = k_weight;
+    fuse.cos_t = cos_t;
+    fuse.sin_t = sin_t;
+    fuse.slots = slots;
+    fuse.k_out = (bf16*)k_pool;
+    fuse.v_out = (bf16*)v_pool;
+    fuse.eps = eps;
+    fuse.page_size = page_size;
+    int rc;
+    if (D == 64)
+        rc = launch_tc<64>(nullptr, k_pool, v_pool, partial, block_table, table_stride, kv_len, n_seqs, Hq, Hkv, page_size, scale,
+                           window, n_splits, tickets ? out : nullptr, tickets, stream, fuse);
+    else
+        rc = launch_tc<128>(nullptr, k_pool, v_pool, partial, block_table, table_stride, kv_len, n_seqs, Hq, Hkv, page_size, scale,
+                            window, n_splits, tickets ? out : nullptr, tickets, stream, fuse);
+    if (rc != 0 || tickets != nullptr) return rc;
+    return pb_decode_combine(dtype, partial, out, n_seqs * Hq, D, n_splits, stream);
 }

@@ -51,6 +51,7 @@ _SIGNATURES = {
     "pb_paged_attention_decode": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_paged_attention_decode_tc": [_I, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_decode_tc_supported": [_I, _I, _I, _I, _I],
+    "pb_paged_attention_decode_tc_qkv": [_I, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_paged_attention_decode_tc_fused": [_I, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "pb_paged_attention_prefill_tc": [_I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "pb_prefill_tc_supported": [_I, _I, _I, _I, _I],
@@ -87,6 +88,7 @@ _fns = {}
 # the entry points that launch kernels (the others answer questions on the host): what PULSAR_PROF=1 times
 _LAUNCHERS = {"embed", "scale_cap", "move_ids", "add_rmsnorm", "rope_table", "qk_norm_rope_write", "silu_mul", "gather_words",
               "paged_attention_generic", "paged_attention_decode", "paged_attention_decode_tc", "paged_attention_decode_tc_fused",
+              "paged_attention_decode_tc_qkv",
               "paged_attention_prefill_tc", "paged_attention_prefill_tcgen05", "gemm_skinny", "gemm_skinny_accumulate",
               "gemm_skinny_scaled", "gemm_tcgen05", "gemm_tcgen05_stream", "gemm_simt", "sample", "argmax", "table_update"}
 
@@ -704,6 +706,53 @@ def paged_attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
     check(fn(name)(code(q.dtype), _p(q), _p(k_pool), _p(v_pool), _p(out), _p(partial),
                    _p(block_table), block_table.shape[1], _p(kv_len), s, hq, hkv, d, page_size,
                    float(scale), int(window or 0), n_splits, stream()), name[3:], kernels=2)
+
+
+# A step of single tokens can leave the per-head norm, the rotation and the cache write of its projected rows to
+# the attention kernel (one launch less per layer in a chain of dependent launches).  PULSAR_FUSED_QK=0: a kernel
+# of its own does them, as in every other step.
+FUSED_QK = os.environ.get("PULSAR_FUSED_QK", "1") != "0"
+
+
+def decode_qkv_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, rotary: int, page_size: int) -> bool:
+    """Whether ``paged_attention_decode_qkv`` takes these sizes: those of the tensor-core decode kernel, heads of
+    their own keys and values, the whole head rotating."""
+    return bool(FUSED_QK and n_kv_heads > 0 and rotary == head_dim
+                and decode_tc_supported(dtype, n_heads, n_kv_heads, head_dim, page_size))
+
+
+def paged_attention_decode_qkv(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                               cos: torch.Tensor, sin: torch.Tensor, eps: float, slots: torch.Tensor, k_pool: torch.Tensor,
+                               v_pool: torch.Tensor, out: torch.Tensor, partial: torch.Tensor, block_table: torch.Tensor,
+                               kv_len: torch.Tensor, scale: float, window: Optional[int], n_splits: int,
+                               fused: Optional[bool] = None) -> None:
+    """Decode attention straight from the projected rows ``qkv`` [S, (Hq + 2 Hkv) * D] (bfloat16): the kernel
+    normalises and rotates the query heads and the newest key itself and writes that key and the value to
+    ``slots`` of their pools before it reads them.  ``out`` [S, Hq, D]; the rest as ``paged_attention_decode``."""
+    _cuda(qkv, q_weight, k_weight, cos, sin, slots, k_pool, v_pool, out, partial, block_table, kv_len)
+    _check_against(k_pool)
+    s, hq, d = out.shape
+    pages, hkv, page_size, d2 = k_pool.shape
+    assert d2 == d and v_pool.shape == k_pool.shape and qkv.shape == (s, (hq + 2 * hkv) * d) and kv_len.numel() == s
+    assert qkv.dtype == torch.bfloat16 and k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype and out.dtype == qkv.dtype
+    assert cos.shape == (s, d // 2) and sin.shape == cos.shape and cos.dtype == torch.float32 and sin.dtype == torch.float32
+    assert slots.dtype == torch.int32 and slots.numel() == s
+    assert block_table.dtype == torch.int32 and kv_len.dtype == torch.int32 and block_table.shape[0] == s
+    assert partial.dtype == torch.float32 and partial.numel() >= s * hq * n_splits * (d + 2)
+    for w in (q_weight, k_weight):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == d)
+    if fused is None:
+        fused = n_splits == 1
+    tickets = None
+    if fused and n_splits <= 64 and s * hkv <= _TICKETS:
+        tickets = _decode_tickets.get(qkv.device)
+        if tickets is None:
+            tickets = _decode_tickets[qkv.device] = torch.zeros(_TICKETS, dtype=torch.int32, device=qkv.device)
+    check(fn("pb_paged_attention_decode_tc_qkv")(code(qkv.dtype), _p(qkv), _p(q_weight), _p(k_weight), _p(cos), _p(sin), float(eps),
+                                                 _p(slots), _p(k_pool), _p(v_pool), _p(out), _p(partial), _p(tickets),
+                                                 _p(block_table), block_table.shape[1], _p(kv_len), s, hq, hkv, d, page_size,
+                                                 float(scale), int(window or 0), n_splits, stream()),
+          "paged_attention_decode_tc_qkv", kernels=1 if tickets is not None else 2)
 
 
 def prefill_tc_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> bool:

@@ -111,6 +111,15 @@ class Attention(Mixer):
         else:
             cos = sin = ctx.scratch("attn.norope", (n, 0), torch.float32)
             rotary = 0
+        if (ctx.all_decode and self.position is not None and qkv.dtype == torch.bfloat16
+                and ops.decode_qkv_supported(qkv.dtype, s.n_heads, n_kv, s.head_dim, rotary, cache.page_size)):
+            # a step of single tokens: the attention kernel normalises, rotates and writes the cache itself
+            o = ctx.scratch("attn.o", (n, s.n_heads, s.head_dim))
+            n_splits = ops.decode_splits(ctx.n_seqs, n_kv, cache.block_table.shape[1] * cache.page_size)
+            partial = ctx.scratch("attn.partial", (ctx.n_seqs * s.n_heads * n_splits * (s.head_dim + 2),), torch.float32)
+            ops.paged_attention_decode_qkv(qkv, self.q_norm, self.k_norm, cos, sin, s.qk_norm_eps or 0.0, cache.slots, cache.k_pool,
+                                           cache.v_pool, o, partial, cache.block_table, ctx.kv_len, s.scale, s.window, n_splits)
+            return o
         ops.qk_norm_rope_write(qkv, q, cache.k_pool if n_kv else None, cache.v_pool if n_kv else None,
                                cache.slots if n_kv else None, cos, sin, self.q_norm, self.k_norm,
                                s.qk_norm_eps or 0.0, s.n_heads, n_kv, s.head_dim, rotary, cache.page_size)

@@ -480,6 +480,58 @@ def test_attention_decode_tensor_cores(hq, hkv, d, page, window, n_splits):
     assert torch.equal(outs[0], outs[3]), "second fused launch on the same tickets"
 
 
+@pytest.mark.parametrize("hq,hkv,d,page", TC_SHAPES)
+@pytest.mark.parametrize("window", [None, 50])
+@pytest.mark.parametrize("n_splits,with_norm", [(1, True), (3, True), (37, False)])
+def test_attention_decode_from_the_projected_rows(hq, hkv, d, page, window, n_splits, with_norm):
+    """The decode kernel that takes the step's raw q/k/v rows (per-head norm, rotation and the cache write of the
+    newest key and value inside it) against the two kernels it stands in for: same pools afterwards (values bit
+    for bit, keys up to the order of the sum of squares), same output; contexts of one key (only the newest), at
+    tile and page edges; a wrong value left in the newest slot beforehand shows that the kernel reads what it wrote."""
+    from pulsar_b200 import ops
+    dtype = torch.bfloat16
+    assert ops.decode_qkv_supported(dtype, hq, hkv, d, d, page)
+    g = torch.Generator().manual_seed(12)
+    lens_kv = [1, 15, 16, 17, 63, 64, 65, 128, 129, 700, 1025]
+    s = len(lens_kv)
+    lens_q = [1] * s
+    case = _paged_case(g, lens_q, lens_kv, hq, hkv, d, page, dtype)
+    scale = 1.0 / math.sqrt(d)
+    qkv = (torch.randn(s, (hq + 2 * hkv) * d, generator=g) * 1.5).to(dtype)
+    qw = (1.0 + 0.2 * torch.randn(d, generator=g)) if with_norm else None
+    kw = (1.0 + 0.2 * torch.randn(d, generator=g)) if with_norm else None
+    ang = torch.rand(s, d // 2, generator=g, dtype=torch.float64) * 6.28
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    # slot of the newest position of every sequence; what lies there now must not be read
+    table = case["table"]
+    slots = torch.tensor([int(table[i, (kv - 1) // page]) * page + (kv - 1) % page for i, kv in enumerate(lens_kv)], dtype=torch.int32)
+    kp, vp = case["kp"].clone(), case["vp"].clone()
+    for i, sl in enumerate(slots.tolist()):
+        kp[sl // page, :, sl % page] = 77.0
+        vp[sl // page, :, sl % page] = -55.0
+    eps = 1e-5
+    # the two kernels
+    kp_a, vp_a = dev(kp), dev(vp)
+    q_a = torch.empty(s, hq, d, dtype=dtype, device="cuda")
+    ops.qk_norm_rope_write(dev(qkv), q_a, kp_a, vp_a, dev(slots), dev(cos), dev(sin), dev(qw) if with_norm else None,
+                           dev(kw) if with_norm else None, eps, hq, hkv, d, d, page)
+    out_a = torch.empty(s, hq, d, dtype=dtype, device="cuda")
+    partial = torch.empty(s * hq * n_splits * (d + 2), dtype=torch.float32, device="cuda")
+    ops.paged_attention_decode(q_a, kp_a, vp_a, out_a, partial, dev(table), dev(case["kv"]), scale, window, n_splits, tensor_cores=True)
+    # the one kernel, merged by the combine kernel and merged in the kernel
+    for fused in (False, True):
+        kp_b, vp_b = dev(kp), dev(vp)
+        out_b = torch.full((s, hq, d), float("nan"), dtype=dtype, device="cuda")
+        partial.fill_(float("nan"))
+        ops.paged_attention_decode_qkv(dev(qkv), dev(qw) if with_norm else None, dev(kw) if with_norm else None, dev(cos), dev(sin),
+                                       eps, dev(slots), kp_b, vp_b, out_b, partial, dev(table), dev(case["kv"]), scale, window,
+                                       n_splits, fused=fused)
+        assert torch.equal(vp_b, vp_a), "values in the pool"
+        close(kp_b, kp_a.double(), 1e-2, "keys in the pool")
+        close(out_b, out_a.double(), TOL[dtype], f"output, merged in the kernel: {fused}")
+    ops.check_wait_words()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_splits", [1, 3])
 def test_attention_decode_of_a_sequence_without_keys_gives_zeros(dtype, n_splits):
