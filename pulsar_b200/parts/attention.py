@@ -111,7 +111,10 @@ class Attention(Mixer):
         else:
             cos = sin = ctx.scratch("attn.norope", (n, 0), torch.float32)
             rotary = 0
-        if (ctx.all_decode and self.position is not None and qkv.dtype == torch.bfloat16
+        # (A lone sequence keeps the kernel of its own: its keys are cut into so many splits that every block's share
+        # is short, and the norm and rotation in each block's start then cost more than the launch they save:
+        # 2.990 against 2.973 ms per step; with two sequences and more the one kernel is ahead by 1.1 to 1.4 %.)
+        if (ctx.all_decode and ctx.n_seqs >= 2 and self.position is not None and qkv.dtype == torch.bfloat16
                 and ops.decode_qkv_supported(qkv.dtype, s.n_heads, n_kv, s.head_dim, rotary, cache.page_size)):
             # a step of single tokens: the attention kernel normalises, rotates and writes the cache itself
             o = ctx.scratch("attn.o", (n, s.n_heads, s.head_dim))
