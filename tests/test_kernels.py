@@ -195,6 +195,31 @@ def test_gemm_skinny(m, n, k):
     close(act, gate * torch.sigmoid(gate) * up, 1e-2, "swiglu")
 
 
+@pytest.mark.parametrize("m", [9, 12, 16])
+@pytest.mark.parametrize("n,k", [(9536, 256), (19072, 192), (24576, 512)])
+def test_gemm_skinny_with_32_rows_per_block(m, n, k):
+    """9 to 16 tokens against weights with many tiles: blocks of two row groups (and, with PULSAR_SKINNY_TALL=0 in the
+    environment, the blocks of 16 rows), plain and with the SwiGLU epilogue, against float64; one large weight in each
+    row group's range, a width of three k-blocks over eight warps (warps without work)."""
+    from pulsar_b200 import ops
+    g = torch.Generator().manual_seed(19)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).bfloat16()
+    w[n // 3, (5 * k) // 7] = 3.0
+    w[n // 3 + 16, k // 9] = -3.0
+    w[n - 1, k - 1] = 2.5
+    ref = a.double() @ w.double().T
+    for dt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 1e-2)):
+        out = torch.full((m, n), float("nan"), dtype=dt, device="cuda")
+        assert ops.gemm_skinny(dev(a), dev(w), out)
+        close(out, ref, tol, f"plain {dt}")
+    inter = n // 2
+    gate, up = ref[:, :inter], ref[:, inter:]
+    act = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops.gemm_skinny(dev(a), dev(w), act, swiglu=True)
+    close(act, gate * torch.sigmoid(gate) * up, 1e-2, "swiglu")
+
+
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("n,k", [(96, 192), (4096, 4096), (1024, 12288), (64, 2048), (192, 832), (640, 5120)])
 def test_gemm_skinny_adds_into_the_residual_and_prepares_the_norm_that_follows(m, n, k):
