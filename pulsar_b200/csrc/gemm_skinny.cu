@@ -193,10 +193,10 @@ __device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
 //            columns: y = bfloat16(x_new * next_w) and the block's part of sum_k x_new[token, k]^2.
 //   kScaled  the tokens come as such a prepared y; the sums of token m are scaled by rsqrt(sum / K + eps), the sum
 //            being the parts added in block order within a lane, then a fixed tree (float32: the same bits every
-//            time).  Block 0 adds them when the kernel starts and leaves the sums behind the parts with a word
-//            that says so; the other blocks, which need them only at their end, read that word then and take the
-//            sums, or, if block 0 should not have come that far, add the parts themselves in the same order.  No
-//            block waits for another.
+//            time).  A block of its own (block 0 of a grid with one block more than tiles) adds them and leaves
+//            the sums behind the parts with a word that says so; the blocks of the product, which need them only
+//            at their end, read that word then and take the sums, or, if block 0 should not have come that far,
+//            add the parts themselves in the same order.  No block waits for another.
 // rmsnorm(x) W^T = rsqrt(mean(x^2) + eps) * ((x * norm_w) W^T): the per-token factor commutes with the product.
 
 // rsqrt(mean(x^2) + eps) of every token into scale_s from the parts of its sum of squares; the sums themselves to
@@ -238,9 +238,26 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
     __shared__ __align__(16) unsigned char pre[kPre > 0 ? kWarps : 1][kPre > 0 ? kRows : 1][kPre > 0 ? kPreRow : 16];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    // kScaled: the grid has one block more than the product has tiles.  Block 0 only adds the parts of the sums of
+    // squares, leaves the sums behind them with the word that says so, and ends; it is the first block to be placed and
+    // is done long before any other block reaches its end, where the sums are wanted.
+    const int bid = kScaled ? (int)blockIdx.x - 1 : (int)blockIdx.x;
+    if constexpr (kScaled) {
+        if (bid < 0) {
+            pdl_wait();
+            float* sums = fuse.parts + (size_t)fuse.n_parts * M;
+            add_parts(fuse.parts, fuse.n_parts, M, K, fuse.eps, warp, lane, scale_s, sums);
+            __syncthreads();
+            if (tid == 0 && fuse.publish) {
+                __threadfence();
+                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sums + M), "r"(1u) : "memory");
+            }
+            return;
+        }
+    }
     int row_a, row_b;
-    if (MODE == kSwiGLU) { row_a = blockIdx.x * 8 + g; row_b = inter + blockIdx.x * 8 + g; }
-    else { row_a = blockIdx.x * kRows + g; row_b = row_a + 8; }
+    if (MODE == kSwiGLU) { row_a = bid * 8 + g; row_b = inter + bid * 8 + g; }
+    else { row_a = bid * kRows + g; row_b = row_a + 8; }
     const bf16* wa_p = w + (size_t)row_a * K + 16 * t;
     const bf16* wb_p = w + (size_t)row_b * K + 16 * t;
     const bf16* x_p[NT];
@@ -278,8 +295,8 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
         for (int i = 0; i < kRows / kRowsPerCopy; ++i) {
             const int r = i * kRowsPerCopy + r0;
             int wrow;
-            if (MODE == kSwiGLU) wrow = r < 8 ? blockIdx.x * 8 + r : inter + blockIdx.x * 8 + (r - 8);
-            else wrow = blockIdx.x * kRows + r;
+            if (MODE == kSwiGLU) wrow = r < 8 ? bid * 8 + r : inter + bid * 8 + (r - 8);
+            else wrow = bid * kRows + r;
             const bf16* src = w + (size_t)wrow * K + (size_t)(kb + kUnroll) * kWideK + chunk * 8;
             cp_async16_policy(smem_u32(&pre[warp][r][chunk * 16]), src, true, policy);
         }
@@ -289,23 +306,12 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
     // What the epilogue needs from the kernel before this one is asked for now and used at the end, so that no warp
     // waits for it: the parts of the sums of squares (copied to shared memory), the residual's old value.
     float old_value = 0.0f, next_weight = 0.0f;
-    if constexpr (kScaled) {
-        if (blockIdx.x == 0) {
-            float* sums = fuse.parts + (size_t)fuse.n_parts * M;
-            add_parts(fuse.parts, fuse.n_parts, M, K, fuse.eps, warp, lane, scale_s, sums);
-            __syncthreads();
-            if (tid == 0 && fuse.publish) {
-                __threadfence();
-                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sums + M), "r"(1u) : "memory");
-            }
-        }
-    }
     if constexpr (kAcc) {
         // the word that says "the sums are there" is taken back before the product behind the norm can look at it
-        if (fuse.next_w != nullptr && blockIdx.x == 0 && tid == 0)
+        if (fuse.next_w != nullptr && bid == 0 && tid == 0)
             __stcg(reinterpret_cast<unsigned int*>(fuse.parts + (size_t)(gridDim.x + 1) * M), 0u);
         if (tid < kRows * M) {
-            const int col = blockIdx.x * kRows + tid % kRows;
+            const int col = bid * kRows + tid % kRows;
             old_value = to_float(out[(size_t)(tid / kRows) * N + col]);
             if (fuse.next_w != nullptr) next_weight = __ldg(fuse.next_w + col);
         }
@@ -379,7 +385,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
         red[warp][g + 8][n * 8 + 2 * t + 1] = c[n][3];
     }
     if constexpr (kScaled) {
-        if (blockIdx.x != 0) {
+        {
             const float* sums = fuse.parts + (size_t)fuse.n_parts * M;
             if (tid == 0) {
                 unsigned int ready;
@@ -402,7 +408,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
 #pragma unroll
             for (int wi = 0; wi < kWarps; ++wi) { gate += red[wi][r][token]; up += red[wi][r + 8][token]; }
             if constexpr (kScaled) { gate *= scale_s[token]; up *= scale_s[token]; }
-            out[(size_t)token * inter + blockIdx.x * 8 + r] = from_float<OutT>(gate / (1.0f + expf(-gate)) * up);
+            out[(size_t)token * inter + bid * 8 + r] = from_float<OutT>(gate / (1.0f + expf(-gate)) * up);
         }
     } else {
         static_assert(kRows * 8 * NT <= kWarps * 32, "one output per thread");
@@ -412,7 +418,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
 #pragma unroll
             for (int wi = 0; wi < kWarps; ++wi) acc += red[wi][r][token];
             if constexpr (kScaled) acc *= scale_s[token];
-            const int col = blockIdx.x * kRows + r;
+            const int col = bid * kRows + r;
             OutT* dst = out + (size_t)token * N + col;
             if constexpr (kAcc) {
                 const float x_new = old_value + acc;
@@ -432,7 +438,7 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
                     float sum = 0.0f;
 #pragma unroll
                     for (int rr = 0; rr < kRows; ++rr) sum += square_s[tid][rr];
-                    __stcg(fuse.parts + (size_t)blockIdx.x * M + tid, sum);
+                    __stcg(fuse.parts + (size_t)bid * M + tid, sum);
                 }
             }
         }
@@ -768,7 +774,7 @@ PB_EXPORT int pb_gemm_skinny_scaled(int mode, const void* y, const void* w, void
     const int inter = mode == kSwiGLU ? N / 2 : 0;
     const bool many = tiles > 2 * sm_count();
 #define PB_SCALED(NT, MODE, KU, PRE) \
-    return launch_pdl(gemm_skinny_scaled_kernel<NT, MODE, KU, PRE>, tiles, kWarps * 32, 0, stream, yp, wp, (bf16*)out, M, N, K, inter, fuse)
+    return launch_pdl(gemm_skinny_scaled_kernel<NT, MODE, KU, PRE>, tiles + 1, kWarps * 32, 0, stream, yp, wp, (bf16*)out, M, N, K, inter, fuse)
     if (M <= 8) {
         if (mode == kSwiGLU) { if (many) PB_SCALED(1, kSwiGLU, 2, 2); PB_SCALED(1, kSwiGLU, 4, 2); }
         if (many) PB_SCALED(1, kPlain, 2, 2);
