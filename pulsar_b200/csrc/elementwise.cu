@@ -111,6 +111,13 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
                                        const int* __restrict__ rows, int width, float eps, int write_back) {
     __shared__ float scratch[32];
     pdl_trigger();      // a short kernel: let the next one (a weight-streaming product) start fetching its weights now
+    // the norm's weight depends on no kernel: it is here before the row is, not fetched after the sum is known
+    float w[VPT][4];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int i = (threadIdx.x + v * blockDim.x) * 4;
+        if (i < width) load4(weight + i, w[v]);
+    }
     pdl_wait();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -141,10 +148,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
     for (int v = 0; v < VPT; ++v) {
         const int i = (threadIdx.x + v * blockDim.x) * 4;
         if (i < width) {
-            float w[4], y[4];
-            load4(weight + i, w);
+            float y[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) y[e] = x[v][e] * inv * w[e];
+            for (int e = 0; e < 4; ++e) y[e] = x[v][e] * inv * w[v][e];
             store4(o + i, y);
         }
     }
@@ -283,8 +289,12 @@ qk_norm_rope_write_bf16_d128_kernel(const uint32_t* __restrict__ qkv, uint32_t* 
                                     const float2* __restrict__ sin_t, const float2* __restrict__ q_weight,
                                     const float2* __restrict__ k_weight, float eps, int Hq, int Hkv, int page_size, const PoolBounds bounds) {
     pdl_trigger();
-    pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31;
+    // the norms' weights depend on no kernel: they are here before the rows are
+    float2 qw_a = make_float2(1.f, 1.f), qw_b = qw_a, kw_a = qw_a, kw_b = qw_a;
+    if (q_weight) { qw_a = q_weight[lane]; qw_b = q_weight[lane + 32]; }
+    if (k_weight) { kw_a = k_weight[lane]; kw_b = k_weight[lane + 32]; }
+    pdl_wait();
     const int heads = Hq + 2 * Hkv;
     const int head0 = (blockIdx.y * 4 + (threadIdx.x >> 5)) * kRopeHeadsPerWarp;
     if (head0 >= heads) return;
@@ -324,7 +334,7 @@ qk_norm_rope_write_bf16_d128_kernel(const uint32_t* __restrict__ qkv, uint32_t* 
         const float2* w = is_q ? q_weight : k_weight;
         if (w) {
             const float inv = rsqrtf(warp_sum(a0 * a0 + a1 * a1 + b0 * b0 + b1 * b1) / 128.0f + eps);
-            const float2 wa = w[lane], wb = w[lane + 32];
+            const float2 wa = is_q ? qw_a : kw_a, wb = is_q ? qw_b : kw_b;
             a0 *= inv * wa.x; a1 *= inv * wa.y; b0 *= inv * wb.x; b1 *= inv * wb.y;
         }
         const __nv_bfloat162 lo = __floats2bfloat162_rn(a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
