@@ -194,15 +194,22 @@ __device__ __forceinline__ Wide load_x32(const void* p, bool ok) {
 //   kScaled  the tokens come as such a prepared y; the sums of token m are scaled by rsqrt(sum / K + eps), the sum
 //            being the parts added in block order within a lane, then a fixed tree (float32: the same bits every
 //            time).  A block of its own (block 0 of a grid with one block more than tiles) adds them and leaves
-//            the sums behind the parts with a word that says so; the blocks of the product, which need them only
-//            at their end, read that word then and take the sums, or, if block 0 should not have come that far,
-//            add the parts themselves in the same order.  No block waits for another.
+//            each sum behind the parts in one word with a tag that says it is there; the blocks of the product
+//            look for them when they start (all but the first round find them) and, if need be, once more at
+//            their end, where the sums are wanted; if block 0 should not have come that far they add the parts
+//            themselves in the same order.  No block waits for another.
 // rmsnorm(x) W^T = rsqrt(mean(x^2) + eps) * ((x * norm_w) W^T): the per-token factor commutes with the product.
 
-// rsqrt(mean(x^2) + eps) of every token into scale_s from the parts of its sum of squares; the sums themselves to
-// sums_out where that is not null.  All warps of the block.
+// A token's sum of squares travels as one 64-bit word, the sum beside a tag that says it is there (1): written and
+// read with one scalar access each, so that whoever reads the tag 1 holds the sum that was written with it.
+__device__ __forceinline__ unsigned long long pack_sum(float sum, unsigned int tag) {
+    return ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(sum);
+}
+
+// rsqrt(mean(x^2) + eps) of every token into scale_s from the parts of its sum of squares; the sums themselves, tagged,
+// to pairs_out where that is not null.  All warps of the block.
 __device__ __forceinline__ void add_parts(const float* parts, int n_parts, int M, int K, float eps, int warp, int lane,
-                                          float* scale_s, float* sums_out) {
+                                          float* scale_s, unsigned long long* pairs_out, unsigned int tag) {
     for (int token = warp; token < M; token += kWarps) {
         float sum = 0.0f;
         for (int b = lane; b < n_parts; b += 32) sum += __ldcg(parts + (size_t)b * M + token);
@@ -210,7 +217,7 @@ __device__ __forceinline__ void add_parts(const float* parts, int n_parts, int M
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         if (lane == 0) {
             scale_s[token] = rsqrtf(sum / (float)K + eps);
-            if (sums_out != nullptr) __stcg(sums_out + token, sum);
+            if (pairs_out != nullptr) __stcg(pairs_out + token, pack_sum(sum, tag));
         }
     }
 }
@@ -218,8 +225,8 @@ __device__ __forceinline__ void add_parts(const float* parts, int n_parts, int M
 struct SkinnyFuse {
     const float* next_w;      // kAcc: weight of the norm that follows, or null
     bf16* y;                  // kAcc: [M, N] prepared operand
-    float* parts;             // [n_parts, M] each producing block's part of the sums of squares, then [M] their sums,
-                              // then one word that says whether the sums are there
+    float* parts;             // [n_parts, M] each producing block's part of the sums of squares, then [M] 64-bit words:
+                              // a token's sum and the tag that says it is there
     int n_parts;              // blocks of the producing product
     int publish;              // kScaled: block 0 leaves the sums for the others (0: every block adds the parts itself)
     float eps;
@@ -233,7 +240,6 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
     constexpr int kPreRow = kPre * 128 + 16;          // bytes of a row's prefetched part in shared memory
     __shared__ float red[kWarps][kRows][8 * NT + 1];
     __shared__ float scale_s[kScaled ? 8 * NT : 1];                 // kScaled: rsqrt(mean(x^2) + eps) per token
-    __shared__ int ready_s;                                         // kScaled: the sums are there
     __shared__ float square_s[kAcc ? 8 * NT : 1][kAcc ? kRows : 1]; // kAcc: x_new^2 of the block's columns
     __shared__ __align__(16) unsigned char pre[kPre > 0 ? kWarps : 1][kPre > 0 ? kRows : 1][kPre > 0 ? kPreRow : 16];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -245,13 +251,8 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
     if constexpr (kScaled) {
         if (bid < 0) {
             pdl_wait();
-            float* sums = fuse.parts + (size_t)fuse.n_parts * M;
-            add_parts(fuse.parts, fuse.n_parts, M, K, fuse.eps, warp, lane, scale_s, sums);
-            __syncthreads();
-            if (tid == 0 && fuse.publish) {
-                __threadfence();
-                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sums + M), "r"(1u) : "memory");
-            }
+            add_parts(fuse.parts, fuse.n_parts, M, K, fuse.eps, warp, lane, scale_s,
+                      reinterpret_cast<unsigned long long*>(fuse.parts + (size_t)fuse.n_parts * M), fuse.publish ? 1u : 0u);
             return;
         }
     }
@@ -306,10 +307,15 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
     // What the epilogue needs from the kernel before this one is asked for now and used at the end, so that no warp
     // waits for it: the parts of the sums of squares (copied to shared memory), the residual's old value.
     float old_value = 0.0f, next_weight = 0.0f;
+    unsigned long long early = 0ull;
+    if constexpr (kScaled) {
+        // a block that starts after block 0 is done (every block but those of the first round) finds the sums already
+        if (tid < M) early = __ldcg(reinterpret_cast<const unsigned long long*>(fuse.parts + (size_t)fuse.n_parts * M) + tid);
+    }
     if constexpr (kAcc) {
-        // the word that says "the sums are there" is taken back before the product behind the norm can look at it
-        if (fuse.next_w != nullptr && bid == 0 && tid == 0)
-            __stcg(reinterpret_cast<unsigned int*>(fuse.parts + (size_t)(gridDim.x + 1) * M), 0u);
+        // the tags that say "the sum is there" are taken back before the product behind the norm can look at them
+        if (fuse.next_w != nullptr && bid == 0 && tid < M)
+            __stcg(reinterpret_cast<unsigned long long*>(fuse.parts + (size_t)gridDim.x * M) + tid, 0ull);
         if (tid < kRows * M) {
             const int col = bid * kRows + tid % kRows;
             old_value = to_float(out[(size_t)(tid / kRows) * N + col]);
@@ -385,20 +391,16 @@ skinny_wide_body(const bf16* __restrict__ x, const bf16* __restrict__ w, OutT* _
         red[warp][g + 8][n * 8 + 2 * t + 1] = c[n][3];
     }
     if constexpr (kScaled) {
-        {
-            const float* sums = fuse.parts + (size_t)fuse.n_parts * M;
-            if (tid == 0) {
-                unsigned int ready;
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(ready) : "l"(sums + M) : "memory");
-                ready_s = (int)ready;
-            }
-            __syncthreads();
-            if (ready_s) {
-                if (tid < M) scale_s[tid] = rsqrtf(__ldcg(sums + tid) / (float)K + fuse.eps);
-            } else {
-                add_parts(fuse.parts, fuse.n_parts, M, K, fuse.eps, warp, lane, scale_s, nullptr);
+        const unsigned long long* pairs = reinterpret_cast<const unsigned long long*>(fuse.parts + (size_t)fuse.n_parts * M);
+        unsigned long long pair = early;
+        if (!__syncthreads_and(tid >= M || (pair >> 32) == 1ull)) {
+            if (tid < M) pair = __ldcg(pairs + tid);                 // once more, now that block 0 has had the time
+            if (!__syncthreads_and(tid >= M || (pair >> 32) == 1ull)) {
+                add_parts(fuse.parts, fuse.n_parts, M, K, fuse.eps, warp, lane, scale_s, nullptr, 0u);
+                pair = 0ull;
             }
         }
+        if (tid < M && (pair >> 32) == 1ull) scale_s[tid] = rsqrtf(__uint_as_float((unsigned int)pair) / (float)K + fuse.eps);
     }
     __syncthreads();
     if (MODE == kSwiGLU) {
@@ -723,7 +725,7 @@ PB_EXPORT int pb_gemm_skinny_fused_supported(int mode, int M, int N, int K) {
 
 // residual[M, N] (float32) += x[M, K] W[N, K]^T.  With next_w (float32 [N], the weight of the RMSNorm that follows) also
 // y[M, N] = bfloat16(residual * next_w) and parts[N / 16, M] = each block's part of sum_n residual[m, n]^2; parts has
-// room for (N / 16 + 1) * M + 1 floats: behind the parts pb_gemm_skinny_scaled keeps the sums and a word, which this
+// room for (N / 16 + 2) * M floats: behind the parts pb_gemm_skinny_scaled keeps each token's sum with a tag, which this
 // kernel sets to zero; for
 // pb_gemm_skinny_scaled.
 PB_EXPORT int pb_gemm_skinny_accumulate(const void* x, const void* w, float* residual, int M, int N, int K, const float* next_w,
@@ -756,8 +758,8 @@ PB_EXPORT int pb_gemm_skinny_publish_sums(int on) {
 }
 
 // out = (y W^T) * rsqrt(sum_m / K + eps) per token m, sum_m = the K / 16 parts of parts[K / 16, M] added in order:
-// with y and parts from pb_gemm_skinny_accumulate this is rmsnorm(residual) W^T.  parts: (K / 16 + 1) * M + 1 floats,
-// the sums and one word behind the parts are written here.  mode 0: bfloat16 [M, N]; mode 1: the
+// with y and parts from pb_gemm_skinny_accumulate this is rmsnorm(residual) W^T.  parts: (K / 16 + 2) * M floats,
+// the tagged sums behind the parts are written here.  mode 0: bfloat16 [M, N]; mode 1: the
 // SwiGLU form, bfloat16 [M, N / 2].
 PB_EXPORT int pb_gemm_skinny_scaled(int mode, const void* y, const void* w, void* out, int M, int N, int K, float* parts,
                                     float eps, cudaStream_t stream) {

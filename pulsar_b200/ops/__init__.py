@@ -333,8 +333,8 @@ def fused_projection_supported(m: int, w: torch.Tensor, swiglu: bool = False) ->
 
 def norm_parts_numel(m: int, width: int) -> int:
     """Floats of the buffer in which ``linear_accumulate`` leaves the parts of the sums of squares of ``m`` rows
-    ``width`` wide: a part per 16 columns and row, the sums, one word."""
-    return (width // 16 + 1) * m + 1
+    ``width`` wide: a part per 16 columns and row, then a 64-bit word per row (its sum and a tag)."""
+    return (width // 16 + 2) * m
 
 
 def linear_accumulate(a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, next_norm_weight: Optional[torch.Tensor] = None,

@@ -254,8 +254,8 @@ def test_gemm_skinny_adds_into_the_residual_and_prepares_the_norm_that_follows(m
     close(res_dev, x, 2e-5, "accumulate twice")
     close(prepared, x * nw.double(), 1e-2, "prepared operand")
     close(parts[:(n // 16) * m].view(n // 16, m).sum(0), (x ** 2).sum(-1), 2e-5, "parts of the sums of squares")
-    word = parts[(n // 16 + 1) * m:].view(torch.int32)
-    assert int(word) == 0                                   # "the sums are not there yet"
+    tagged = parts[(n // 16) * m:].view(torch.int32).view(m, 2)          # per row: the sum's bits, the tag
+    assert int(tagged[:, 1].abs().sum()) == 0                # "the sums are not there yet"
     # the product behind the norm: rows of W2 [n2, n]
     n2 = 256
     w2 = (torch.randn(n2, n, generator=g) / n ** 0.5).bfloat16()
@@ -264,18 +264,18 @@ def test_gemm_skinny_adds_into_the_residual_and_prepares_the_norm_that_follows(m
     if n % 64 == 0:
         assert ops.linear_prenormed(prepared, parts, eps, dev(w2), out)
         close(out, exact, 1.6e-2, "product behind the prepared norm")
-        # its first block has left the sums behind the parts and said so; the producing product takes the word back
-        assert int(word) == 1
-        close(parts[(n // 16) * m:(n // 16 + 1) * m], (x ** 2).sum(-1), 2e-5, "sums of squares")
+        # its block 0 has left the sums behind the parts, each with its tag; the producing product takes the tags back
+        assert bool((tagged[:, 1] == 1).all())
+        close(tagged[:, 0].contiguous().view(torch.float32), (x ** 2).sum(-1), 2e-5, "sums of squares")
         if m > 2:
             assert float(out[1].float().abs().max()) == 0.0
         # the same bits on the path on which every block adds the parts itself (block 0 keeps its sums to itself)
-        word.zero_()
+        tagged.zero_()
         ops.fn("pb_gemm_skinny_publish_sums")(0)
         try:
             again = torch.full((m, n2), float("nan"), dtype=torch.bfloat16, device="cuda")
             assert ops.linear_prenormed(prepared, parts, eps, dev(w2), again)
-            assert int(word) == 0 and torch.equal(again, out)
+            assert int(tagged[:, 1].abs().sum()) == 0 and torch.equal(again, out)
         finally:
             ops.fn("pb_gemm_skinny_publish_sums")(1)
         act = torch.full((m, n2 // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
