@@ -21,7 +21,7 @@ line:
                bandwidth) and at batch 8 with contexts 2,048 and 3,072
   index_bytes  host-to-device bytes of a decode step of 64 sequences, with the block tables
                resident on the device and with whole tables sent
-  clocks       SM clock (median, maximum) and throttle reasons sampled through NVML every 5 ms
+  clocks       SM clock (median, maximum) and throttle reasons sampled through NVML every 2 ms
                during the timed steps
 
 --impl reference runs the unmodified reference (built by baseline/build_reference.py into
@@ -74,7 +74,7 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons while a timed region runs: NVML every 5 ms from a thread of this
+    """Samples SM clocks and throttle reasons while a timed region runs: NVML every 2 ms from a thread of this
     process (dozens of samples for a region of a few hundred ms), nvidia-smi every 100 ms where NVML cannot be had.
     It only reads."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -95,7 +95,7 @@ class ClockSampler:
                 self.rows.append([str(sm), str(mx)] + ["Active" if reasons & b else "Not Active" for b in bits])
             except Exception:
                 break
-            time.sleep(0.005)
+            time.sleep(0.002)
 
     def start(self):
         self.rows, self.stop_flag = [], threading.Event()
