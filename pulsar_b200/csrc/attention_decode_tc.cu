@@ -58,7 +58,8 @@ __global__ void __launch_bounds__(kWarps * 32, 2)
 decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                  float* __restrict__ partial, const int* __restrict__ block_table, int table_stride,
                  const int* __restrict__ kv_len, int Hq, int Hkv, int page_shift, float scale, int window, int n_splits,
-                 bf16* __restrict__ out, unsigned int* __restrict__ tickets, int evict_first, const PoolBounds bounds,
+                 bf16* __restrict__ out, unsigned int* __restrict__ tickets, int evict_first /* bit 0: the L2 hint; bits 4-6: tiles asked of L2 ahead */,
+                 const PoolBounds bounds,
                  const QkvFuse fuse) {
     constexpr int kTileBytes = kTile * D * 2;
     constexpr int kKSteps = D / 16;                   // k-steps of Q K^T
@@ -83,7 +84,7 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
     const int n_tiles = begin < end ? (end - 1) / kTile - tile0 + 1 : 0;
 
     // Every cached key and value is read by exactly one block of a step: with the policy the lines leave L2 first.
-    const uint64_t policy = evict_first ? l2_policy_evict_first() : 0;
+    const uint64_t policy = (evict_first & 1) ? l2_policy_evict_first() : 0;
     auto issue_tile = [&](int tile_index, int stage) {
         const uint32_t k_dst = smem_base + stage * 2 * kTileBytes;
         load_kv_tile<D, kWarps * 32>(k_dst, k_dst + kTileBytes, k_pool, v_pool, table, (tile0 + tile_index) * kTile, begin,
@@ -98,6 +99,10 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
         early[i] = i < n_tiles && (tile0 + i) * kTile + kTile - 1 < p;
         if (early[i]) { issue_tile(i, i); cp_async_commit(); }
     }
+    const int ahead = (evict_first >> 4) & 7;           // tiles beyond the two in flight that L2 is asked for
+    for (int i = 0; i < ahead; ++i)
+        if (kStages - 1 + i < n_tiles)
+            prefetch_kv_tile_l2<D>(k_pool, v_pool, table, (tile0 + kStages - 1 + i) * kTile, begin, end - 1, kvh, Hkv, page_shift, tid, bounds);
     pdl_wait();
 
     // Q fragments: rows = query heads of the group (zero beyond G), straight from global memory.
@@ -217,6 +222,8 @@ decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, co
         __syncthreads();                              // tile `it` has landed; stage (it-1) % kStages is free
         if (it + kStages - 1 < n_tiles) issue_tile(it + kStages - 1, (it + kStages - 1) % kStages);
         cp_async_commit();
+        if (ahead > 0 && it + kStages - 1 + ahead < n_tiles)
+            prefetch_kv_tile_l2<D>(k_pool, v_pool, table, (tile0 + it + kStages - 1 + ahead) * kTile, begin, end - 1, kvh, Hkv, page_shift, tid, bounds);
 
         const int stage = it % kStages;
         const uint32_t k_s = smem_base + stage * 2 * kTileBytes, v_s = k_s + kTileBytes;
@@ -400,7 +407,19 @@ int launch_tc(const void* q, const void* k_pool, const void* v_pool, float* part
         if (rc != cudaSuccess) return (int)rc;
         configured = true;
     }
-    static const int evict_first = [] { const char* v = getenv("PULSAR_DECODE_EVICT_FIRST"); return (v && v[0] == '0' && v[1] == 0) ? 0 : 1; }();
+    // With fewer blocks than SMs (a lone sequence) the two tiles a block has in flight are not enough to hide the
+    // memory's latency: such a launch also asks L2 for the two tiles behind them (2.828 against 2.858 ms per step of one
+    // sequence).  With more blocks that costs time (3.626 against 3.538 ms at 8 sequences, 10.31 against 9.49 at 64).
+    // PULSAR_DECODE_AHEAD=n forces n tiles for every launch.
+    static const int forced_ahead = [] { const char* a = getenv("PULSAR_DECODE_AHEAD"); return a ? (atoi(a) < 0 ? 0 : atoi(a) > 7 ? 7 : atoi(a)) : -1; }();
+    static const int sms = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) v = 0;
+        return v > 0 ? v : 148;
+    }();
+    static const int evict_flag = [] { const char* v = getenv("PULSAR_DECODE_EVICT_FIRST"); return (v && v[0] == '0' && v[1] == 0) ? 0 : 1; }();
+    const int ahead = forced_ahead >= 0 ? forced_ahead : ((long long)n_splits * Hkv * n_seqs <= sms ? 2 : 0);
+    const int evict_first = evict_flag | (ahead << 4);
     dim3 grid(n_splits, Hkv, n_seqs);
     return launch_pdl(decode_tc_kernel<D>, grid, kWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
                       partial, block_table, table_stride, kv_len, Hq, Hkv, page_shift, scale, window, n_splits, (bf16*)out, tickets, evict_first,

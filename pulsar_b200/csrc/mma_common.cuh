@@ -71,6 +71,25 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 // 2^page_shift keys (a power of two that divides 64); pools are [pages, Hkv, page, D].
 // Each thread keeps one 16-byte column and walks down the rows, so that the swizzle and
 // most of the address are loop constants.
+// Asks L2 for the pages of one 64-key tile of K and of V for kv head `kvh` (one bulk prefetch per page and pool,
+// issued by the first threads): a later load_kv_tile of the same tile then finds them there.  Pages without a key in
+// [first_key, last_key] are not touched.
+template <int D>
+__device__ __forceinline__ void prefetch_kv_tile_l2(const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                                                    const int* __restrict__ table, int key0, int first_key, int last_key, int kvh,
+                                                    int Hkv, int page_shift, int tid, const PoolBounds bounds = PoolBounds{0, nullptr}) {
+    const int pages = 64 >> page_shift;
+    if (tid >= 2 * pages) return;
+    const int pj = tid % pages;
+    const int key = key0 + (pj << page_shift);
+    if (key > last_key || key + (1 << page_shift) - 1 < first_key) return;
+    const int page = table[key >> page_shift];
+    if (!page_ok(page, bounds)) return;
+    const size_t page_elems = (size_t)D << page_shift;
+    const bf16* src = (tid < pages ? k_pool : v_pool) + (size_t)(page * Hkv + kvh) * page_elems;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)(page_elems * 2)) : "memory");
+}
+
 template <int D, int THREADS>
 __device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, const bf16* __restrict__ k_pool,
                                              const bf16* __restrict__ v_pool, const int* __restrict__ table, int key0,
